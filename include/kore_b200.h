@@ -1,0 +1,173 @@
+/*
+ * kore_b200 — C ABI of the B200-native BitLinear / QuatLinear forward path.
+ *
+ * This is the boundary a KORE maintainer binds from Rust (or any FFI): plain
+ * pointers and sizes, integer status codes, an opaque weight handle with a paired
+ * destroy.  Each entry point names the KORE interface it stands in for (path inside
+ * the KORE source tree : lines).
+ *
+ * Orientation follows KORE's kernels: M = out_features (weight rows),
+ * K = in_features, N = tokens.  Module-shaped calls take x as [N,K] and write
+ * y as [N,M]; the kernel-shaped one-shots take b as [K,N] and write c as [M,N].
+ *
+ * Arithmetic (W2A8): activations are quantised per token to int8 by absmax
+ * (s = max|x|/127, or 1.0 when max|x| < 1e-8; q = clamp(rne(x/s), -127, 127)),
+ * accumulated against the 2-bit weights in int32, and dequantised as
+ * y = (float(acc) * w_scale[m]) * s[n] (+ bias[m]) with separately rounded
+ * multiplies.  There is no CPU fallback anywhere behind this header: every entry
+ * point that computes runs CUDA kernels for sm_100a or fails with a status code.
+ *
+ * Threading: a handle is immutable after creation; any number of host threads may
+ * call the forward entry points on one handle concurrently, each on its own stream.
+ * Per-call scratch comes from the stream-ordered allocator unless the caller passes
+ * a workspace.  Calls return after enqueueing work on the given stream unless they
+ * take host pointers, in which case they synchronise before returning.
+ */
+#ifndef KORE_B200_H
+#define KORE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  Names follow KoreError (crates/kore-core/src/error.rs:6-51) and
+ * CudaError (crates/kore-kernels/src/cuda/context.rs:58-80). */
+enum {
+    KB_OK = 0,
+    KB_ERR_SHAPE = 1,       /* KoreError::ShapeMismatch                      */
+    KB_ERR_STORAGE = 2,     /* KoreError::StorageError ("... too small")     */
+    KB_ERR_DTYPE = 3,       /* KoreError::UnsupportedDType                   */
+    KB_ERR_CUDA = 4,        /* CudaError::{DeviceInit,LaunchError,MemoryError} */
+    KB_ERR_TIMEOUT = 6,     /* a bounded device-side wait gave up             */
+    KB_ERR_BAD_HANDLE = 7,  /* null or destroyed handle                      */
+    KB_ERR_INVALID = 8,     /* null pointer / unknown enum / zero dimension  */
+    KB_ERR_UNSUPPORTED = 9  /* shape outside what the chosen kernel accepts   */
+};
+
+enum { KB_TERNARY = 0, KB_QUATERNARY = 1 };
+
+/* weight quantiser used by *_from_f32 */
+enum {
+    KB_QUANT_REFERENCE = 0, /* KORE's: per-row absmax (ternary: +-1 beyond threshold; quaternary: absmax/3) */
+    KB_QUANT_ABSMEAN = 1    /* ternary only: per-tensor s = mean|W|, clamp(rne(W/s),-1,1) */
+};
+
+/* kernel choice for kb_linear_forward_ex (test hook; AUTO picks by N) */
+enum { KB_PATH_AUTO = 0, KB_PATH_GEMV = 1, KB_PATH_GEMM_TC = 2 };
+
+typedef struct kb_linear kb_linear; /* opaque: device-resident 2-bit weights + scales + bias */
+typedef void *kb_stream;            /* a cudaStream_t; NULL = the legacy default stream */
+
+/* ---- library ---- */
+const char *kb_version(void);
+/* Thread-local description of the last failure on the calling thread, worded like
+ * the KoreError it mirrors (e.g. "a_packed too small: need 52 bytes, got 51"). */
+const char *kb_last_error(void);
+int kb_device_count(int *count);
+
+/* ---- weights: construction (one-time upload + repack into the device layout) ---- */
+
+/* Takes BitLinear::packed_weights()/scales() or QuatLinear::packed_weights()/scales()
+ * unchanged: ternary base-243 [M,ceil(K/5)] or quaternary 2-bit LSB-first
+ * [M,ceil(K/4)], f32 per-row scales [M], optional bias [M] (host pointers).
+ * Stands in for the per-call upload in QuatLinear::try_cuda_forward
+ * (crates/kore-nn/src/quat_linear.rs:166-197) and the per-call row decode in
+ * ternary_matmul (crates/kore-kernels/src/cpu_ternary_matmul.rs:59-62). */
+int kb_linear_create_from_ref_packed(int kind, const uint8_t *packed, size_t packed_len,
+                                     const float *scales, size_t scales_len, const float *bias,
+                                     size_t m, size_t k, int device, kb_linear **out);
+
+/* BitLinear::new / QuatLinear::new (crates/kore-nn/src/bit_linear.rs:48-77,
+ * quat_linear.rs:46-73): quantise f32 weights [M,K] (host) on the device. */
+int kb_linear_create_from_f32(int kind, int quantiser, const float *w, const float *bias, size_t m,
+                              size_t k, float threshold, int device, kb_linear **out);
+
+/* Null-tolerant, like the frees of crates/kore-edge/src/ffi.rs:131-161. */
+void kb_linear_destroy(kb_linear *h);
+
+/* in_features()/out_features()/weight_memory_bytes() (bit_linear.rs:104-132);
+ * weight_bytes reports the reference's own formula: wire-format bytes + 4*M. */
+int kb_linear_info(const kb_linear *h, size_t *m, size_t *k, int *kind, int *device,
+                   size_t *weight_bytes);
+/* scales() (bit_linear.rs:124-127): copies the M per-row scales to the host. */
+int kb_linear_scales(const kb_linear *h, float *scales, size_t scales_len);
+/* packed_weights() (bit_linear.rs:119-122): re-encodes the device layout into the
+ * reference wire format on the device and copies it to the host. */
+int kb_linear_packed_weights(const kb_linear *h, uint8_t *packed, size_t packed_len);
+/* dequantize_weights() (bit_linear.rs:145-167, quat_linear.rs:134-157): f32 [M,K] to the host. */
+int kb_linear_dequantize_weights(const kb_linear *h, float *w, size_t w_len);
+
+/* ---- activations ---- */
+
+/* Fused per-token absmax int8 quantiser (device pointers).  xq is [N,ldq] with
+ * ldq >= K, ldq % 16 == 0, columns K..ldq-1 written as zero; sx[N] scales;
+ * sumq[N] = sum of each row's codes (nullable).  No counterpart in the reference,
+ * whose activations stay f32 (cpu_ternary_matmul.rs:37-40). */
+int kb_quantize_act_i8(const float *x, size_t n, size_t k, int8_t *xq, size_t ldq, float *sx,
+                       int32_t *sumq, kb_stream stream);
+/* Leading dimension the forward entry points expect for pre-quantised activations. */
+size_t kb_act_ld(size_t k);
+
+/* ---- forward (device pointers) ---- */
+
+/* Module::forward for BitLinear / QuatLinear (bit_linear.rs:175-237,
+ * quat_linear.rs:245-319): x [N,K] f32 -> y [N,M] f32, bias added when present.
+ * Picks the decode GEMV for small N and the tcgen05 GEMM otherwise. */
+int kb_linear_forward(const kb_linear *h, const float *x, size_t n, float *y, kb_stream stream);
+
+/* Same with an explicit kernel choice, an optional raw-accumulator output
+ * acc [N,M] int32 (nullable) and an optional caller workspace (nullable; size from
+ * kb_linear_workspace_bytes).  in_dim is checked against K like the ShapeMismatch
+ * test of bit_linear.rs:179-184.  ldy is the row stride of y and acc in elements
+ * (0 = M), which lets a column-sharded layer write straight into its slice. */
+int kb_linear_forward_ex(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *y,
+                         size_t ldy, int32_t *acc, int path, void *workspace,
+                         size_t workspace_bytes, kb_stream stream);
+size_t kb_linear_workspace_bytes(const kb_linear *h, size_t n);
+
+/* Forward from activations the caller already quantised (kb_quantize_act_i8 layout,
+ * ldq = kb_act_ld(K)).  y and acc are each nullable (not both). */
+int kb_linear_forward_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const float *sx,
+                         const int32_t *sumq, size_t n, float *y, size_t ldy, int32_t *acc,
+                         int path, kb_stream stream);
+
+/* ---- forward (host pointers; what a Tensor-in/Tensor-out caller uses) ---- */
+
+/* Copies x to the device, runs kb_linear_forward, copies y back, synchronises.
+ * Replaces the H2D/launch/D2H sequence of quat_linear.rs:183-212. */
+int kb_linear_forward_host(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *y);
+
+/* ---- kernel-shaped one-shots (host pointers), signatures of
+ * ternary_matmul (crates/kore-kernels/src/cpu_ternary_matmul.rs:29-36) and
+ * quat_matmul (crates/kore-kernels/src/cpu_quat_matmul.rs:22-29):
+ * a_packed wire format, b [K,N] f32, c [M,N] f32.  Buffer-length checks and their
+ * messages follow :44-57 / :37-50. */
+int kb_ternary_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scales,
+                      size_t scales_len, const float *b, float *c, size_t m, size_t n, size_t k);
+int kb_quat_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scales, size_t scales_len,
+                   const float *b, float *c, size_t m, size_t n, size_t k);
+
+/* pack_weights_ternary (cpu_ternary_matmul.rs:198-240) and pack_weights_quaternary
+ * (cpu_quat_matmul.rs:174-214), computed on the device: f32 [M,K] host in,
+ * wire-format bytes and per-row scales out (host). */
+int kb_pack_weights_ternary(const float *w, size_t m, size_t k, float threshold, uint8_t *packed,
+                            size_t packed_len, float *scales, size_t scales_len, int device);
+int kb_pack_weights_quaternary(const float *w, size_t m, size_t k, uint8_t *packed,
+                               size_t packed_len, float *scales, size_t scales_len, int device);
+
+/* ---- plumbing used by the host layers ---- */
+
+/* Raw device pointers of a handle (read-only views; valid until destroy). */
+int kb_linear_device_ptrs(const kb_linear *h, const void **w2, size_t *row_bytes,
+                          const float **scales, const float **bias);
+/* Device-side status word of the last tcgen05 GEMM launched by the calling thread
+ * on this handle: 0 = clean, otherwise a code saying which bounded wait gave up. */
+int kb_linear_last_device_status(const kb_linear *h, kb_stream stream, int *status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KORE_B200_H */

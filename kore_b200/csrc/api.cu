@@ -1,0 +1,472 @@
+// extern "C" boundary of kore_b200 (see include/kore_b200.h).  Host logic only:
+// argument checks in the wording of the KoreError they mirror, handle lifetime,
+// workspace, kernel choice.  No arithmetic happens on the host.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+
+namespace kb {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+    return fail(KB_ERR_CUDA, "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    cudaError_t err = cudaSuccess;
+    explicit DeviceGuard(int dev) {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != dev) {
+            err = cudaSetDevice(dev);
+            switched = (err == cudaSuccess);
+        }
+    }
+    ~DeviceGuard() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+
+static size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static size_t wire_row_bytes(int kind, size_t k) { return kind == KB_TERNARY ? (k + 4) / 5 : (k + 3) / 4; }
+
+static const Linear *check(const kb_linear *h) {
+    const Linear *L = reinterpret_cast<const Linear *>(h);
+    if (!L || L->magic != HANDLE_MAGIC) {
+        fail(KB_ERR_BAD_HANDLE, "null or destroyed kb_linear handle");
+        return nullptr;
+    }
+    return L;
+}
+
+static void free_linear(Linear *L) {
+    if (!L) return;
+    DeviceGuard g(L->device);
+    if (L->w2) cudaFree(L->w2);
+    if (L->scales) cudaFree(L->scales);
+    if (L->bias) cudaFree(L->bias);
+    if (L->dev_status) cudaFree(L->dev_status);
+    L->magic = 0;
+    delete L;
+}
+
+// allocate the device-side containers of a layer (weights zeroed, scales unset)
+static int alloc_linear(int kind, size_t m, size_t k, const float *bias, int device, Linear **out) {
+    if (kind != KB_TERNARY && kind != KB_QUATERNARY) return fail(KB_ERR_INVALID, "unknown kind %d", kind);
+    if (m == 0 || k == 0) return fail(KB_ERR_INVALID, "zero dimension: m=%zu k=%zu", m, k);
+    if (m >= (1u << 30) || k >= (1u << 30)) return fail(KB_ERR_UNSUPPORTED, "dimension too large: m=%zu k=%zu", m, k);
+    Linear *L = new (std::nothrow) Linear();
+    if (!L) return fail(KB_ERR_CUDA, "host allocation failed");
+    memset(L, 0, sizeof(*L));
+    L->magic = HANDLE_MAGIC;
+    L->kind = kind;
+    L->device = device;
+    L->m = m;
+    L->k = k;
+    L->kp = round_up(k, K_ALIGN);
+    L->m_alloc = round_up(m, M_ALIGN);
+    L->row_bytes = L->kp / 4;
+    L->mul = kind == KB_TERNARY ? 1 : 2;
+    L->off = kind == KB_TERNARY ? 1 : 3;
+    cudaError_t e;
+    if ((e = cudaMalloc(&L->w2, L->m_alloc * L->row_bytes)) != cudaSuccess ||
+        (e = cudaMalloc(&L->scales, L->m_alloc * sizeof(float))) != cudaSuccess ||
+        (e = cudaMalloc(&L->dev_status, sizeof(int))) != cudaSuccess ||
+        (e = cudaMemset(L->dev_status, 0, sizeof(int))) != cudaSuccess) {
+        free_linear(L);
+        return cuda_fail(e, "weight allocation");
+    }
+    if (bias) {
+        if ((e = cudaMalloc(&L->bias, L->m_alloc * sizeof(float))) != cudaSuccess ||
+            (e = cudaMemset(L->bias, 0, L->m_alloc * sizeof(float))) != cudaSuccess ||
+            (e = cudaMemcpy(L->bias, bias, m * sizeof(float), cudaMemcpyHostToDevice)) != cudaSuccess) {
+            free_linear(L);
+            return cuda_fail(e, "bias upload");
+        }
+    }
+    *out = L;
+    return KB_OK;
+}
+
+static size_t workspace_bytes(const Linear *L, size_t n) {
+    return round_up(n * L->kp, 256) + 2 * round_up(n * 4, 256);
+}
+
+static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim, float *y, size_t ldy,
+                        int32_t *acc, int path, void *workspace, size_t ws_bytes, cudaStream_t stream) {
+    if (in_dim != L->k)
+        return fail(KB_ERR_SHAPE, "shape mismatch: expected [%zu], got last dimension %zu", L->k, in_dim);
+    if (!x || (!y && !acc)) return fail(KB_ERR_INVALID, "null activation or output pointer");
+    if (ldy != 0 && ldy < L->m) return fail(KB_ERR_INVALID, "ldy %zu smaller than out_features %zu", ldy, L->m);
+    if (n == 0) return KB_OK;
+    if (path == KB_PATH_AUTO) path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : KB_PATH_GEMM_TC;
+    FwdArgs a = {};
+    a.lin = L; a.n = n; a.y = y; a.acc = acc; a.ldy = ldy;
+    if (path == KB_PATH_GEMV) {
+        a.x = x;
+        return launch_gemv(a, stream);
+    }
+    if (path != KB_PATH_GEMM_TC) return fail(KB_ERR_INVALID, "unknown path %d", path);
+    const size_t need = workspace_bytes(L, n);
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    bool own = false;
+    if (!ws) {
+        KB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&ws), need, stream));
+        own = true;
+    } else if (ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255)) {
+        return fail(KB_ERR_STORAGE, "workspace too small or misaligned: need %zu bytes (256-byte aligned), got %zu", need, ws_bytes);
+    }
+    int8_t *xq = reinterpret_cast<int8_t *>(ws);
+    float *sx = reinterpret_cast<float *>(ws + round_up(n * L->kp, 256));
+    int32_t *sumq = reinterpret_cast<int32_t *>(ws + round_up(n * L->kp, 256) + round_up(n * 4, 256));
+    int rc = launch_act_quant(x, n, L->k, xq, L->kp, sx, sumq, stream);
+    if (rc == KB_OK) {
+        a.xq = xq; a.ldq = L->kp; a.sx = sx; a.sumq = sumq;
+        rc = launch_gemm_tc(a, stream);
+    }
+    if (own) {
+        cudaError_t e = cudaFreeAsync(ws, stream);
+        if (rc == KB_OK && e != cudaSuccess) rc = cuda_fail(e, "workspace free");
+    }
+    return rc;
+}
+
+// x [n,k] host -> y [n,m] host, on this thread's private stream
+static int forward_host_impl(const Linear *L, const float *x, size_t n, size_t in_dim, float *y) {
+    if (in_dim != L->k)
+        return fail(KB_ERR_SHAPE, "shape mismatch: expected [%zu], got last dimension %zu", L->k, in_dim);
+    if (!x || !y) return fail(KB_ERR_INVALID, "null activation or output pointer");
+    if (n == 0) return KB_OK;
+    cudaStream_t st = cudaStreamPerThread;
+    float *dx = nullptr, *dy = nullptr;
+    KB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dx), n * L->k * sizeof(float), st));
+    cudaError_t e = cudaMallocAsync(reinterpret_cast<void **>(&dy), n * L->m * sizeof(float), st);
+    if (e != cudaSuccess) { cudaFreeAsync(dx, st); return cuda_fail(e, "output allocation"); }
+    int rc = KB_OK;
+    if ((e = cudaMemcpyAsync(dx, x, n * L->k * sizeof(float), cudaMemcpyHostToDevice, st)) != cudaSuccess)
+        rc = cuda_fail(e, "activation upload");
+    if (rc == KB_OK) rc = forward_impl(L, dx, n, in_dim, dy, 0, nullptr, KB_PATH_AUTO, nullptr, 0, st);
+    if (rc == KB_OK && (e = cudaMemcpyAsync(y, dy, n * L->m * sizeof(float), cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+        rc = cuda_fail(e, "output download");
+    cudaFreeAsync(dx, st);
+    cudaFreeAsync(dy, st);
+    e = cudaStreamSynchronize(st);
+    if (rc == KB_OK && e != cudaSuccess) rc = cuda_fail(e, "stream synchronize");
+    return rc;
+}
+
+static int create_from_wire(int kind, const uint8_t *packed, size_t packed_len, const float *scales,
+                            size_t scales_len, const float *bias, size_t m, size_t k, int device,
+                            Linear **out) {
+    if (!packed || !scales || !out) return fail(KB_ERR_INVALID, "null pointer");
+    if (kind != KB_TERNARY && kind != KB_QUATERNARY) return fail(KB_ERR_INVALID, "unknown kind %d", kind);
+    const size_t need = m * wire_row_bytes(kind, k);
+    if (packed_len < need)
+        return fail(KB_ERR_STORAGE, "a_packed too small: need %zu bytes, got %zu", need, packed_len);
+    if (scales_len < m) return fail(KB_ERR_STORAGE, "a_scales too small: need %zu, got %zu", m, scales_len);
+    DeviceGuard g(device);
+    if (g.err != cudaSuccess) return cuda_fail(g.err, "cudaSetDevice");
+    Linear *L = nullptr;
+    int rc = alloc_linear(kind, m, k, bias, device, &L);
+    if (rc) return rc;
+    uint8_t *dwire = nullptr;
+    cudaError_t e;
+    if ((e = cudaMalloc(&dwire, need)) != cudaSuccess) { free_linear(L); return cuda_fail(e, "wire staging"); }
+    if ((e = cudaMemcpy(dwire, packed, need, cudaMemcpyHostToDevice)) != cudaSuccess ||
+        (e = cudaMemset(L->scales, 0, L->m_alloc * sizeof(float))) != cudaSuccess ||
+        (e = cudaMemcpy(L->scales, scales, m * sizeof(float), cudaMemcpyHostToDevice)) != cudaSuccess) {
+        cudaFree(dwire); free_linear(L);
+        return cuda_fail(e, "weight upload");
+    }
+    rc = launch_repack_wire(kind, dwire, m, k, L->w2, L->row_bytes, L->m_alloc, 0);
+    e = cudaDeviceSynchronize();
+    cudaFree(dwire);
+    if (rc == KB_OK && e != cudaSuccess) rc = cuda_fail(e, "repack");
+    if (rc == KB_OK) rc = encode_weight_tmap(L);
+    if (rc) { free_linear(L); return rc; }
+    *out = L;
+    return KB_OK;
+}
+
+static int create_from_f32(int kind, int quantiser, const float *w, const float *bias, size_t m, size_t k,
+                           float threshold, int device, Linear **out) {
+    if (!w || !out) return fail(KB_ERR_INVALID, "null pointer");
+    if (kind != KB_TERNARY && kind != KB_QUATERNARY) return fail(KB_ERR_INVALID, "unknown kind %d", kind);
+    if (quantiser != KB_QUANT_REFERENCE && !(quantiser == KB_QUANT_ABSMEAN && kind == KB_TERNARY))
+        return fail(KB_ERR_INVALID, "quantiser %d not defined for kind %d", quantiser, kind);
+    DeviceGuard g(device);
+    if (g.err != cudaSuccess) return cuda_fail(g.err, "cudaSetDevice");
+    Linear *L = nullptr;
+    int rc = alloc_linear(kind, m, k, bias, device, &L);
+    if (rc) return rc;
+    float *dw = nullptr;
+    cudaError_t e;
+    if ((e = cudaMalloc(&dw, m * k * sizeof(float))) != cudaSuccess) { free_linear(L); return cuda_fail(e, "f32 weight staging"); }
+    if ((e = cudaMemcpy(dw, w, m * k * sizeof(float), cudaMemcpyHostToDevice)) != cudaSuccess) {
+        cudaFree(dw); free_linear(L);
+        return cuda_fail(e, "weight upload");
+    }
+    rc = launch_quantise_f32(kind, quantiser, dw, m, k, threshold, L->w2, L->row_bytes, L->m_alloc, L->scales, 0);
+    e = cudaDeviceSynchronize();
+    cudaFree(dw);
+    if (rc == KB_OK && e != cudaSuccess) rc = cuda_fail(e, "quantise");
+    if (rc == KB_OK) rc = encode_weight_tmap(L);
+    if (rc) { free_linear(L); return rc; }
+    *out = L;
+    return KB_OK;
+}
+
+// reference-shaped one-shot: b [K,N] host -> c [M,N] host
+static int one_shot(int kind, const uint8_t *a_packed, size_t a_len, const float *a_scales, size_t scales_len,
+                    const float *b, float *c, size_t m, size_t n, size_t k) {
+    if (!b || !c) return fail(KB_ERR_INVALID, "null pointer");
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    Linear *L = nullptr;
+    int rc = create_from_wire(kind, a_packed, a_len, a_scales, scales_len, nullptr, m, k, device, &L);
+    if (rc) return rc;
+    if (n == 0) { free_linear(L); return KB_OK; }
+    cudaStream_t st = cudaStreamPerThread;
+    float *db = nullptr, *dx = nullptr, *dy = nullptr, *dc = nullptr;
+    const size_t xb = n * k * sizeof(float), yb = n * m * sizeof(float);
+    if ((e = cudaMalloc(&db, xb)) != cudaSuccess || (e = cudaMalloc(&dx, xb)) != cudaSuccess ||
+        (e = cudaMalloc(&dy, yb)) != cudaSuccess || (e = cudaMalloc(&dc, yb)) != cudaSuccess) {
+        rc = cuda_fail(e, "one-shot allocation");
+    }
+    if (rc == KB_OK && (e = cudaMemcpyAsync(db, b, xb, cudaMemcpyHostToDevice, st)) != cudaSuccess) rc = cuda_fail(e, "b upload");
+    if (rc == KB_OK) rc = launch_transpose_f32(db, k, n, dx, st);  // [K,N] -> [N,K]
+    if (rc == KB_OK) rc = forward_impl(L, dx, n, k, dy, 0, nullptr, KB_PATH_AUTO, nullptr, 0, st);
+    if (rc == KB_OK) rc = launch_transpose_f32(dy, n, m, dc, st);  // [N,M] -> [M,N]
+    if (rc == KB_OK && (e = cudaMemcpyAsync(c, dc, yb, cudaMemcpyDeviceToHost, st)) != cudaSuccess) rc = cuda_fail(e, "c download");
+    e = cudaStreamSynchronize(st);
+    if (rc == KB_OK && e != cudaSuccess) rc = cuda_fail(e, "stream synchronize");
+    cudaFree(db); cudaFree(dx); cudaFree(dy); cudaFree(dc);
+    free_linear(L);
+    return rc;
+}
+
+static int pack_weights(int kind, const float *w, size_t m, size_t k, float threshold, uint8_t *packed,
+                        size_t packed_len, float *scales, size_t scales_len, int device) {
+    if (!w || !packed || !scales) return fail(KB_ERR_INVALID, "null pointer");
+    const size_t need = m * wire_row_bytes(kind, k);
+    if (packed_len < need) return fail(KB_ERR_STORAGE, "packed too small: need %zu bytes, got %zu", need, packed_len);
+    if (scales_len < m) return fail(KB_ERR_STORAGE, "scales too small: need %zu, got %zu", m, scales_len);
+    Linear *L = nullptr;
+    int rc = create_from_f32(kind, KB_QUANT_REFERENCE, w, nullptr, m, k, threshold, device, &L);
+    if (rc) return rc;
+    rc = kb_linear_packed_weights(reinterpret_cast<kb_linear *>(L), packed, packed_len);
+    if (rc == KB_OK) rc = kb_linear_scales(reinterpret_cast<kb_linear *>(L), scales, scales_len);
+    free_linear(L);
+    return rc;
+}
+
+}  // namespace kb
+
+using namespace kb;
+
+extern "C" {
+
+const char *kb_version(void) { return "kore_b200 0.1.0 (sm_100a)"; }
+const char *kb_last_error(void) { return g_err; }
+
+int kb_device_count(int *count) {
+    if (!count) return fail(KB_ERR_INVALID, "null pointer");
+    cudaError_t e = cudaGetDeviceCount(count);
+    if (e != cudaSuccess) { *count = 0; return cuda_fail(e, "cudaGetDeviceCount"); }
+    return KB_OK;
+}
+
+int kb_linear_create_from_ref_packed(int kind, const uint8_t *packed, size_t packed_len, const float *scales,
+                                     size_t scales_len, const float *bias, size_t m, size_t k, int device,
+                                     kb_linear **out) {
+    if (out) *out = nullptr;
+    Linear *L = nullptr;
+    int rc = create_from_wire(kind, packed, packed_len, scales, scales_len, bias, m, k, device, &L);
+    if (rc == KB_OK) *out = reinterpret_cast<kb_linear *>(L);
+    return rc;
+}
+
+int kb_linear_create_from_f32(int kind, int quantiser, const float *w, const float *bias, size_t m, size_t k,
+                              float threshold, int device, kb_linear **out) {
+    if (out) *out = nullptr;
+    Linear *L = nullptr;
+    int rc = create_from_f32(kind, quantiser, w, bias, m, k, threshold, device, &L);
+    if (rc == KB_OK) *out = reinterpret_cast<kb_linear *>(L);
+    return rc;
+}
+
+void kb_linear_destroy(kb_linear *h) {
+    Linear *L = reinterpret_cast<Linear *>(h);
+    if (!L || L->magic != HANDLE_MAGIC) return;
+    free_linear(L);
+}
+
+int kb_linear_info(const kb_linear *h, size_t *m, size_t *k, int *kind, int *device, size_t *weight_bytes) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    if (m) *m = L->m;
+    if (k) *k = L->k;
+    if (kind) *kind = L->kind;
+    if (device) *device = L->device;
+    if (weight_bytes) *weight_bytes = L->m * wire_row_bytes(L->kind, L->k) + 4 * L->m;
+    return KB_OK;
+}
+
+int kb_linear_scales(const kb_linear *h, float *scales, size_t scales_len) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    if (!scales) return fail(KB_ERR_INVALID, "null pointer");
+    if (scales_len < L->m) return fail(KB_ERR_STORAGE, "scales too small: need %zu, got %zu", L->m, scales_len);
+    DeviceGuard g(L->device);
+    KB_CUDA(cudaMemcpy(scales, L->scales, L->m * sizeof(float), cudaMemcpyDeviceToHost));
+    return KB_OK;
+}
+
+int kb_linear_packed_weights(const kb_linear *h, uint8_t *packed, size_t packed_len) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    if (!packed) return fail(KB_ERR_INVALID, "null pointer");
+    const size_t need = L->m * wire_row_bytes(L->kind, L->k);
+    if (packed_len < need) return fail(KB_ERR_STORAGE, "packed too small: need %zu bytes, got %zu", need, packed_len);
+    DeviceGuard g(L->device);
+    uint8_t *d = nullptr;
+    KB_CUDA(cudaMalloc(&d, need));
+    int rc = launch_export_wire(L->kind, L->w2, L->row_bytes, L->m, L->k, d, 0);
+    cudaError_t e = cudaMemcpy(packed, d, need, cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    if (rc == KB_OK && e != cudaSuccess) rc = cuda_fail(e, "wire download");
+    return rc;
+}
+
+int kb_linear_dequantize_weights(const kb_linear *h, float *w, size_t w_len) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    if (!w) return fail(KB_ERR_INVALID, "null pointer");
+    if (w_len < L->m * L->k) return fail(KB_ERR_STORAGE, "w too small: need %zu, got %zu", L->m * L->k, w_len);
+    DeviceGuard g(L->device);
+    float *d = nullptr;
+    KB_CUDA(cudaMalloc(&d, L->m * L->k * sizeof(float)));
+    int rc = launch_dequantize(L->kind, L->w2, L->row_bytes, L->scales, L->m, L->k, d, 0);
+    cudaError_t e = cudaMemcpy(w, d, L->m * L->k * sizeof(float), cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    if (rc == KB_OK && e != cudaSuccess) rc = cuda_fail(e, "weight download");
+    return rc;
+}
+
+size_t kb_act_ld(size_t k) { return round_up(k, K_ALIGN); }
+
+int kb_quantize_act_i8(const float *x, size_t n, size_t k, int8_t *xq, size_t ldq, float *sx, int32_t *sumq,
+                       kb_stream stream) {
+    if (!x || !xq || !sx) return fail(KB_ERR_INVALID, "null pointer");
+    if (k == 0) return fail(KB_ERR_INVALID, "zero dimension: k=0");
+    if (ldq < k || ldq % 16 || (reinterpret_cast<uintptr_t>(xq) & 15))
+        return fail(KB_ERR_INVALID, "xq must be 16-byte aligned with ldq >= k and ldq %% 16 == 0 (ldq=%zu, k=%zu)", ldq, k);
+    return launch_act_quant(x, n, k, xq, ldq, sx, sumq, static_cast<cudaStream_t>(stream));
+}
+
+int kb_linear_forward(const kb_linear *h, const float *x, size_t n, float *y, kb_stream stream) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    DeviceGuard g(L->device);
+    return forward_impl(L, x, n, L->k, y, 0, nullptr, KB_PATH_AUTO, nullptr, 0, static_cast<cudaStream_t>(stream));
+}
+
+int kb_linear_forward_ex(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *y, size_t ldy,
+                         int32_t *acc, int path, void *workspace, size_t workspace_bytes_, kb_stream stream) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    DeviceGuard g(L->device);
+    return forward_impl(L, x, n, in_dim, y, ldy, acc, path, workspace, workspace_bytes_,
+                        static_cast<cudaStream_t>(stream));
+}
+
+size_t kb_linear_workspace_bytes(const kb_linear *h, size_t n) {
+    const Linear *L = check(h);
+    return L ? workspace_bytes(L, n) : 0;
+}
+
+int kb_linear_forward_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const float *sx, const int32_t *sumq,
+                         size_t n, float *y, size_t ldy, int32_t *acc, int path, kb_stream stream) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    if (!xq || !sx || !sumq || (!y && !acc)) return fail(KB_ERR_INVALID, "null pointer");
+    if (ldy != 0 && ldy < L->m) return fail(KB_ERR_INVALID, "ldy %zu smaller than out_features %zu", ldy, L->m);
+    if (n == 0) return KB_OK;
+    DeviceGuard g(L->device);
+    if (path == KB_PATH_AUTO) path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : KB_PATH_GEMM_TC;
+    FwdArgs a = {};
+    a.lin = L; a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq; a.n = n; a.y = y; a.acc = acc; a.ldy = ldy;
+    if (path == KB_PATH_GEMV) return launch_gemv(a, static_cast<cudaStream_t>(stream));
+    if (path == KB_PATH_GEMM_TC) return launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
+    return fail(KB_ERR_INVALID, "unknown path %d", path);
+}
+
+int kb_linear_forward_host(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *y) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    DeviceGuard g(L->device);
+    return forward_host_impl(L, x, n, in_dim, y);
+}
+
+int kb_ternary_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scales, size_t scales_len,
+                      const float *b, float *c, size_t m, size_t n, size_t k) {
+    return one_shot(KB_TERNARY, a_packed, a_len, a_scales, scales_len, b, c, m, n, k);
+}
+
+int kb_quat_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scales, size_t scales_len, const float *b,
+                   float *c, size_t m, size_t n, size_t k) {
+    return one_shot(KB_QUATERNARY, a_packed, a_len, a_scales, scales_len, b, c, m, n, k);
+}
+
+int kb_pack_weights_ternary(const float *w, size_t m, size_t k, float threshold, uint8_t *packed, size_t packed_len,
+                            float *scales, size_t scales_len, int device) {
+    return pack_weights(KB_TERNARY, w, m, k, threshold, packed, packed_len, scales, scales_len, device);
+}
+
+int kb_pack_weights_quaternary(const float *w, size_t m, size_t k, uint8_t *packed, size_t packed_len,
+                               float *scales, size_t scales_len, int device) {
+    return pack_weights(KB_QUATERNARY, w, m, k, 0.0f, packed, packed_len, scales, scales_len, device);
+}
+
+int kb_linear_device_ptrs(const kb_linear *h, const void **w2, size_t *row_bytes, const float **scales,
+                          const float **bias) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    if (w2) *w2 = L->w2;
+    if (row_bytes) *row_bytes = L->row_bytes;
+    if (scales) *scales = L->scales;
+    if (bias) *bias = L->bias;
+    return KB_OK;
+}
+
+int kb_linear_last_device_status(const kb_linear *h, kb_stream stream, int *status) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    if (!status) return fail(KB_ERR_INVALID, "null pointer");
+    DeviceGuard g(L->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    KB_CUDA(cudaMemcpyAsync(status, L->dev_status, sizeof(int), cudaMemcpyDeviceToHost, st));
+    KB_CUDA(cudaStreamSynchronize(st));
+    if (*status != 0) {
+        KB_CUDA(cudaMemsetAsync(L->dev_status, 0, sizeof(int), st));
+        KB_CUDA(cudaStreamSynchronize(st));
+        return fail(KB_ERR_TIMEOUT, "tcgen05 GEMM gave up on a bounded wait (device code %d)", *status);
+    }
+    return KB_OK;
+}
+
+}  // extern "C"

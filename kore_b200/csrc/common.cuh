@@ -1,0 +1,100 @@
+// Shared declarations of the kore_b200 CUDA library (sm_100a only).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/kore_b200.h"
+
+namespace kb {
+
+// ---- device weight layout -------------------------------------------------------
+// Weights live in HBM as 2-bit codes, row-major [M_alloc][Kp/4] bytes with
+// Kp = K rounded up to 128 (row stride is a multiple of 32 bytes) and M_alloc = M
+// rounded up to 128 (pad rows are zero).  Inside every aligned 32-bit word, which
+// covers 16 consecutive k, element k0 + 4*j + b sits in byte b at bits [2j+1:2j].
+// (word >> 2j) & 0x03030303 therefore yields the four codes of k0+4j .. k0+4j+3 as
+// four bytes in memory order — the operand order of dp4a and of an int8 MMA tile.
+//   ternary   : code = trit + 1      value = code - 1       (pad code 1)
+//   quaternary: code = KORE's index  value = 2*code - 3     (pad code 0)
+// Kernels accumulate S = sum(code * xq) and correct in the epilogue:
+//   acc = mul * S - off * sum(xq),  (mul, off) = (1,1) ternary, (2,3) quaternary.
+constexpr int K_ALIGN = 128;
+constexpr int M_ALIGN = 128;
+
+constexpr uint32_t HANDLE_MAGIC = 0x4b42324cu;  // "KB2L"
+
+// status word written by the tcgen05 GEMM when a bounded wait gives up
+enum DevStatus : int {
+    DEV_OK = 0,
+    DEV_TIMEOUT_TMA_EMPTY = 1,
+    DEV_TIMEOUT_UNPACK_FULL = 2,
+    DEV_TIMEOUT_MMA_FULL = 3,
+    DEV_TIMEOUT_MMA_UNPACKED = 4,
+    DEV_TIMEOUT_MMA_TMEM_EMPTY = 5,
+    DEV_TIMEOUT_EPI_TMEM_FULL = 6,
+    DEV_TIMEOUT_DRAIN = 7
+};
+
+struct Linear {
+    uint32_t magic;
+    int kind;
+    int device;
+    size_t m, k, kp, m_alloc, row_bytes;
+    uint8_t *w2;    // [m_alloc][row_bytes]
+    float *scales;  // [m_alloc]
+    float *bias;    // [m_alloc] or nullptr
+    int mul, off;
+    CUtensorMap tmap_w;  // 2-D map over w2 for the GEMM (box 32 B x 128 rows)
+    bool has_tmap;
+    int *dev_status;  // one int in device memory
+};
+
+// ---- error plumbing (api.cu) -----------------------------------------------------
+int fail(int code, const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+#define KB_CUDA(expr)                                      \
+    do {                                                   \
+        cudaError_t _e = (expr);                           \
+        if (_e != cudaSuccess) return kb::cuda_fail(_e, #expr); \
+    } while (0)
+
+// ---- launchers (each returns a KB_* status; all work is enqueued on `stream`) ----
+int launch_act_quant(const float *x, size_t n, size_t k, int8_t *xq, size_t ldq, float *sx,
+                     int32_t *sumq, cudaStream_t stream);
+
+int launch_repack_wire(int kind, const uint8_t *wire, size_t m, size_t k, uint8_t *w2,
+                       size_t row_bytes, size_t m_alloc, cudaStream_t stream);
+int launch_quantise_f32(int kind, int quantiser, const float *w, size_t m, size_t k, float threshold,
+                        uint8_t *w2, size_t row_bytes, size_t m_alloc, float *scales,
+                        cudaStream_t stream);
+int launch_export_wire(int kind, const uint8_t *w2, size_t row_bytes, size_t m, size_t k,
+                       uint8_t *wire, cudaStream_t stream);
+int launch_dequantize(int kind, const uint8_t *w2, size_t row_bytes, const float *scales, size_t m,
+                      size_t k, float *w, cudaStream_t stream);
+int launch_transpose_f32(const float *src, size_t rows, size_t cols, float *dst, cudaStream_t stream);
+
+struct FwdArgs {
+    const Linear *lin;
+    // exactly one of (x) or (xq, sx, sumq) is set
+    const float *x;
+    const int8_t *xq;
+    size_t ldq;
+    const float *sx;
+    const int32_t *sumq;
+    size_t n;
+    float *y;      // nullable
+    int32_t *acc;  // nullable
+    size_t ldy;
+};
+// decode GEMV; when args.x is set the activation quantiser is fused into its prologue
+int launch_gemv(const FwdArgs &a, cudaStream_t stream);
+// tcgen05 int8 GEMM; needs pre-quantised activations
+int launch_gemm_tc(const FwdArgs &a, cudaStream_t stream);
+bool gemv_supports(const Linear *lin, size_t n);
+bool gemm_tc_supports(const Linear *lin, size_t n);
+int encode_weight_tmap(Linear *lin);
+
+}  // namespace kb

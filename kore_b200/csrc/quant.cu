@@ -1,0 +1,332 @@
+// Activation quantiser and load-time weight kernels (sm_100a).
+//
+//  * act_quant_kernel      per-token absmax -> int8, scale and code sum, one CTA per token
+//  * repack_*              reference wire format (base-243 / 2-bit LSB-first) -> device layout
+//  * quantise_*            f32 weights -> device layout + per-row scales, on the device
+//  * export_wire / dequantize   device layout -> wire format / f32
+//
+// Everything here is HBM-bound byte work: one thread produces one aligned 32-bit word
+// of the destination so stores coalesce; nothing is reshaped into a GEMM.
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace kb {
+
+// ------------------------------------------------------------------ activations
+
+// One CTA per token row.  Pass 1 reduces max|x|, pass 2 (re-reading the row from L1/L2)
+// emits 16 codes per thread-iteration as one 16-byte store.  The division is an IEEE
+// round-to-nearest divide and the conversion rounds half to even, so the codes equal
+// the CPU definition bit for bit.
+template <bool VEC4>
+__global__ void __launch_bounds__(256) act_quant_kernel(const float *__restrict__ x, int k,
+                                                        int8_t *__restrict__ xq, int ldq,
+                                                        float *__restrict__ sx,
+                                                        int32_t *__restrict__ sumq) {
+    __shared__ float red_f[32];
+    __shared__ int red_i[32];
+    const size_t t = blockIdx.x;
+    const float *row = x + t * (size_t)k;
+    float amax = 0.0f;
+    if (VEC4) {
+        const float4 *row4 = reinterpret_cast<const float4 *>(row);
+        for (int i = threadIdx.x; i < k / 4; i += blockDim.x) {
+            float4 v = row4[i];
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
+    } else {
+        for (int i = threadIdx.x; i < k; i += blockDim.x) amax = fmaxf(amax, fabsf(row[i]));
+    }
+    amax = block_reduce_max(amax, red_f);
+    const float s = amax < 1e-8f ? 1.0f : __fdiv_rn(amax, 127.0f);
+
+    int local_sum = 0;
+    int8_t *qrow = xq + t * (size_t)ldq;
+    for (int g = threadIdx.x; g < ldq / 16; g += blockDim.x) {
+        uint32_t out[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const int base = g * 16 + w * 4;
+            float v[4];
+            if (VEC4 && base + 3 < k) {
+                float4 f = *reinterpret_cast<const float4 *>(row + base);
+                v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] = (base + e < k) ? row[base + e] : 0.0f;
+            }
+            uint32_t word = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                int q = quantise_one(v[e], s);
+                local_sum += q;
+                word |= (uint32_t)(q & 0xff) << (8 * e);
+            }
+            out[w] = word;
+        }
+        *reinterpret_cast<uint4 *>(qrow + g * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+    local_sum = block_reduce_sum(local_sum, red_i);
+    if (threadIdx.x == 0) {
+        sx[t] = s;
+        if (sumq) sumq[t] = local_sum;
+    }
+}
+
+int launch_act_quant(const float *x, size_t n, size_t k, int8_t *xq, size_t ldq, float *sx,
+                     int32_t *sumq, cudaStream_t stream) {
+    if (n == 0) return KB_OK;
+    const bool vec4 = (k % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    if (vec4)
+        act_quant_kernel<true><<<(unsigned)n, 256, 0, stream>>>(x, (int)k, xq, (int)ldq, sx, sumq);
+    else
+        act_quant_kernel<false><<<(unsigned)n, 256, 0, stream>>>(x, (int)k, xq, (int)ldq, sx, sumq);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "act_quant launch");
+}
+
+// ------------------------------------------------------------------ weights
+
+// position of element i (0..15) of a 32-bit word: byte i%4, bit pair i/4
+__device__ __forceinline__ uint32_t place_code(uint32_t code, int i) {
+    return code << (8 * (i & 3) + 2 * (i >> 2));
+}
+__device__ __forceinline__ uint32_t take_code(uint32_t word, int i) {
+    return (word >> (8 * (i & 3) + 2 * (i >> 2))) & 3u;
+}
+
+// base-243 digit i of a wire byte as a device code (digit 0/1/2 = trit -1/0/+1 = code);
+// bytes >= 243 decode to five zero trits (code 1)
+__device__ __forceinline__ uint32_t trit_code_of_byte(uint32_t byte, int i) {
+    if (byte >= 243u) return 1u;
+    const uint32_t p3[5] = {1u, 3u, 9u, 27u, 81u};
+    return (byte / p3[i]) % 3u;
+}
+
+// one thread per destination word; rows >= m and k >= K are filled with the pad code
+template <int KIND>
+__global__ void repack_wire_kernel(const uint8_t *__restrict__ wire, int m, int k, int kpw,
+                                   uint32_t *__restrict__ w2, int row_words, size_t total_words) {
+    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (idx >= total_words) return;
+    const int row = (int)(idx / row_words);
+    const int k0 = (int)(idx % row_words) * 16;
+    const uint32_t pad = KIND == KB_TERNARY ? 1u : 0u;
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int kk = k0 + i;
+        uint32_t code = pad;
+        if (row < m && kk < k) {
+            if (KIND == KB_TERNARY)
+                code = trit_code_of_byte(wire[(size_t)row * kpw + kk / 5], kk % 5);
+            else
+                code = (wire[(size_t)row * kpw + kk / 4] >> (2 * (kk % 4))) & 3u;
+        }
+        word |= place_code(code, i);
+    }
+    w2[idx] = word;
+}
+
+int launch_repack_wire(int kind, const uint8_t *wire, size_t m, size_t k, uint8_t *w2,
+                       size_t row_bytes, size_t m_alloc, cudaStream_t stream) {
+    const int row_words = (int)(row_bytes / 4);
+    const size_t total = m_alloc * (size_t)row_words;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (kind == KB_TERNARY)
+        repack_wire_kernel<KB_TERNARY><<<blocks, 256, 0, stream>>>(
+            wire, (int)m, (int)k, (int)((k + 4) / 5), reinterpret_cast<uint32_t *>(w2), row_words, total);
+    else
+        repack_wire_kernel<KB_QUATERNARY><<<blocks, 256, 0, stream>>>(
+            wire, (int)m, (int)k, (int)((k + 3) / 4), reinterpret_cast<uint32_t *>(w2), row_words, total);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "repack launch");
+}
+
+// per-row max|w| -> scale (mode 0: absmax, mode 1: absmax/3), 1.0 below 1e-8
+__global__ void __launch_bounds__(256) row_scale_kernel(const float *__restrict__ w, int k, int mode,
+                                                        float *__restrict__ scales) {
+    __shared__ float red[32];
+    const float *row = w + blockIdx.x * (size_t)k;
+    float amax = 0.0f;
+    for (int i = threadIdx.x; i < k; i += blockDim.x) amax = fmaxf(amax, fabsf(row[i]));
+    amax = block_reduce_max(amax, red);
+    if (threadIdx.x == 0)
+        scales[blockIdx.x] = amax < 1e-8f ? 1.0f : (mode == 0 ? amax : __fdiv_rn(amax, 3.0f));
+}
+
+// absmean: each row summed in ascending k in f64 by one thread, then the row sums are
+// added in ascending m by a single thread — the exact order the CPU definition uses,
+// so the f32 scale is reproducible bit for bit.  Load-time only.
+__global__ void abs_rowsum_f64_kernel(const float *__restrict__ w, int m, int k,
+                                      double *__restrict__ rowsum) {
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= m) return;
+    const float *p = w + (size_t)row * k;
+    double s = 0.0;
+    for (int i = 0; i < k; ++i) s += (double)fabsf(p[i]);
+    rowsum[row] = s;
+}
+__global__ void absmean_finish_kernel(const double *__restrict__ rowsum, int m, int k, int m_alloc,
+                                      float *__restrict__ scales) {
+    __shared__ float s_sh;
+    if (threadIdx.x == 0) {
+        double total = 0.0;
+        for (int r = 0; r < m; ++r) total += rowsum[r];
+        float s = (float)(total / ((double)m * (double)k));
+        s_sh = s < 1e-8f ? 1.0f : s;
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < m_alloc; r += blockDim.x) scales[r] = r < m ? s_sh : 1.0f;
+}
+
+// MODE 0: ternary, reference rule (sign beyond threshold); 1: ternary absmean (rne, clamp);
+// 2: quaternary reference rule
+template <int MODE>
+__global__ void quantise_f32_kernel(const float *__restrict__ w, int m, int k, float thr,
+                                    const float *__restrict__ scales, uint32_t *__restrict__ w2,
+                                    int row_words, size_t total_words) {
+    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (idx >= total_words) return;
+    const int row = (int)(idx / row_words);
+    const int k0 = (int)(idx % row_words) * 16;
+    const uint32_t pad = MODE == 2 ? 0u : 1u;
+    const float scale = row < m ? scales[row] : 1.0f;
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int kk = k0 + i;
+        uint32_t code = pad;
+        if (row < m && kk < k) {
+            const float nrm = __fdiv_rn(w[(size_t)row * k + kk], scale);
+            if (MODE == 0) {
+                code = nrm > thr ? 2u : (nrm < -thr ? 0u : 1u);
+            } else if (MODE == 1) {
+                const float q = rintf(nrm);
+                code = q > 1.0f ? 2u : (q < -1.0f ? 0u : (uint32_t)((int)q + 1));
+            } else {
+                code = nrm < -2.0f ? 0u : (nrm < 0.0f ? 1u : (nrm < 2.0f ? 2u : 3u));
+            }
+        }
+        word |= place_code(code, i);
+    }
+    w2[idx] = word;
+}
+
+__global__ void fill_f32_kernel(float *p, size_t from, size_t to, float v) {
+    const size_t i = from + blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (i < to) p[i] = v;
+}
+
+int launch_quantise_f32(int kind, int quantiser, const float *w, size_t m, size_t k, float threshold,
+                        uint8_t *w2, size_t row_bytes, size_t m_alloc, float *scales,
+                        cudaStream_t stream) {
+    const int row_words = (int)(row_bytes / 4);
+    const size_t total = m_alloc * (size_t)row_words;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    uint32_t *dst = reinterpret_cast<uint32_t *>(w2);
+    if (kind == KB_TERNARY && quantiser == KB_QUANT_ABSMEAN) {
+        double *rowsum = nullptr;
+        KB_CUDA(cudaMallocAsync(&rowsum, m * sizeof(double), stream));
+        abs_rowsum_f64_kernel<<<(unsigned)((m + 63) / 64), 64, 0, stream>>>(w, (int)m, (int)k, rowsum);
+        absmean_finish_kernel<<<1, 256, 0, stream>>>(rowsum, (int)m, (int)k, (int)m_alloc, scales);
+        quantise_f32_kernel<1><<<blocks, 256, 0, stream>>>(w, (int)m, (int)k, threshold, scales, dst,
+                                                           row_words, total);
+        KB_CUDA(cudaFreeAsync(rowsum, stream));
+    } else {
+        row_scale_kernel<<<(unsigned)m, 256, 0, stream>>>(w, (int)k, kind == KB_TERNARY ? 0 : 1, scales);
+        if (m_alloc > m)
+            fill_f32_kernel<<<(unsigned)((m_alloc - m + 255) / 256), 256, 0, stream>>>(scales, m, m_alloc, 1.0f);
+        if (kind == KB_TERNARY)
+            quantise_f32_kernel<0><<<blocks, 256, 0, stream>>>(w, (int)m, (int)k, threshold, scales, dst,
+                                                               row_words, total);
+        else
+            quantise_f32_kernel<2><<<blocks, 256, 0, stream>>>(w, (int)m, (int)k, threshold, scales, dst,
+                                                               row_words, total);
+    }
+    return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "quantise launch");
+}
+
+// device layout -> wire format, one thread per wire byte.  Pad slots follow the
+// reference packers: Zero trits for ternary, code 0 for quaternary.
+template <int KIND>
+__global__ void export_wire_kernel(const uint32_t *__restrict__ w2, int row_words, int m, int k,
+                                   int kpw, uint8_t *__restrict__ wire) {
+    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (idx >= (size_t)m * kpw) return;
+    const int row = (int)(idx / kpw);
+    const int kb_ = (int)(idx % kpw);
+    const uint32_t *wrow = w2 + (size_t)row * row_words;
+    uint32_t byte = 0;
+    if (KIND == KB_TERNARY) {
+        uint32_t mult = 1;
+        for (int i = 0; i < 5; ++i) {
+            const int kk = kb_ * 5 + i;
+            const uint32_t code = kk < k ? take_code(wrow[kk / 16], kk % 16) : 1u;
+            byte += code * mult;
+            mult *= 3;
+        }
+    } else {
+        for (int i = 0; i < 4; ++i) {
+            const int kk = kb_ * 4 + i;
+            const uint32_t code = kk < k ? take_code(wrow[kk / 16], kk % 16) : 0u;
+            byte |= code << (2 * i);
+        }
+    }
+    wire[idx] = (uint8_t)byte;
+}
+
+int launch_export_wire(int kind, const uint8_t *w2, size_t row_bytes, size_t m, size_t k,
+                       uint8_t *wire, cudaStream_t stream) {
+    const int kpw = (int)(kind == KB_TERNARY ? (k + 4) / 5 : (k + 3) / 4);
+    const size_t total = m * (size_t)kpw;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    const uint32_t *src = reinterpret_cast<const uint32_t *>(w2);
+    if (kind == KB_TERNARY)
+        export_wire_kernel<KB_TERNARY><<<blocks, 256, 0, stream>>>(src, (int)(row_bytes / 4), (int)m, (int)k, kpw, wire);
+    else
+        export_wire_kernel<KB_QUATERNARY><<<blocks, 256, 0, stream>>>(src, (int)(row_bytes / 4), (int)m, (int)k, kpw, wire);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "export launch");
+}
+
+__global__ void dequantize_kernel(const uint32_t *__restrict__ w2, int row_words, int kind,
+                                  const float *__restrict__ scales, int m, int k,
+                                  float *__restrict__ w) {
+    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (idx >= (size_t)m * k) return;
+    const int row = (int)(idx / k), kk = (int)(idx % k);
+    const int code = (int)take_code(w2[(size_t)row * row_words + kk / 16], kk % 16);
+    const float v = kind == KB_TERNARY ? (float)(code - 1) : (float)(2 * code - 3);
+    w[idx] = __fmul_rn(v, scales[row]);
+}
+
+int launch_dequantize(int kind, const uint8_t *w2, size_t row_bytes, const float *scales, size_t m,
+                      size_t k, float *w, cudaStream_t stream) {
+    const size_t total = m * k;
+    dequantize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+        reinterpret_cast<const uint32_t *>(w2), (int)(row_bytes / 4), kind, scales, (int)m, (int)k, w);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "dequantize launch");
+}
+
+// [rows, cols] -> [cols, rows] through a padded shared-memory tile (coalesced both ways)
+__global__ void transpose_f32_kernel(const float *__restrict__ src, int rows, int cols,
+                                     float *__restrict__ dst) {
+    __shared__ float tile[32][33];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const int r = r0 + j, c = c0 + threadIdx.x;
+        if (r < rows && c < cols) tile[j][threadIdx.x] = src[(size_t)r * cols + c];
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const int c = c0 + j, r = r0 + threadIdx.x;
+        if (r < rows && c < cols) dst[(size_t)c * rows + r] = tile[threadIdx.x][j];
+    }
+}
+
+int launch_transpose_f32(const float *src, size_t rows, size_t cols, float *dst, cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return KB_OK;
+    dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
+    transpose_f32_kernel<<<grid, dim3(32, 8), 0, stream>>>(src, (int)rows, (int)cols, dst);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "transpose launch");
+}
+
+}  // namespace kb

@@ -1,0 +1,276 @@
+"""Host-side mirror of KORE's ``BitLinear`` / ``QuatLinear`` modules over the C ABI.
+
+Names, argument meaning and error behaviour follow
+``crates/kore-nn/src/bit_linear.rs`` / ``quat_linear.rs`` and the Python signatures of
+``python/kore/kore.pyi:104-116``.  Inputs may be numpy arrays (host: copied to the
+device and back inside one C call) or CUDA ``torch`` tensors (device pointers, work
+enqueued on torch's current stream).  All arithmetic runs in the CUDA library; this
+file only checks shapes and moves pointers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _cabi
+from ._cabi import KoreError, PATH_AUTO, PATH_GEMM_TC, PATH_GEMV, QUATERNARY, TERNARY  # noqa: F401
+
+
+def _is_torch(x) -> bool:
+    return type(x).__module__.startswith("torch")
+
+
+def _current_stream_ptr(device_index: int) -> int:
+    import torch
+
+    return torch.cuda.current_stream(device_index).cuda_stream
+
+
+class _QuantLinear:
+    """Common body of BitLinear and QuatLinear (the reference duplicates it per type)."""
+
+    KIND = TERNARY
+    NAME = "BitLinear"
+
+    def __init__(self):
+        self._h = None
+        self.in_features = 0
+        self.out_features = 0
+        self.device = 0
+        self._bias = None
+        self.training = False
+
+    # ---- construction ------------------------------------------------------------
+    def _create_from_f32(self, weight, bias, quantiser, threshold, device):
+        w = np.ascontiguousarray(weight, dtype=np.float32)
+        if w.ndim != 2:
+            # the reference asserts here (bit_linear.rs:50-54)
+            raise AssertionError(f"{self.NAME} weight must be 2D, got {list(w.shape)}")
+        m, k = w.shape
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32).reshape(m)
+        h = C.c_void_p()
+        _cabi.check(_cabi.lib().kb_linear_create_from_f32(
+            self.KIND, quantiser, w.ctypes.data, None if b is None else b.ctypes.data, m, k,
+            C.c_float(threshold), device, C.byref(h)))
+        self._adopt(h, m, k, b, device)
+
+    def _create_from_packed(self, packed, scales, bias, out_features, in_features, device):
+        p = np.ascontiguousarray(packed, dtype=np.uint8).ravel()
+        s = np.ascontiguousarray(scales, dtype=np.float32).ravel()
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32).reshape(out_features)
+        h = C.c_void_p()
+        _cabi.check(_cabi.lib().kb_linear_create_from_ref_packed(
+            self.KIND, p.ctypes.data, p.size, s.ctypes.data, s.size, None if b is None else b.ctypes.data,
+            out_features, in_features, device, C.byref(h)))
+        self._adopt(h, out_features, in_features, b, device)
+
+    def _adopt(self, h, m, k, bias, device):
+        self._h = h
+        self.out_features, self.in_features = int(m), int(k)
+        self._bias = bias
+        self.device = device
+
+    def close(self):
+        if self._h is not None:
+            _cabi.lib().kb_linear_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    # ---- accessors (bit_linear.rs:104-167) -----------------------------------------
+    def packed_weights(self) -> np.ndarray:
+        kp = (self.in_features + 4) // 5 if self.KIND == TERNARY else (self.in_features + 3) // 4
+        out = np.zeros(self.out_features * kp, np.uint8)
+        _cabi.check(_cabi.lib().kb_linear_packed_weights(self._h, out.ctypes.data, out.size))
+        return out
+
+    def scales(self) -> np.ndarray:
+        out = np.zeros(self.out_features, np.float32)
+        _cabi.check(_cabi.lib().kb_linear_scales(self._h, out.ctypes.data, out.size))
+        return out
+
+    def weight_memory_bytes(self) -> int:
+        wb = C.c_size_t()
+        _cabi.check(_cabi.lib().kb_linear_info(self._h, None, None, None, None, C.byref(wb)))
+        return int(wb.value)
+
+    def f32_weight_memory_bytes(self) -> int:
+        return self.out_features * self.in_features * 4
+
+    def compression_ratio(self) -> float:
+        return float(np.float32(self.f32_weight_memory_bytes()) / np.float32(self.weight_memory_bytes()))
+
+    def dequantize_weights(self) -> np.ndarray:
+        out = np.zeros((self.out_features, self.in_features), np.float32)
+        _cabi.check(_cabi.lib().kb_linear_dequantize_weights(self._h, out.ctypes.data, out.size))
+        return out
+
+    # ---- Module trait (module.rs:9-34) -----------------------------------------------
+    def forward(self, input, path: int = PATH_AUTO, return_acc: bool = False):
+        """y[..., out] = forward(x[..., in]).  Raises KoreError(ShapeMismatch) when the last
+        dimension is not in_features or the input is 0-dimensional (bit_linear.rs:179-184)."""
+        if _is_torch(input):
+            return self._forward_torch(input, path, return_acc)
+        x = np.ascontiguousarray(input, dtype=np.float32)
+        if x.ndim == 0:
+            raise KoreError(_cabi.ERR_SHAPE, f"shape mismatch: expected [{self.in_features}], got []")
+        in_dim = x.shape[-1]
+        lead = x.shape[:-1]
+        n = int(np.prod(lead)) if x.ndim > 1 else 1
+        y = np.zeros((n, self.out_features), np.float32)
+        if path == PATH_AUTO and not return_acc:
+            _cabi.check(_cabi.lib().kb_linear_forward_host(self._h, x.ctypes.data, n, in_dim, y.ctypes.data))
+            return y.reshape(*lead, self.out_features) if x.ndim > 1 else y.reshape(self.out_features)
+        import torch
+
+        xt = torch.from_numpy(x.reshape(n, in_dim)).to(f"cuda:{self.device}")
+        out = self._forward_torch(xt, path, return_acc)
+        if return_acc:
+            return out[0].cpu().numpy().reshape(*lead, -1), out[1].cpu().numpy().reshape(*lead, -1)
+        return out.cpu().numpy().reshape(*lead, self.out_features) if x.ndim > 1 else out.cpu().numpy().reshape(-1)
+
+    def _forward_torch(self, x, path, return_acc):
+        import torch
+
+        if not x.is_cuda or x.dtype != torch.float32:
+            raise KoreError(_cabi.ERR_DTYPE, f"expected a CUDA float32 tensor, got {x.dtype} on {x.device}")
+        if x.dim() == 0:
+            raise KoreError(_cabi.ERR_SHAPE, f"shape mismatch: expected [{self.in_features}], got []")
+        in_dim = x.shape[-1]
+        lead = tuple(x.shape[:-1])
+        n = int(np.prod(lead)) if x.dim() > 1 else 1
+        x2 = x.reshape(n, in_dim).contiguous()
+        y = torch.empty((n, self.out_features), dtype=torch.float32, device=x.device)
+        acc = torch.empty((n, self.out_features), dtype=torch.int32, device=x.device) if return_acc else None
+        _cabi.check(_cabi.lib().kb_linear_forward_ex(
+            self._h, x2.data_ptr(), n, in_dim, y.data_ptr(), 0, None if acc is None else acc.data_ptr(), path,
+            None, 0, _current_stream_ptr(x.device.index)))
+        y = y.reshape(*lead, self.out_features) if x.dim() > 1 else y.reshape(self.out_features)
+        return (y, acc) if return_acc else y
+
+    __call__ = forward
+
+    def parameters(self):
+        return [] if self._bias is None else [self._bias]
+
+    def named_parameters(self):
+        return [] if self._bias is None else [("bias", self._bias)]
+
+    def train(self, mode: bool = True):
+        self.training = mode
+
+    def is_training(self) -> bool:
+        return self.training
+
+    def state_dict(self):
+        sd = {"weight": self.dequantize_weights()}
+        if self._bias is not None:
+            sd["bias"] = self._bias.copy()
+        return sd
+
+
+def _xavier(rng, out_features, in_features):
+    # Linear::new draws from a Xavier-style uniform range (crates/kore-nn/src/linear.rs:16-22)
+    bound = float(np.sqrt(6.0 / (in_features + out_features)))
+    return rng.uniform(-bound, bound, size=(out_features, in_features)).astype(np.float32)
+
+
+class BitLinear(_QuantLinear):
+    """1.58-bit linear layer (ternary weights), mirror of kore_nn::BitLinear.
+
+    ``BitLinear(in_features, out_features, bias=False, threshold=0.3)`` follows the Python
+    constructor of the reference (random Xavier weights quantised at ``threshold``;
+    the reference's RNG is unseeded, here ``seed`` makes it reproducible).  Use
+    ``BitLinear.new(weight, bias, threshold)`` / ``from_packed`` for given weights.
+    """
+
+    KIND, NAME = TERNARY, "BitLinear"
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, threshold: float = 0.3,
+                 *, seed: int = 0, device: int = 0):
+        super().__init__()
+        self.threshold = float(threshold)
+        rng = np.random.default_rng(seed)
+        w = _xavier(rng, out_features, in_features)
+        b = np.zeros(out_features, np.float32) if bias else None
+        self._create_from_f32(w, b, _cabi.QUANT_REFERENCE, threshold, device)
+
+    @classmethod
+    def new(cls, weight, bias=None, threshold: float = 0.3, *, quantiser: str = "reference", device: int = 0):
+        """BitLinear::new (bit_linear.rs:48-77); quantiser="absmean" selects the per-tensor
+        absmean ternariser instead of the reference's per-row absmax + threshold."""
+        self = cls.__new__(cls)
+        _QuantLinear.__init__(self)
+        self.threshold = float(threshold)
+        q = _cabi.QUANT_ABSMEAN if quantiser == "absmean" else _cabi.QUANT_REFERENCE
+        self._create_from_f32(weight, bias, q, threshold, device)
+        return self
+
+    @classmethod
+    def from_packed(cls, packed_weights, scales, bias, in_features: int, out_features: int, *,
+                    threshold: float = 0.3, device: int = 0):
+        """Adopt BitLinear::packed_weights()/scales() (base-243 wire format) unchanged."""
+        self = cls.__new__(cls)
+        _QuantLinear.__init__(self)
+        self.threshold = float(threshold)
+        self._create_from_packed(packed_weights, scales, bias, out_features, in_features, device)
+        return self
+
+    @classmethod
+    def random(cls, in_features: int, out_features: int, bias: bool, *, seed: int = 0, device: int = 0):
+        """BitLinear::random (bit_linear.rs:87-102): uniform(-1,1) weights, threshold 0.3."""
+        rng = np.random.default_rng(seed)
+        w = rng.uniform(-1.0, 1.0, size=(out_features, in_features)).astype(np.float32)
+        return cls.new(w, np.zeros(out_features, np.float32) if bias else None, 0.3, device=device)
+
+    def __repr__(self):  # Display impl, bit_linear.rs:276-288
+        return (f"BitLinear(in={self.in_features}, out={self.out_features}, threshold={self.threshold:g}, "
+                f"compression={self.compression_ratio():.1f}x, mem={self.weight_memory_bytes() / 1024.0:.1f}KB)")
+
+
+class QuatLinear(_QuantLinear):
+    """2-bit linear layer (weights in {-3,-1,+1,+3} x per-row scale), mirror of kore_nn::QuatLinear."""
+
+    KIND, NAME = QUATERNARY, "QuatLinear"
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, *, seed: int = 0, device: int = 0):
+        super().__init__()
+        rng = np.random.default_rng(seed)
+        w = _xavier(rng, out_features, in_features)
+        b = np.zeros(out_features, np.float32) if bias else None
+        self._create_from_f32(w, b, _cabi.QUANT_REFERENCE, 0.0, device)
+
+    @classmethod
+    def new(cls, weight, bias=None, *, device: int = 0):
+        """QuatLinear::new (quat_linear.rs:46-73)."""
+        self = cls.__new__(cls)
+        _QuantLinear.__init__(self)
+        self._create_from_f32(weight, bias, _cabi.QUANT_REFERENCE, 0.0, device)
+        return self
+
+    @classmethod
+    def from_packed(cls, packed_weights, scales, bias, in_features: int, out_features: int, *, device: int = 0):
+        self = cls.__new__(cls)
+        _QuantLinear.__init__(self)
+        self._create_from_packed(packed_weights, scales, bias, out_features, in_features, device)
+        return self
+
+    @classmethod
+    def random(cls, in_features: int, out_features: int, bias: bool, *, seed: int = 0, device: int = 0):
+        """QuatLinear::random (quat_linear.rs:81-96): uniform(-3,3) weights."""
+        rng = np.random.default_rng(seed)
+        w = rng.uniform(-3.0, 3.0, size=(out_features, in_features)).astype(np.float32)
+        return cls.new(w, np.zeros(out_features, np.float32) if bias else None, device=device)
+
+    def __repr__(self):  # Display impl, quat_linear.rs:227-238
+        return (f"QuatLinear(in={self.in_features}, out={self.out_features}, "
+                f"bias={'true' if self._bias is not None else 'false'}, compression={self.compression_ratio():.1f}x)")
