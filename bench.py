@@ -1,0 +1,406 @@
+#!/usr/bin/env python
+"""Benchmark of the BitLinear / QuatLinear forward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline workload (N = 1): the batch-1 decode GEMV of BASELINE.json configs[1] —
+ternary 4096x4096 weights (absmean-ternarised N(0, 0.02^2), seed 2001), one f32
+activation row N(0,1) (seed 2002), per-token int8 absmax fused into the kernel.
+A "step" is one pass over a pool of POOL distinct copies of that layer (each copy has
+its own allocation, POOL * 4 MiB > the 126 MB L2, so every weight byte comes from HBM),
+replayed as one CUDA graph.  value = algorithmic bytes of the step / device time.
+
+With N > 1 every rank owns a 4096-row shard of a K=4096 x M=4096*N projection (weak
+scaling: per-GPU work is the N = 1 workload), computes its slice and the slices are
+exchanged so that every rank holds the full y[1, 4096*N].
+
+All inputs are synthetic (no dataset or checkpoint exists for this path).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M_DEC, K_DEC = 4096, 4096
+POOL = 160  # 160 x 4 MiB = 640 MiB of packed weights, five times the L2
+METRIC, UNIT = "bitlinear_gemv_hbm_gbs", "GB/s"
+
+
+def gemv_bytes(m, k, n):
+    """Algorithmic bytes of one decode GEMV launch: packed 2-bit weights + scales
+    + f32 activations in + f32 outputs out."""
+    return m * k // 4 + 4 * m + 4 * k * n + 4 * m * n
+
+
+def gaussian(seed, shape, sigma):
+    return (np.random.default_rng(seed).standard_normal(shape) * sigma).astype(np.float32)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_reference_arm(budget_s: float = 12.0):
+    """Times the CPU restatement of what the reference runs today for the headline
+    workload: BitLinear::new(W, threshold 0.3) then forward(x[1,4096]) — per-call row
+    decode, both transposes, rows in parallel over all host cores (rayon rule)."""
+    from oracle import kbref
+
+    threads = kbref.max_threads()
+    w = gaussian(2001, (M_DEC, K_DEC), 0.02)
+    x = gaussian(2002, (1, K_DEC), 1.0)
+    packed, scales = kbref.pack_weights_ternary(w, M_DEC, K_DEC, 0.3)
+    kbref.linear_forward(kbref.TERNARY, packed, scales, None, M_DEC, K_DEC, x, threads=threads)  # warm-up
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while time.perf_counter() < t_end and len(times) < 2000:
+        t0 = time.perf_counter()
+        kbref.linear_forward(kbref.TERNARY, packed, scales, None, M_DEC, K_DEC, x, threads=threads)
+        times.append(time.perf_counter() - t0)
+    best = float(np.median(times))
+    return {"value": gemv_bytes(M_DEC, K_DEC, 1) / best / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{len(times)} forwards of the 4096x4096 batch-1 layer (median {best * 1e3:.3f} ms each), "
+                      "reference quantiser (per-row absmax, threshold 0.3), f32 activations",
+            "ms_per_forward": best * 1e3}
+
+
+def run_reference_impl(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base = cpu_reference_arm(budget_s=max(5.0, min(60.0, 4.0 * (args.steps + args.warmup))))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_forward"] * POOL,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "decode_gemv_ternary_4096x4096_batch1", "pool": POOL, "l2": "inputs larger than L2 on the GPU arm; CPU arm re-uses one layer"},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+def time_graph(torch, fn, steps, warmup, stream):
+    """Capture fn() (one step) into a CUDA graph, replay warmup + steps, return seconds per step."""
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        fn()  # eager warm-up (also sets function attributes outside capture)
+        stream.synchronize()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+        for _ in range(warmup):
+            g.replay()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            g.replay()
+        e1.record(stream)
+        stream.synchronize()
+    return e0.elapsed_time(e1) / 1e3 / steps, g
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="kore_b200")
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill / quaternary / batch side measurements")
+    ap.add_argument("--pool", type=int, default=POOL)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference_impl(args)
+
+    import torch
+
+    from kore_b200 import _cabi, kernels, nn
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_
+
+        dist = dist_
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _cabi.lib()
+    pool_n = args.pool
+    peaks = measured_peaks()
+
+    # ---- weights: one seeded layer, POOL separately allocated copies of its shard
+    w = gaussian(2001 + rank, (M_DEC, K_DEC), 0.02)
+    proto = nn.BitLinear.new(w, None, 0.3, quantiser="absmean", device=local_rank)
+    packed, scales = proto.packed_weights(), proto.scales()
+    pool = [proto] + [nn.BitLinear.from_packed(packed, scales, None, K_DEC, M_DEC, device=local_rank) for _ in range(pool_n - 1)]
+    x_host = gaussian(2002, (1, K_DEC), 1.0)
+    x_pin = torch.from_numpy(x_host).pin_memory()
+    x_dev = x_pin.to(dev)
+    m_total = M_DEC * world
+    y_full = torch.zeros((1, m_total), dtype=torch.float32, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    sptr = stream.cuda_stream
+
+    gather = None
+    if world > 1:
+        from kore_b200 import sharded
+
+        gather = sharded.SliceExchange(y_full, rank, world, M_DEC, dist)
+
+    def step():
+        for lay in pool:
+            _cabi.check(lib.kb_linear_forward_ex(lay.handle, x_dev.data_ptr(), 1, K_DEC,
+                                                 y_full.data_ptr() + 4 * rank * M_DEC, m_total, None, _cabi.PATH_GEMV,
+                                                 None, 0, sptr))
+            if gather is not None:
+                gather.exchange(stream)
+
+    launches_per_step = pool_n * (1 if gather is None else 1 + gather.launches_per_exchange)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(local_rank) as clocks:
+        sec_per_step, graph = time_graph(torch, step, args.steps, args.warmup, stream)
+    torch.cuda.synchronize()
+    if dist is not None:
+        t = torch.tensor([sec_per_step], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec_per_step = float(t.item())
+    step_bytes = pool_n * gemv_bytes(M_DEC, K_DEC, 1) * world
+    value = step_bytes / sec_per_step / 1e9
+
+    # correctness spot check of what was just timed (cheap, outside the timed region)
+    y_chk = y_full[0, rank * M_DEC:(rank + 1) * M_DEC].cpu().numpy()
+
+    # ---- end to end: host buffers through the C ABI, copies inside the timed region
+    y_host = np.zeros((1, M_DEC), np.float32)
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        for lay in pool:
+            _cabi.check(lib.kb_linear_forward_host(lay.handle, x_pin.data_ptr(), 1, K_DEC, y_host.ctypes.data))
+
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_sec = (time.perf_counter() - t0) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_sec], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_sec = float(t.item())
+    e2e = {"value": step_bytes / e2e_sec / 1e9, "unit": UNIT, "h2d_bytes_per_step": pool_n * 4 * K_DEC,
+           "d2h_bytes_per_step": pool_n * 4 * M_DEC, "ms_per_step": e2e_sec * 1e3,
+           "note": "kb_linear_forward_host per layer: pinned x -> device, fused quantiser+GEMV, y -> host, synchronise"}
+    assert (y_host[0] == y_chk).all(), "host entry point and graph replay disagree"
+
+    if rank != 0:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    per_launch_s = sec_per_step / pool_n
+    achieved = gemv_bytes(M_DEC, K_DEC, 1) / per_launch_s / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["src"],
+                "kernel": "gemv_kernel<1,4,fused>", "us_per_launch": per_launch_s * 1e6,
+                "frac_of_nominal_8000": achieved / 8000.0}
+    tpath = os.path.join(ROOT, "profiles", "gemv_traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            roofline["traffic"] = json.load(f).get("dram_bytes_per_launch_4096x4096_b1")
+
+    cpu = cpu_reference_arm(budget_s=12.0) if world == 1 else None
+
+    extras = {}
+    if not args.no_extras and world == 1:
+        try:
+            extras = side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args)
+        except Exception as exc:  # side numbers must never cost the headline line
+            extras = {"error": repr(exc)}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "decode_gemv_ternary_4096x4096_batch1" if world == 1 else
+                   f"decode_gemv_ternary_K4096_M{m_total}_batch1_column_sharded_{world}x4096",
+                   "pool": pool_n, "pool_bytes": pool_n * M_DEC * K_DEC // 4,
+                   "l2": "inputs larger than L2 (pool of separately allocated weight copies)",
+                   "quantiser": "absmean per-tensor", "timing": "CUDA events around CUDA-graph replays of the step"},
+        "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks.summary(),
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if extras:
+        line["extra"] = extras
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args):
+    """Other configurations of BASELINE.json, measured briefly: quaternary GEMV, batch-8 GEMV,
+    prefill GEMM (2048 tokens, 4096 -> 11008 and 11008 -> 4096) with a library int8 GEMM
+    timed beside it as a local ceiling."""
+    out = {}
+    sptr = stream.cuda_stream
+    steps, warm = 10, 3
+
+    # quaternary twin of the headline layer, same pool scheme
+    w = gaussian(2001, (M_DEC, K_DEC), 0.02)
+    qproto = nn.QuatLinear.new(w, device=dev.index)
+    qp, qs = qproto.packed_weights(), qproto.scales()
+    qpool = [qproto] + [nn.QuatLinear.from_packed(qp, qs, None, K_DEC, M_DEC, device=dev.index) for _ in range(63)]
+    for nb in (1, 8):
+        x = torch.from_numpy(gaussian(2002, (nb, K_DEC), 1.0)).to(dev)
+        y = torch.empty((nb, M_DEC), dtype=torch.float32, device=dev)
+
+        def qstep():
+            for lay in qpool:
+                _cabi.check(lib.kb_linear_forward_ex(lay.handle, x.data_ptr(), nb, K_DEC, y.data_ptr(), 0, None,
+                                                     _cabi.PATH_GEMV, None, 0, sptr))
+
+        sec, _ = time_graph(torch, qstep, steps, warm, stream)
+        gbs = len(qpool) * gemv_bytes(M_DEC, K_DEC, nb) / sec / 1e9
+        out[f"quat_gemv_4096x4096_batch{nb}"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                                                  "us_per_launch": sec / len(qpool) * 1e6}
+    del qpool
+
+    # prefill GEMM
+    for name, m, k, seed in (("up_4096_to_11008", 11008, 4096, 3001), ("down_11008_to_4096", 4096, 11008, 3003)):
+        n = 2048
+        wg = torch.Generator(device="cpu").manual_seed(seed)
+        w = (torch.randn((m, k), generator=wg) * 0.02).numpy()
+        lay = nn.BitLinear.new(w, None, 0.3, quantiser="absmean", device=dev.index)
+        x = torch.from_numpy(gaussian(3002, (n, k), 1.0)).to(dev)
+        y = torch.empty((n, m), dtype=torch.float32, device=dev)
+        xq, sx, sumq = kernels.quantize_act_i8(x)
+
+        def gemm_only():
+            _cabi.check(lib.kb_linear_forward_q8(lay.handle, xq.data_ptr(), xq.stride(0), sx.data_ptr(), sumq.data_ptr(),
+                                                 n, y.data_ptr(), 0, None, _cabi.PATH_GEMM_TC, sptr))
+
+        def full():
+            _cabi.check(lib.kb_linear_forward_ex(lay.handle, x.data_ptr(), n, k, y.data_ptr(), 0, None,
+                                                 _cabi.PATH_GEMM_TC, None, 0, sptr))
+
+        sec_g, _ = time_graph(torch, gemm_only, 20, 5, stream)
+        sec_f, _ = time_graph(torch, full, 20, 5, stream)
+        st = C.c_int(0)
+        rc = lib.kb_linear_last_device_status(lay.handle, None, C.byref(st))
+        ops = 2.0 * n * m * k
+        entry = {"gemm_TOPS": ops / sec_g / 1e12, "gemm_ms": sec_g * 1e3, "with_act_quant_TOPS": ops / sec_f / 1e12,
+                 "with_act_quant_ms": sec_f * 1e3, "device_status": int(st.value), "status_rc": int(rc),
+                 "frac_of_nominal_int8_4500": ops / sec_g / 1e12 / 4500.0,
+                 "frac_of_2x_measured_bf16": ops / sec_g / 1e12 / (2 * peaks["bf16_tflops"])}
+        try:  # library int8 GEMM on the same shape as a local ceiling
+            a8 = torch.randint(-127, 127, (n, k), dtype=torch.int8, device=dev)
+            b8 = torch.randint(-1, 2, (k, m), dtype=torch.int8, device=dev)
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    torch._int_mm(a8, b8)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(20):
+                    torch._int_mm(a8, b8)
+                e1.record(stream)
+                stream.synchronize()
+            lib_s = e0.elapsed_time(e1) / 1e3 / 20
+            entry["library_int8_gemm_TOPS"] = ops / lib_s / 1e12
+            entry["frac_of_library_int8"] = sec_g and (lib_s / sec_g)
+        except Exception as exc:
+            entry["library_int8_gemm_TOPS"] = None
+            entry["library_error"] = repr(exc)[:200]
+        out[f"prefill_gemm_2048tok_{name}"] = entry
+        del lay
+    return out
+
+
+if __name__ == "__main__":
+    main()
