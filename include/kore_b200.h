@@ -140,6 +140,29 @@ int kb_linear_forward_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const
  * Replaces the H2D/launch/D2H sequence of quat_linear.rs:183-212. */
 int kb_linear_forward_host(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *y);
 
+/* ---- forward without any allocation (device pointers) ----
+ * No counterpart in the reference (its CUDA path allocates a fresh output and three
+ * upload buffers on every call, quat_linear.rs:183-199, cuda/ops.rs:778-780).
+ *
+ * For callers that may not allocate device memory while they run — a latency-critical
+ * loop with a fixed memory budget, a plugin inside a process whose own allocator has
+ * claimed the GPU, an engine whose pools are frozen after start-up.  Same result as
+ * kb_linear_forward, but the quantised activations live in a fixed array inside the
+ * library (kb_static_scratch_bytes() = 1 MiB, resident on every GPU that loads the
+ * library until the process exits) instead of stream-ordered scratch, and the call
+ * performs no cudaMalloc/cudaFree of any kind; x and y stay caller-owned.
+ *   - needs round_up(N*Kp,256) + 2*round_up(4*N,256) <= kb_static_scratch_bytes(),
+ *     Kp = kb_act_ld(K); larger requests fail with KB_ERR_UNSUPPORTED and a message
+ *     stating both sizes;
+ *   - the first call on each device resolves the array's device address
+ *     (cudaGetSymbolAddress); make that call during set-up, before any stream capture;
+ *   - all calls on a device share the array and it keeps the previous call's bytes.
+ *     Each call overwrites everything it reads, so nothing has to be cleared, but calls
+ *     that overlap on the GPU (two streams, two threads) race: serialise them. */
+int kb_linear_forward_static(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *y,
+                             kb_stream stream);
+size_t kb_static_scratch_bytes(void);
+
 /* ---- kernel-shaped one-shots (host pointers), signatures of
  * ternary_matmul (crates/kore-kernels/src/cpu_ternary_matmul.rs:29-36) and
  * quat_matmul (crates/kore-kernels/src/cpu_quat_matmul.rs:22-29):

@@ -39,6 +39,8 @@ SIGNATURES = {
     "kb_linear_workspace_bytes": (_sz, [_vp, _sz]),
     "kb_linear_forward_q8": (C.c_int, [_vp, _vp, _sz, _vp, _vp, _sz, _vp, _sz, _vp, C.c_int, _vp]),
     "kb_linear_forward_host": (C.c_int, [_vp, _vp, _sz, _sz, _vp]),
+    "kb_linear_forward_static": (C.c_int, [_vp, _vp, _sz, _sz, _vp, _vp]),
+    "kb_static_scratch_bytes": (_sz, []),
     "kb_ternary_matmul": (C.c_int, [_vp, _sz, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
     "kb_quat_matmul": (C.c_int, [_vp, _sz, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
     "kb_pack_weights_ternary": (C.c_int, [_vp, _sz, _sz, C.c_float, _vp, _sz, _vp, _sz, C.c_int]),
