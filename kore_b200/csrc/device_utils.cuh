@@ -43,6 +43,18 @@ __device__ __forceinline__ int quantise_one(float x, float s) {
     return max(-127, min(127, q));
 }
 
+// Same result as quantise_one without a division per element.  r = 1/s (correctly
+// rounded).  t = x*r is within ~1.5e-5 of the true quotient for |x/s| <= 127, so
+// rint(t) equals rint(fl(x/s)) unless t sits within 1e-3 of a rounding tie; only then
+// is the exact IEEE division evaluated.
+__device__ __forceinline__ int quantise_one_fast(float x, float s, float r) {
+    const float t = x * r;
+    const float frac = fabsf(t - rintf(t));
+    int q = __float2int_rn(t);
+    if (frac > 0.499f) q = __float2int_rn(__fdiv_rn(x, s));
+    return max(-127, min(127, q));
+}
+
 // sum over four (unsigned byte of a) * (signed byte of b) + c
 __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
     int d;

@@ -13,11 +13,19 @@
 // Codes are unsigned (0..3); the signed value is recovered in the epilogue as
 // mul * S - off * sum(xq).
 //
+// Latency structure (what matters for a 4 MiB layer that streams in under a
+// microsecond): each warp keeps PF weight chunks x R rows in flight in registers and
+// issues the first PF of them before anything else — before the activation prologue
+// and before griddepcontrol.wait — so with programmatic dependent launch a layer's
+// weights arrive while the previous kernel of the stream is still finishing.
+//
 // Activations sit in shared memory, permuted so that for a fixed 16-byte sub-chunk
-// the 32 lanes of a warp read 32 consecutive 16-byte slots (conflict-free).  When
-// the caller passes f32 activations the per-token absmax quantiser runs in the
-// prologue of every CTA (the row is a few KB and L2-resident), which removes one
-// launch and one global round trip per linear layer in decode.
+// the 32 lanes of a warp read 32 consecutive 16-byte slots (conflict-free).  When the
+// caller passes f32 activations the per-token absmax quantiser runs in the prologue of
+// every CTA from registers (one global read of the row, L2-resident), which removes a
+// launch and a global round trip per linear layer in decode.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "device_utils.cuh"
 
@@ -42,21 +50,35 @@ struct GemvParams {
     int x_vec4;
 };
 
-// shared-memory slot of the 16-element group g (k = 16*g .. 16*g+15) of one token row:
-// inside each 2048-element block, lane l = (g%128)/4 and sub-chunk i = g%4 land at i*32 + l
-__device__ __forceinline__ int xs_slot(int g) {
-    const int blk = g >> 7, within = g & 127;
-    return (blk << 7) + ((within & 3) << 5) + (within >> 2);
-}
+// 16-element group g (k = 16*g .. 16*g+15) <-> shared-memory slot: inside each
+// 2048-element block, lane l = (g%128)/4 and sub-chunk i = g%4 live at slot i*32 + l
 __device__ __forceinline__ int xs_group_of_slot(int d) {
     const int blk = d >> 7, within = d & 127;
     return (blk << 7) + ((within & 31) << 2) + (within >> 5);
 }
 
-template <int NT, int R, bool FUSED>
+#ifdef KB_TIMELINE
+// Developer build only: CTA 0..2047 of the most recent launch record %globaltimer at five
+// points (entry, weights issued, dependency wait over, prologue done, rows done).
+__device__ unsigned long long g_timeline[5][2048];
+__device__ __forceinline__ void tl_mark(int i) {
+    if (threadIdx.x == 0 && blockIdx.x < 2048 && blockIdx.y == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_timeline[i][blockIdx.x] = t;
+    }
+}
+#define TL_MARK(i) tl_mark(i)
+#else
+#define TL_MARK(i)
+#endif
+
+constexpr int XR = 8;  // float4 registers per thread for the single-pass fused quantiser
+
+template <int NT, int R, int PF, bool FUSED>
 __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    uint4 *xs = reinterpret_cast<uint4 *>(smem_raw);  // [NT][kp/16] permuted slots
+    uint4 *xs = reinterpret_cast<uint4 *>(smem_raw);  // [NT][slots] permuted 16-byte slots
     __shared__ float s_sx[NT];
     __shared__ int s_sum[NT];
     __shared__ float red_f[32];
@@ -65,26 +87,48 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int tok0 = blockIdx.y * NT;
     const int groups16 = p.kp >> 4;
-    const int slots = (groups16 + 127) & ~127;  // row stride in 16-byte slots (whole 2048-element blocks)
+    const int slots = (groups16 + 127) & ~127;  // row stride in slots (whole 2048-element blocks)
+    const int nch = (p.kp + 2047) >> 11;        // 2048-element chunks per row (uniform over lanes)
     const int row_groups = (p.m + R - 1) / R;
     const int first_group = blockIdx.x * nwarps + warp;
+    const int stride_groups = gridDim.x * nwarps;
+    const int kc0 = lane * 64;
 
-    // Weight loads do not depend on the activations: issue the first chunk before the
-    // prologue (and before waiting on the previous kernel of the stream).
-    uint4 wpre[R];
-    {
-        const int g0 = first_group < row_groups ? first_group : 0;
-        const int kc = lane * 64;
+    TL_MARK(0);
+    // ---- weight pipeline: PF chunks x R rows in registers ----
+    uint4 buf[PF][R];
+    int lg = first_group, lci = 0;  // load cursor (row group, chunk)
+    auto issue = [&](uint4(&dst)[R]) {
+        const int kc = kc0 + (lci << 11);
+        const bool ok = lg < row_groups && kc < p.kp;
+        const uint8_t *src = p.w2 + (size_t)(lg * R) * p.row_bytes + (kc >> 2);
 #pragma unroll
         for (int r = 0; r < R; ++r)
-            wpre[r] = kc < p.kp ? ld_stream_v4(p.w2 + (size_t)(g0 * R + r) * p.row_bytes + (kc >> 2))
-                                : make_uint4(0, 0, 0, 0);
-    }
+            dst[r] = ok ? ld_stream_v4(src + (size_t)r * p.row_bytes) : make_uint4(0, 0, 0, 0);
+        if (++lci == nch) { lci = 0; lg += stride_groups; }
+    };
+#pragma unroll
+    for (int s = 0; s < PF; ++s) issue(buf[s]);
+    // per-row constants of the group a lane will finish (lane r*NT+t <-> row r): loaded at the
+    // start of a group so their latency is hidden behind the group's weight stream
+    float my_sw = 0.0f, my_bias = 0.0f;
+    auto load_row_consts = [&](int g) {
+        if (lane < R * NT && g < row_groups) {
+            const int row = g * R + lane / NT;  // rows up to m_alloc-1 are allocated
+            my_sw = p.sw[row];
+            my_bias = p.bias ? p.bias[row] : 0.0f;
+        }
+    };
+    load_row_consts(first_group);
+
+    TL_MARK(1);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    TL_MARK(2);
 
     // ---- prologue: activations -> shared memory (int8, permuted) ----
     if (FUSED) {
+        const bool single_pass = p.x_vec4 && slots * 4 <= XR * (int)blockDim.x;
 #pragma unroll 1
         for (int t = 0; t < NT; ++t) {
             const int tok = tok0 + t;
@@ -95,44 +139,77 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
                 continue;
             }
             const float *row = p.x + (size_t)tok * p.k;
-            float amax = 0.0f;
-            if (p.x_vec4) {
-                const float4 *row4 = reinterpret_cast<const float4 *>(row);
-                for (int i = threadIdx.x; i < (p.k >> 2); i += blockDim.x) {
-                    float4 v = row4[i];
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            int local_sum = 0;
+            float s, rs;
+            if (single_pass) {
+                // thread owns destination words widx = tid + i*blockDim (conflict-free stores);
+                // word w of slot d holds elements 16*g + 4*w .. +3 of group g = group_of_slot(d)
+                float4 v[XR];
+                float amax = 0.0f;
+                const int nv4 = p.k >> 2;
+#pragma unroll
+                for (int i = 0; i < XR; ++i) {
+                    const int widx = threadIdx.x + i * blockDim.x;
+                    const int src = xs_group_of_slot(widx >> 2) * 4 + (widx & 3);
+                    v[i] = (widx < slots * 4 && src < nv4) ? reinterpret_cast<const float4 *>(row)[src]
+                                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+                }
+                amax = block_reduce_max(amax, red_f);
+                s = amax < 1e-8f ? 1.0f : __fdiv_rn(amax, 127.0f);
+                rs = __frcp_rn(s);
+                uint32_t *dstw = reinterpret_cast<uint32_t *>(dst);
+#pragma unroll
+                for (int i = 0; i < XR; ++i) {
+                    const int widx = threadIdx.x + i * blockDim.x;
+                    if (widx < slots * 4) {
+                        const int q0 = quantise_one_fast(v[i].x, s, rs), q1 = quantise_one_fast(v[i].y, s, rs);
+                        const int q2 = quantise_one_fast(v[i].z, s, rs), q3 = quantise_one_fast(v[i].w, s, rs);
+                        local_sum += q0 + q1 + q2 + q3;
+                        dstw[widx] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) |
+                                     ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+                    }
                 }
             } else {
-                for (int i = threadIdx.x; i < p.k; i += blockDim.x) amax = fmaxf(amax, fabsf(row[i]));
-            }
-            amax = block_reduce_max(amax, red_f);
-            const float s = amax < 1e-8f ? 1.0f : __fdiv_rn(amax, 127.0f);
-            int local_sum = 0;
-            for (int d = threadIdx.x; d < slots; d += blockDim.x) {
-                const int g = xs_group_of_slot(d);
-                if (g >= groups16) continue;  // slot of a lane that lies beyond Kp in the last block
-                uint32_t out[4];
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const int base = g * 16 + w * 4;
-                    float v[4];
-                    if (p.x_vec4 && base + 3 < p.k) {
-                        float4 f = *reinterpret_cast<const float4 *>(row + base);
-                        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) v[e] = (base + e < p.k) ? row[base + e] : 0.0f;
+                float amax = 0.0f;
+                if (p.x_vec4) {
+                    const float4 *row4 = reinterpret_cast<const float4 *>(row);
+                    for (int i = threadIdx.x; i < (p.k >> 2); i += blockDim.x) {
+                        float4 v = row4[i];
+                        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
                     }
-                    uint32_t word = 0;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        int q = quantise_one(v[e], s);
-                        local_sum += q;
-                        word |= (uint32_t)(q & 0xff) << (8 * e);
-                    }
-                    out[w] = word;
+                } else {
+                    for (int i = threadIdx.x; i < p.k; i += blockDim.x) amax = fmaxf(amax, fabsf(row[i]));
                 }
-                dst[d] = make_uint4(out[0], out[1], out[2], out[3]);
+                amax = block_reduce_max(amax, red_f);
+                s = amax < 1e-8f ? 1.0f : __fdiv_rn(amax, 127.0f);
+                rs = __frcp_rn(s);
+                for (int d = threadIdx.x; d < slots; d += blockDim.x) {
+                    const int g = xs_group_of_slot(d);
+                    if (g >= groups16) continue;  // slot of a lane that lies beyond Kp in the last block
+                    uint32_t out[4];
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        const int base = g * 16 + w * 4;
+                        float v[4];
+                        if (p.x_vec4 && base + 3 < p.k) {
+                            float4 f = *reinterpret_cast<const float4 *>(row + base);
+                            v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) v[e] = (base + e < p.k) ? row[base + e] : 0.0f;
+                        }
+                        uint32_t word = 0;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            int q = quantise_one_fast(v[e], s, rs);
+                            local_sum += q;
+                            word |= (uint32_t)(q & 0xff) << (8 * e);
+                        }
+                        out[w] = word;
+                    }
+                    dst[d] = make_uint4(out[0], out[1], out[2], out[3]);
+                }
             }
             local_sum = block_reduce_sum(local_sum, red_i);
             if (threadIdx.x == 0) { s_sx[t] = s; s_sum[t] = local_sum; }
@@ -154,96 +231,120 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
         }
     }
     __syncthreads();
+    TL_MARK(3);
 
-    // ---- main loop: one warp owns R weight rows at a time ----
-    const int stride_groups = gridDim.x * nwarps;
-    for (int g = first_group; g < row_groups; g += stride_groups) {
-        int acc[R][NT][4];
+    // ---- main loop: consume chunk, refill its registers, finish a row group when its
+    //      last chunk has been consumed (control flow is uniform across the warp) ----
+    int acc[R][NT][4];
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+    for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int t = 0; t < NT; ++t)
+        for (int t = 0; t < NT; ++t)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[r][t][j] = 0;
+            for (int j = 0; j < 4; ++j) acc[r][t][j] = 0;
 
-        const uint8_t *wbase = p.w2 + (size_t)(g * R) * p.row_bytes;
-        const bool first = (g == first_group);
-        for (int kc = lane * 64; kc < p.kp; kc += 2048) {
-            uint4 wv[R];
-            if (first && kc == lane * 64) {
+    int cg = first_group, cci = 0;  // consume cursor
+    while (cg < row_groups) {
 #pragma unroll
-                for (int r = 0; r < R; ++r) wv[r] = wpre[r];
-            } else {
+        for (int s = 0; s < PF; ++s) {
+            if (cg < row_groups) {
+                // lanes beyond Kp hold zero weights, so their (unwritten) activation slots contribute 0
+                const int slot0 = (cci << 7) + lane;
 #pragma unroll
-                for (int r = 0; r < R; ++r) wv[r] = ld_stream_v4(wbase + (size_t)r * p.row_bytes + (kc >> 2));
-            }
-            const int slot0 = ((kc >> 11) << 7) + lane;  // block*128 + lane, sub-chunk i adds 32*i
+                for (int i = 0; i < 4; ++i) {
+                    uint4 xv[NT];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint4 xv[NT];
+                    for (int t = 0; t < NT; ++t) xv[t] = xs[(size_t)t * slots + slot0 + 32 * i];
 #pragma unroll
-                for (int t = 0; t < NT; ++t) xv[t] = xs[(size_t)t * slots + slot0 + 32 * i];
+                    for (int r = 0; r < R; ++r) {
+                        const uint32_t w = i == 0 ? buf[s][r].x : (i == 1 ? buf[s][r].y : (i == 2 ? buf[s][r].z : buf[s][r].w));
+                        const uint32_t w0 = w & 0x03030303u, w1 = w & 0x0c0c0c0cu;
+                        const uint32_t w2_ = w & 0x30303030u, w3 = w & 0xc0c0c0c0u;
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const uint32_t w = i == 0 ? wv[r].x : (i == 1 ? wv[r].y : (i == 2 ? wv[r].z : wv[r].w));
-                    const uint32_t w0 = w & 0x03030303u, w1 = w & 0x0c0c0c0cu;
-                    const uint32_t w2_ = w & 0x30303030u, w3 = w & 0xc0c0c0c0u;
-#pragma unroll
-                    for (int t = 0; t < NT; ++t) {
-                        acc[r][t][0] = dp4a_u8s8(w0, xv[t].x, acc[r][t][0]);
-                        acc[r][t][1] = dp4a_u8s8(w1, xv[t].y, acc[r][t][1]);
-                        acc[r][t][2] = dp4a_u8s8(w2_, xv[t].z, acc[r][t][2]);
-                        acc[r][t][3] = dp4a_u8s8(w3, xv[t].w, acc[r][t][3]);
+                        for (int t = 0; t < NT; ++t) {
+                            acc[r][t][0] = dp4a_u8s8(w0, xv[t].x, acc[r][t][0]);
+                            acc[r][t][1] = dp4a_u8s8(w1, xv[t].y, acc[r][t][1]);
+                            acc[r][t][2] = dp4a_u8s8(w2_, xv[t].z, acc[r][t][2]);
+                            acc[r][t][3] = dp4a_u8s8(w3, xv[t].w, acc[r][t][3]);
+                        }
                     }
+                }
+                issue(buf[s]);
+                if (++cci == nch) {
+                    // combine the four scaled partials (exact), reduce over lanes, and let lane
+                    // r*NT+t finish output (row cg*R+r, token tok0+t)
+                    int mine = 0;
+#pragma unroll
+                    for (int r = 0; r < R; ++r)
+#pragma unroll
+                        for (int t = 0; t < NT; ++t) {
+                            int v = acc[r][t][0] + (acc[r][t][1] >> 2) + (acc[r][t][2] >> 4) + (acc[r][t][3] >> 6);
+                            v = warp_reduce_sum(v);
+                            if (lane == r * NT + t) mine = v;
+                            acc[r][t][0] = acc[r][t][1] = acc[r][t][2] = acc[r][t][3] = 0;
+                        }
+                    if (lane < R * NT) {
+                        const int r = lane / NT, t = lane - r * NT;
+                        const int row = cg * R + r, tok = tok0 + t;
+                        if (row < p.m && tok < p.n) {
+                            const int a = p.mul * mine - p.off * s_sum[t];
+                            const size_t o = (size_t)tok * p.ldy + row;
+                            if (p.acc) p.acc[o] = a;
+                            if (p.y) p.y[o] = dequant_out(a, my_sw, s_sx[t], my_bias, p.bias != nullptr);
+                        }
+                    }
+                    cci = 0;
+                    cg += stride_groups;
+                    load_row_consts(cg);
                 }
             }
         }
-
-        // combine the four scaled partials (exact), reduce over lanes, and let lane
-        // r*NT+t finish output (row g*R+r, token tok0+t)
-        int mine = 0;
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-#pragma unroll
-            for (int t = 0; t < NT; ++t) {
-                int s = acc[r][t][0] + (acc[r][t][1] >> 2) + (acc[r][t][2] >> 4) + (acc[r][t][3] >> 6);
-                s = warp_reduce_sum(s);
-                if (lane == r * NT + t) mine = s;
-            }
-        if (lane < R * NT) {
-            const int r = lane / NT, t = lane - r * NT;
-            const int row = g * R + r, tok = tok0 + t;
-            if (row < p.m && tok < p.n) {
-                const int a = p.mul * mine - p.off * s_sum[t];
-                const size_t o = (size_t)tok * p.ldy + row;
-                if (p.acc) p.acc[o] = a;
-                if (p.y) p.y[o] = dequant_out(a, p.sw[row], s_sx[t], p.bias ? p.bias[row] : 0.0f, p.bias != nullptr);
-            }
-        }
     }
+    TL_MARK(4);
 }
+
+#ifdef KB_TIMELINE
+extern "C" int kb_debug_timeline(unsigned long long *host) {
+    return (int)cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline));
+}
+#endif
+
+static size_t gemv_smem_bytes(size_t kp, size_t nt) { return nt * ((kp + 2047) / 2048 * 2048); }
 
 bool gemv_supports(const Linear *lin, size_t n) {
     // the activations of up to 8 tokens must fit in shared memory
     const size_t nt = n >= 8 ? 8 : (n > 2 ? (n > 4 ? 8 : 4) : n);
-    return nt * ((lin->kp + 2047) / 2048 * 2048) <= 200 * 1024;
+    return gemv_smem_bytes(lin->kp, nt) <= 200 * 1024;
 }
 
-template <int NT, int R, bool FUSED>
+// tuning overrides, read once: KB_GEMV_THREADS (128|256), KB_GEMV_PDL (0|1), KB_GEMV_PF (2|4)
+static int env_int(const char *name, int dflt) {
+    const char *v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+
+template <int NT, int R, int PF, bool FUSED>
 static int launch_one(const GemvParams &p, int tok_groups, cudaStream_t stream) {
+    static const int env_threads = env_int("KB_GEMV_THREADS", 0);
+    static const int env_pdl = env_int("KB_GEMV_PDL", 1);
     const int row_groups = (p.m + R - 1) / R;
-    // few rows: smaller CTAs so that every SM gets work
-    const int threads = row_groups <= 148 * 16 ? 128 : 256;
+    int threads = 256;
+    if (env_threads == 128 || env_threads == 256) threads = env_threads;
     const int nwarps = threads / 32;
-    int ctas = (row_groups + nwarps - 1) / nwarps;
-    const int cap = 148 * 8;
-    if (ctas > cap) ctas = cap;
-    const size_t smem = (size_t)NT * (((size_t)p.kp + 2047) / 2048 * 2048);
-    auto kern = gemv_kernel<NT, R, FUSED>;
+    const size_t smem = gemv_smem_bytes((size_t)p.kp, NT);
+    auto kern = gemv_kernel<NT, R, PF, FUSED>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return cuda_fail(e, "gemv smem attribute");
     }
+    // persistent grid: at most one resident wave (SMs x CTAs per SM), rows are grid-strided,
+    // so there is no partial last wave and activations are staged once per CTA
+    int occ = 0, dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, smem) != cudaSuccess || occ < 1) occ = 1;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+    int ctas = (row_groups + nwarps - 1) / nwarps;
+    if (ctas > sms * occ) ctas = sms * occ;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ctas, (unsigned)tok_groups, 1);
     cfg.blockDim = dim3((unsigned)threads, 1, 1);
@@ -253,7 +354,7 @@ static int launch_one(const GemvParams &p, int tok_groups, cudaStream_t stream) 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = env_pdl ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "gemv launch");
 }
@@ -261,10 +362,16 @@ static int launch_one(const GemvParams &p, int tok_groups, cudaStream_t stream) 
 template <bool FUSED>
 static int dispatch(const GemvParams &p, cudaStream_t stream) {
     const int n = p.n;
-    if (n == 1) return launch_one<1, 4, FUSED>(p, 1, stream);
-    if (n == 2) return launch_one<2, 4, FUSED>(p, 1, stream);
-    if (n <= 4) return launch_one<4, 2, FUSED>(p, 1, stream);
-    return launch_one<8, 1, FUSED>(p, (n + 7) / 8, stream);
+    static const int env_pf = env_int("KB_GEMV_PF", 0);
+    if (n == 1) {
+        // two chunks in flight per warp at two CTAs per SM measured faster than four chunks at
+        // one CTA per SM (register pressure) on 8192-wide rows; the deep variant stays selectable
+        const bool deep = env_pf == 4;
+        return deep ? launch_one<1, 4, 4, FUSED>(p, 1, stream) : launch_one<1, 4, 2, FUSED>(p, 1, stream);
+    }
+    if (n == 2) return launch_one<2, 4, 2, FUSED>(p, 1, stream);
+    if (n <= 4) return launch_one<4, 2, 2, FUSED>(p, 1, stream);
+    return launch_one<8, 1, 2, FUSED>(p, (n + 7) / 8, stream);
 }
 
 int launch_gemv(const FwdArgs &a, cudaStream_t stream) {

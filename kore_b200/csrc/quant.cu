@@ -15,9 +15,10 @@ namespace kb {
 // ------------------------------------------------------------------ activations
 
 // One CTA per token row.  Pass 1 reduces max|x|, pass 2 (re-reading the row from L1/L2)
-// emits 16 codes per thread-iteration as one 16-byte store.  The division is an IEEE
-// round-to-nearest divide and the conversion rounds half to even, so the codes equal
-// the CPU definition bit for bit.
+// emits 16 codes per thread-iteration as one 16-byte store.  Codes equal the CPU
+// definition clamp(rne(x / s)) bit for bit: the quotient is formed as x * (1/s) and the
+// exact IEEE division is evaluated only for the rare element that lands next to a
+// rounding tie (see quantise_one_fast).
 template <bool VEC4>
 __global__ void __launch_bounds__(256) act_quant_kernel(const float *__restrict__ x, int k,
                                                         int8_t *__restrict__ xq, int ldq,
@@ -39,6 +40,7 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const float *__restrict_
     }
     amax = block_reduce_max(amax, red_f);
     const float s = amax < 1e-8f ? 1.0f : __fdiv_rn(amax, 127.0f);
+    const float rs = __frcp_rn(s);
 
     int local_sum = 0;
     int8_t *qrow = xq + t * (size_t)ldq;
@@ -58,7 +60,7 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const float *__restrict_
             uint32_t word = 0;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                int q = quantise_one(v[e], s);
+                int q = quantise_one_fast(v[e], s, rs);
                 local_sum += q;
                 word |= (uint32_t)(q & 0xff) << (8 * e);
             }

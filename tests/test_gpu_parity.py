@@ -54,6 +54,35 @@ def test_act_quant_bit_exact(torch, kb, n, k):
     assert (sumq.cpu().numpy() == sum_ref).all()
 
 
+def test_act_quant_rounding_ties_and_neighbours(torch, kb):
+    """Values placed on and next to rounding ties (j + 0.5) * s: the kernel's
+    multiply-by-reciprocal shortcut must still agree with the IEEE division everywhere."""
+    rows = []
+    for amax in (127.0, 1.0, 3.3333, 0.017, 1234.567, 2.0 ** -20):
+        s = np.float32(np.float32(amax) / np.float32(127.0))
+        j = np.arange(-127, 127, dtype=np.float32)
+        tie = ((j + np.float32(0.5)) * s).astype(np.float32)
+        vals = np.concatenate([tie, np.nextafter(tie, np.float32(np.inf)), np.nextafter(tie, np.float32(-np.inf)),
+                               (j * s).astype(np.float32)])
+        vals = np.clip(vals, -np.float32(amax), np.float32(amax))
+        vals[0] = np.float32(amax)
+        rows.append(vals.astype(np.float32))
+    x = np.stack(rows)
+    xq_ref, sx_ref, sum_ref = kbref.quantize_act_i8(x, ldq=kb.kernels.act_ld(x.shape[1]))
+    xq, sx, sumq = kb.kernels.quantize_act_i8(torch.from_numpy(x).cuda())
+    assert (sx.cpu().numpy() == sx_ref).all()
+    assert (xq.cpu().numpy() == xq_ref).all()
+    assert (sumq.cpu().numpy() == sum_ref).all()
+    # the same rows through the fused GEMV prologue (identity-like layer exposes the codes)
+    k = x.shape[1]
+    w = np.zeros((k, k), np.float32)
+    np.fill_diagonal(w, 1.0)
+    lay = kb.nn.BitLinear.new(w, None, 0.3)
+    for r in range(x.shape[0]):
+        _, acc = lay.forward(torch.from_numpy(x[r:r + 1]).cuda(), path=kb.cabi.PATH_GEMV, return_acc=True)
+        assert (acc.cpu().numpy()[0] == xq_ref[r, :k].astype(np.int32)).all()
+
+
 def test_act_quant_unaligned_rows(torch, kb):
     # a view whose rows start 4 bytes off a 16-byte boundary takes the scalar-load path
     big = torch.from_numpy(cases.gaussian(5, (1, 3 * 256 + 1), 1.0)).cuda()
