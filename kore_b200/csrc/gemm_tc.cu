@@ -21,6 +21,8 @@
 // Every wait on an mbarrier is bounded; a wait that gives up records a code in a
 // device status word, raises a CTA-wide abort flag that all other waits observe, and
 // the CTA drains its copies, frees its TMEM and returns.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "device_utils.cuh"
 
@@ -42,7 +44,7 @@ struct Cfg {
     static constexpr int STAGE_BYTES = ACT_BYTES + UNP_BYTES + PK_BYTES;
     static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 5 : 6);
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr int TAIL_BYTES = 8 * (3 * STAGES + 5) + 16 + 2 * BN * 8;
+    static constexpr int TAIL_BYTES = 8 * (3 * STAGES + 5) + 16;
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + TAIL_BYTES;
 };
 
@@ -55,7 +57,27 @@ struct GemmParams {
     size_t ldy;
     int mul, off;
     int *status;
+#ifdef KB_GEMM_DEBUG
+    int dbg;  // developer build: bit0 skip unpack work, bit1 skip packed TMA, bit2 skip act TMA, bit3 skip MMA
+#endif
 };
+#ifdef KB_GEMM_DEBUG
+#define DBG(p, bit) (((p).dbg >> (bit)) & 1)
+// developer build: per (CTA, local tile) timestamps: 0 mma start, 1 mma done issuing,
+// 2 epilogue got the accumulator, 3 epilogue done
+__device__ unsigned long long g_gemm_tl[4][148 * 8];
+__device__ __forceinline__ void gtl(int i, uint32_t ti) {
+    if (blockIdx.x < 148 && ti < 8) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_gemm_tl[i][blockIdx.x * 8 + ti] = t;
+    }
+}
+#define GTL(i, ti) gtl(i, ti)
+#else
+#define GTL(i, ti)
+#define DBG(p, bit) 0
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -167,8 +189,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     uint8_t *tail_ptr = base_ptr + STAGES * C::STAGE_BYTES;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail_ptr + 8 * (3 * STAGES + 5));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    float *ssx = reinterpret_cast<float *>(tail_ptr + 8 * (3 * STAGES + 5) + 16);  // [2][BN]
-    int *ssum = reinterpret_cast<int *>(ssx + 2 * BN);                             // [2][BN]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = p.kp / BK;
@@ -213,9 +233,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, DEV_TIMEOUT_TMA_EMPTY))) break;
-                    mbar_expect_tx(full_bar(s), C::ACT_BYTES + C::PK_BYTES);
-                    tma_load_2d(act_addr(s), &tmap_x, full_bar(s), kb * BK, n0);
-                    tma_load_2d(pk_addr(s), &tmap_w, full_bar(s), kb * (BK / 4), m0);
+                    mbar_expect_tx(full_bar(s), (DBG(p, 2) ? 0 : C::ACT_BYTES) + (DBG(p, 1) ? 0 : C::PK_BYTES));
+                    if (!DBG(p, 2)) tma_load_2d(act_addr(s), &tmap_x, full_bar(s), kb * BK, n0);
+                    if (!DBG(p, 1)) tma_load_2d(pk_addr(s), &tmap_w, full_bar(s), kb * (BK / 4), m0);
                 }
             }
             // drain: every copy this thread issued must have landed before the CTA exits
@@ -239,6 +259,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 const int b = ti & 1;
                 if (!(ok = mbar_wait(tempty_bar(b), ((ti >> 1) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM_EMPTY))) break;
                 tc_fence_after();
+                GTL(0, ti);
                 const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -250,11 +271,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     const uint64_t bdesc = umma_desc_sw128(act_addr(s));
 #pragma unroll
                     for (int k4 = 0; k4 < BK / 32; ++k4)
-                        umma_i8(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc,
+                        if (!DBG(p, 3)) umma_i8(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc,
                                 (kb | k4) != 0 ? 1u : 0u);
                     umma_commit(empty_bar(s));
                 }
                 if (ok) umma_commit(tfull_bar(b));
+                GTL(1, ti);
             }
             // all MMAs issued by this thread must retire before smem/TMEM are released
             umma_commit(drain_bar);
@@ -272,6 +294,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1u;
                 if (!(ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, DEV_TIMEOUT_UNPACK_FULL))) break;
+                if (DBG(p, 0)) { mbar_arrive(unp_bar(s)); continue; }
                 const uint8_t *pk = base_ptr + (pk_addr(s) - base) + r * 32;
                 uint8_t *dst = base_ptr + (unp_addr(s) - base) + r * 128;
                 const uint4 lo = *reinterpret_cast<const uint4 *>(pk);
@@ -292,46 +315,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         }
     } else if (warp >= 8) {
         // ---------------- epilogue ----------------
+        // Lane l of warp e owns output feature m0 + 32e + l (one TMEM lane); a chunk is 32
+        // token columns.  Per-token scale and code sum are held one column per lane in
+        // registers and broadcast with shuffles, so the loop touches no memory besides the
+        // output stores (32 lanes x 4 B = one 128-byte row segment per instruction).
         const int e = warp - 8;            // TMEM lane quarter (warp index % 4)
         const int et = threadIdx.x - 256;  // 0..127
+        constexpr int NCH = BN / 32;
+        const bool has_bias = p.bias != nullptr;
         uint32_t ti = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti) {
             const int b = ti & 1;
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
-            float *bsx = ssx + b * BN;
-            int *bsum = ssum + b * BN;
-            for (int i = et; i < BN; i += 128) {
-                const int tok = n0 + i;
-                bsx[i] = tok < p.n ? p.sx[tok] : 1.0f;
-                bsum[i] = tok < p.n ? p.sumq[tok] : 0;
-            }
             const int row = m0 + e * 32 + lane;
             const bool row_ok = row < p.m;
             const float sw = row_ok ? p.sw[row] : 0.0f;
-            const float bias = (row_ok && p.bias) ? p.bias[row] : 0.0f;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const float bias = (row_ok && has_bias) ? p.bias[row] : 0.0f;
+            // per-token scale and code sum of chunk c, one column per lane (next chunk prefetched)
+            auto load_cols = [&](int c, float &sxv, int &smv) {
+                const int tok = n0 + 32 * c + lane;
+                const bool in = c < NCH && tok < p.n;
+                sxv = in ? __ldg(p.sx + tok) : 1.0f;
+                smv = in ? __ldg(p.sumq + tok) : 0;
+            };
+            float sx_cur, sx_next;
+            int sm_cur, sm_next;
+            load_cols(0, sx_next, sm_next);
+            float *yrow = p.y ? p.y + (size_t)n0 * p.ldy + row : nullptr;
+            int32_t *arow = p.acc ? p.acc + (size_t)n0 * p.ldy + row : nullptr;
             ok = mbar_wait(tfull_bar(b), (ti >> 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_EPI_TMEM_FULL);
             if (!ok) break;
             tc_fence_after();
+            if (et == 0) GTL(2, ti);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = 0; c < NCH; ++c) {
+                sx_cur = sx_next;
+                sm_cur = sm_next;
+                load_cols(c + 1, sx_next, sm_next);
                 uint32_t v[32];
                 tmem_ld32(tmem_base + (uint32_t)(b * BN + c * 32) + ((uint32_t)(e * 32) << 16), v);
+                if (c == NCH - 1) {
+                    // this thread has read its whole accumulator: hand the TMEM buffer back
+                    // before the last stores go out
+                    tc_fence_before();
+                    mbar_arrive(tempty_bar(b));
+                }
+                const int valid = p.n - (n0 + c * 32);  // columns of this chunk that are real tokens
+                const size_t cbase = (size_t)(c * 32) * p.ldy;
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const int col = c * 32 + i;
-                    const int tok = n0 + col;
-                    if (row_ok && tok < p.n) {
-                        const int a = p.mul * (int)v[i] - p.off * bsum[col];
-                        const size_t o = (size_t)tok * p.ldy + row;
-                        if (p.acc) p.acc[o] = a;
-                        if (p.y) p.y[o] = dequant_out(a, sw, bsx[col], bias, p.bias != nullptr);
+                    const float sx_i = __shfl_sync(0xffffffffu, sx_cur, i);
+                    const int sm_i = __shfl_sync(0xffffffffu, sm_cur, i);
+                    const int a = p.mul * (int)v[i] - p.off * sm_i;
+                    const float out = dequant_out(a, sw, sx_i, bias, has_bias);
+                    if (row_ok && i < valid) {
+                        const size_t o = cbase + (size_t)i * p.ldy;
+                        if (arow) arow[o] = a;
+                        if (yrow) yrow[o] = out;
                     }
                 }
             }
-            tc_fence_before();
-            mbar_arrive(tempty_bar(b));
+            if (et == 0) GTL(3, ti);
         }
     }
 
@@ -343,6 +388,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                      : "memory");
     }
 }
+
+#ifdef KB_GEMM_DEBUG
+}  // namespace
+extern "C" int kb_debug_gemm_timeline(unsigned long long *host) {
+    return (int)cudaMemcpyFromSymbol(host, g_gemm_tl, sizeof(g_gemm_tl));
+}
+namespace {
+#endif
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -399,6 +452,9 @@ int launch_bn(const FwdArgs &a, cudaStream_t stream) {
     p.sw = L->scales; p.bias = L->bias; p.sx = a.sx; p.sumq = a.sumq;
     p.y = a.y; p.acc = a.acc; p.ldy = a.ldy ? a.ldy : L->m;
     p.mul = L->mul; p.off = L->off; p.status = L->dev_status;
+#ifdef KB_GEMM_DEBUG
+    { const char *e = getenv("KB_GEMM_DBG"); p.dbg = e ? atoi(e) : 0; }
+#endif
     auto kern = gemm_tc_kernel<BN>;
     static bool attr_set[64] = {false};
     const int dev = (L->device >= 0 && L->device < 64) ? L->device : 0;
