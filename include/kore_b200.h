@@ -181,6 +181,33 @@ int kb_pack_weights_ternary(const float *w, size_t m, size_t k, float threshold,
 int kb_pack_weights_quaternary(const float *w, size_t m, size_t k, uint8_t *packed,
                                size_t packed_len, float *scales, size_t scales_len, int device);
 
+/* ---- column-sharded forward across the GPUs of one box (one process per GPU) ----
+ * No counterpart in the reference, which has no multi-device execution (its only
+ * cross-device code is a host-staged copy, crates/kore-kernels/src/cuda/memory.rs:93-100).
+ *
+ * Rank r holds the weight rows (= output features) [col_offset, col_offset + M_shard) of a
+ * layer with m_total output features.  y_bases[q] is rank q's full output buffer
+ * [N, m_total] f32 as seen from this process: y_bases[rank] is local, the others are
+ * peer mappings obtained with kb_ipc_open.  The kernel epilogue stores this rank's
+ * slice into all of them (peer stores over NVLink); kb_peer_barrier then publishes
+ * completion to the peers and waits (bounded, about a second) for theirs. */
+int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size_t in_dim,
+                              float *const *y_bases, int world, int rank, size_t m_total,
+                              size_t col_offset, int path, void *workspace,
+                              size_t workspace_bytes, kb_stream stream);
+/* flag_arrays_dev: device array of `world` pointers, entry q = rank q's int32[world]
+ * flag array (local or peer mapping); epoch_counter_dev: one local int32, starts at 0 and
+ * is bumped by every barrier (all ranks must issue the same sequence of barriers);
+ * status_dev: one int32, set to 100+q if rank q never arrived. */
+int kb_peer_barrier(int *const *flag_arrays_dev, int world, int rank, int *epoch_counter_dev,
+                    int *status_dev, kb_stream stream);
+/* zero-filled device allocation that can be shared with peer processes, and its sharing */
+int kb_symm_alloc(size_t bytes, void **out);
+int kb_symm_free(void *p);
+int kb_ipc_export(const void *p, uint8_t *handle64);
+int kb_ipc_open(const uint8_t *handle64, void **out);
+int kb_ipc_close(void *p);
+
 /* ---- plumbing used by the host layers ---- */
 
 /* Raw device pointers of a handle (read-only views; valid until destroy). */

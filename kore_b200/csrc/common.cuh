@@ -21,6 +21,7 @@ namespace kb {
 //   quaternary: code = KORE's index  value = 2*code - 3     (pad code 0)
 // Kernels accumulate S = sum(code * xq) and correct in the epilogue:
 //   acc = mul * S - off * sum(xq),  (mul, off) = (1,1) ternary, (2,3) quaternary.
+constexpr int MAX_PEERS = 8;  // GPUs of one NVSwitch box
 constexpr int K_ALIGN = 128;
 constexpr int M_ALIGN = 128;
 
@@ -88,6 +89,10 @@ struct FwdArgs {
     float *y;      // nullable
     int32_t *acc;  // nullable
     size_t ldy;
+    // column-sharded layers: the same y values are also stored into these buffers (peer GPUs'
+    // copies of the full output, mapped into this process) at the same offsets as in y
+    float *y_more[MAX_PEERS - 1];
+    int n_more;
 };
 // decode GEMV; when args.x is set the activation quantiser is fused into its prologue
 int launch_gemv(const FwdArgs &a, cudaStream_t stream);

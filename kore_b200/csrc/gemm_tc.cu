@@ -57,6 +57,8 @@ struct GemmParams {
     size_t ldy;
     int mul, off;
     int *status;
+    float *y_more[MAX_PEERS - 1];  // further copies of y (peer GPUs), same offsets
+    int n_more;
 #ifdef KB_GEMM_DEBUG
     int dbg;  // developer build: bit0 skip unpack work, bit1 skip packed TMA, bit2 skip act TMA, bit3 skip MMA
 #endif
@@ -199,12 +201,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(unp_bar(s), 128);
+            mbar_init(unp_bar(s), 4);     // one arrival per unpack warp
             mbar_init(empty_bar(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), 128);
+            mbar_init(tempty_bar(b), 4);  // one arrival per epilogue warp
         }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
@@ -294,7 +296,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1u;
                 if (!(ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, DEV_TIMEOUT_UNPACK_FULL))) break;
-                if (DBG(p, 0)) { mbar_arrive(unp_bar(s)); continue; }
+                if (DBG(p, 0)) { __syncwarp(); if (lane == 0) mbar_arrive(unp_bar(s)); continue; }
                 const uint8_t *pk = base_ptr + (pk_addr(s) - base) + r * 32;
                 uint8_t *dst = base_ptr + (unp_addr(s) - base) + r * 128;
                 const uint4 lo = *reinterpret_cast<const uint4 *>(pk);
@@ -309,8 +311,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     o.w = (w[c] >> 6) & 0x03030303u;
                     *reinterpret_cast<uint4 *>(dst + ((c ^ (r & 7)) << 4)) = o;
                 }
+                // every thread publishes its own generic-proxy stores to the async proxy, then
+                // one lane per warp arrives (128 arrivals on one mbarrier would serialise)
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(unp_bar(s));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(unp_bar(s));
             }
         }
     } else if (warp >= 8) {
@@ -342,7 +347,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             float sx_cur, sx_next;
             int sm_cur, sm_next;
             load_cols(0, sx_next, sm_next);
-            float *yrow = p.y ? p.y + (size_t)n0 * p.ldy + row : nullptr;
+            const size_t yoff = (size_t)n0 * p.ldy + row;
+            float *yrow = p.y ? p.y + yoff : nullptr;
             int32_t *arow = p.acc ? p.acc + (size_t)n0 * p.ldy + row : nullptr;
             ok = mbar_wait(tfull_bar(b), (ti >> 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_EPI_TMEM_FULL);
             if (!ok) break;
@@ -359,7 +365,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     // this thread has read its whole accumulator: hand the TMEM buffer back
                     // before the last stores go out
                     tc_fence_before();
-                    mbar_arrive(tempty_bar(b));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(b));
                 }
                 const int valid = p.n - (n0 + c * 32);  // columns of this chunk that are real tokens
                 const size_t cbase = (size_t)(c * 32) * p.ldy;
@@ -372,10 +379,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     if (row_ok && i < valid) {
                         const size_t o = cbase + (size_t)i * p.ldy;
                         if (arow) arow[o] = a;
-                        if (yrow) yrow[o] = out;
+                        if (yrow) {
+                            yrow[o] = out;
+                            for (int q = 0; q < p.n_more; ++q) p.y_more[q][yoff + o] = out;  // peer copies over NVLink
+                        }
                     }
                 }
             }
+            if (p.n_more) __threadfence_system();  // peer copies of this tile are ordered before the exit
             if (et == 0) GTL(3, ti);
         }
     }
@@ -451,6 +462,8 @@ int launch_bn(const FwdArgs &a, cudaStream_t stream) {
     p.m = (int)L->m; p.n = (int)a.n; p.kp = (int)L->kp;
     p.sw = L->scales; p.bias = L->bias; p.sx = a.sx; p.sumq = a.sumq;
     p.y = a.y; p.acc = a.acc; p.ldy = a.ldy ? a.ldy : L->m;
+    p.n_more = a.y ? a.n_more : 0;
+    for (int q = 0; q < MAX_PEERS - 1; ++q) p.y_more[q] = q < p.n_more ? a.y_more[q] : nullptr;
     p.mul = L->mul; p.off = L->off; p.status = L->dev_status;
 #ifdef KB_GEMM_DEBUG
     { const char *e = getenv("KB_GEMM_DBG"); p.dbg = e ? atoi(e) : 0; }

@@ -48,6 +48,8 @@ struct GemvParams {
     size_t ldy;
     int mul, off;
     int x_vec4;
+    float *y_more[MAX_PEERS - 1];  // further copies of y (peer GPUs), same offsets
+    int n_more;
 };
 
 // 16-element group g (k = 16*g .. 16*g+15) <-> shared-memory slot: inside each
@@ -290,7 +292,12 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
                             const int a = p.mul * mine - p.off * s_sum[t];
                             const size_t o = (size_t)tok * p.ldy + row;
                             if (p.acc) p.acc[o] = a;
-                            if (p.y) p.y[o] = dequant_out(a, my_sw, s_sx[t], my_bias, p.bias != nullptr);
+                            if (p.y) {
+                                const float v = dequant_out(a, my_sw, s_sx[t], my_bias, p.bias != nullptr);
+                                p.y[o] = v;
+                                for (int q = 0; q < p.n_more; ++q) p.y_more[q][o] = v;  // peer copies over NVLink
+                                if (p.n_more) __threadfence_system();
+                            }
                         }
                     }
                     cci = 0;
@@ -386,6 +393,8 @@ int launch_gemv(const FwdArgs &a, cudaStream_t stream) {
     p.x = a.x; p.xq = a.xq; p.ldq = a.ldq; p.sx = a.sx; p.sumq = a.sumq;
     p.n = (int)a.n; p.y = a.y; p.acc = a.acc; p.ldy = a.ldy ? a.ldy : L->m;
     p.mul = L->mul; p.off = L->off;
+    p.n_more = a.y ? a.n_more : 0;
+    for (int q = 0; q < MAX_PEERS - 1; ++q) p.y_more[q] = q < p.n_more ? a.y_more[q] : nullptr;
     p.x_vec4 = a.x && (L->k % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
     if (a.x) return dispatch<true>(p, stream);
     if ((reinterpret_cast<uintptr_t>(a.xq) & 15) || (a.ldq % 16) || a.ldq < L->kp)

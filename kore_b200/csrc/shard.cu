@@ -1,0 +1,167 @@
+// Column-sharded forward across the GPUs of one NVSwitch box (one process per GPU).
+//
+// Output features are independent, so rank r owns weight rows [r*M/g, (r+1)*M/g) and
+// every rank needs the full y[N, M].  Instead of computing a slice and then calling a
+// collective, the GEMV / GEMM epilogue stores each output value into every rank's copy
+// of y (local store + peer stores over NVLink, plain st.global to peer-mapped memory),
+// so the exchange overlaps the kernel tile by tile.  A small barrier kernel then tells
+// the peers that this rank's slice has landed and waits until theirs have.
+//
+// Peer buffers are cudaMalloc allocations exchanged as CUDA IPC handles (the host layer
+// moves the 64-byte handles with torch.distributed).  No cluster multicast, no multimem:
+// ordinary peer loads and stores only.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace kb {
+
+// Every rank runs one CTA.  The epoch is a device-side counter bumped by each barrier, so
+// the same captured launch can be replayed from a CUDA graph (all ranks run the same
+// sequence of barriers, hence agree on the epoch).  Thread j < world publishes the epoch
+// into slot [rank] of rank j's flag array (system-scope release; the slice stores of the
+// preceding kernel on this stream are complete before this kernel starts), then waits,
+// bounded, until slot [j] of the local flag array has reached it.
+__global__ void peer_barrier_kernel(int *const *flag_arrays, int world, int rank, int *epoch_counter,
+                                    int *status, long long max_cycles) {
+    __shared__ int s_epoch;
+    if (threadIdx.x == 0) s_epoch = ++(*epoch_counter);
+    __syncthreads();
+    const int epoch = s_epoch;
+    const int j = threadIdx.x;
+    if (j < world) {
+        __threadfence_system();
+        int *remote = flag_arrays[j] + rank;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+        const int *mine = flag_arrays[rank] + j;
+        const long long t0 = clock64();
+        bool ok = false;
+        for (;;) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (v - epoch >= 0) { ok = true; break; }
+            if (clock64() - t0 > max_cycles) break;
+        }
+        if (!ok) atomicCAS(status, 0, 100 + j);  // peer j never arrived
+    }
+}
+
+}  // namespace kb
+
+using namespace kb;
+
+extern "C" {
+
+int kb_symm_alloc(size_t bytes, void **out) {
+    if (!out || bytes == 0) return fail(KB_ERR_INVALID, "null pointer or zero size");
+    void *p = nullptr;
+    KB_CUDA(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    if (e != cudaSuccess) { cudaFree(p); return cuda_fail(e, "cudaMemset"); }
+    *out = p;
+    return KB_OK;
+}
+
+int kb_symm_free(void *p) {
+    if (!p) return KB_OK;
+    KB_CUDA(cudaFree(p));
+    return KB_OK;
+}
+
+int kb_ipc_export(const void *p, uint8_t *handle64) {
+    if (!p || !handle64) return fail(KB_ERR_INVALID, "null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+    cudaIpcMemHandle_t h;
+    KB_CUDA(cudaIpcGetMemHandle(&h, const_cast<void *>(p)));
+    memcpy(handle64, &h, 64);
+    return KB_OK;
+}
+
+int kb_ipc_open(const uint8_t *handle64, void **out) {
+    if (!handle64 || !out) return fail(KB_ERR_INVALID, "null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    KB_CUDA(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess));
+    return KB_OK;
+}
+
+int kb_ipc_close(void *p) {
+    if (!p) return KB_OK;
+    KB_CUDA(cudaIpcCloseMemHandle(p));
+    return KB_OK;
+}
+
+int kb_peer_barrier(int *const *flag_arrays_dev, int world, int rank, int *epoch_counter_dev, int *status_dev,
+                    kb_stream stream) {
+    if (!flag_arrays_dev || !status_dev || !epoch_counter_dev) return fail(KB_ERR_INVALID, "null pointer");
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world)
+        return fail(KB_ERR_INVALID, "world %d / rank %d outside 1..%d", world, rank, MAX_PEERS);
+    // about one second of SM clocks: a peer that never arrives ends the wait with a status code
+    peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flag_arrays_dev, world, rank, epoch_counter_dev,
+                                                                         status_dev, 2000000000ll);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "peer barrier launch");
+}
+
+int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *const *y_bases,
+                              int world, int rank, size_t m_total, size_t col_offset, int path, void *workspace,
+                              size_t workspace_bytes, kb_stream stream) {
+    const Linear *L = reinterpret_cast<const Linear *>(h);
+    if (!L || L->magic != HANDLE_MAGIC) return fail(KB_ERR_BAD_HANDLE, "null or destroyed kb_linear handle");
+    if (!y_bases || !x) return fail(KB_ERR_INVALID, "null pointer");
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world)
+        return fail(KB_ERR_INVALID, "world %d / rank %d outside 1..%d", world, rank, MAX_PEERS);
+    if (in_dim != L->k)
+        return fail(KB_ERR_SHAPE, "shape mismatch: expected [%zu], got last dimension %zu", L->k, in_dim);
+    if (col_offset + L->m > m_total)
+        return fail(KB_ERR_SHAPE, "slice [%zu, %zu) does not fit in %zu output features", col_offset,
+                    col_offset + L->m, m_total);
+    if (n == 0) return KB_OK;
+    for (int q = 0; q < world; ++q)
+        if (!y_bases[q]) return fail(KB_ERR_INVALID, "null output base for rank %d", q);
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (prev != L->device && (e = cudaSetDevice(L->device)) != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    FwdArgs a = {};
+    a.lin = L; a.n = n; a.ldy = m_total;
+    a.y = y_bases[rank] + col_offset;
+    a.n_more = 0;
+    for (int q = 0; q < world; ++q)
+        if (q != rank) a.y_more[a.n_more++] = y_bases[q] + col_offset;
+    if (path == KB_PATH_AUTO) path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : KB_PATH_GEMM_TC;
+    int rc;
+    if (path == KB_PATH_GEMV) {
+        a.x = x;
+        rc = launch_gemv(a, st);
+    } else {
+        const size_t xq_bytes = (n * L->kp + 255) / 256 * 256, vec_bytes = (n * 4 + 255) / 256 * 256;
+        const size_t need = xq_bytes + 2 * vec_bytes;
+        uint8_t *ws = static_cast<uint8_t *>(workspace);
+        bool own = false;
+        rc = KB_OK;
+        if (!ws) {
+            e = cudaMallocAsync(reinterpret_cast<void **>(&ws), need, st);
+            if (e != cudaSuccess) rc = cuda_fail(e, "workspace allocation");
+            own = true;
+        } else if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255)) {
+            rc = fail(KB_ERR_STORAGE, "workspace too small or misaligned: need %zu bytes, got %zu", need, workspace_bytes);
+        }
+        if (rc == KB_OK) {
+            int8_t *xq = reinterpret_cast<int8_t *>(ws);
+            float *sx = reinterpret_cast<float *>(ws + xq_bytes);
+            int32_t *sumq = reinterpret_cast<int32_t *>(ws + xq_bytes + vec_bytes);
+            rc = launch_act_quant(x, n, L->k, xq, L->kp, sx, sumq, st);
+            if (rc == KB_OK) {
+                a.xq = xq; a.ldq = L->kp; a.sx = sx; a.sumq = sumq;
+                rc = launch_gemm_tc(a, st);
+            }
+            if (own) cudaFreeAsync(ws, st);
+        }
+    }
+    if (prev != L->device) cudaSetDevice(prev);
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,228 @@
+"""Column-sharded BitLinear / QuatLinear across the GPUs of one box (one process per GPU).
+
+Output features are independent, so rank r keeps weight rows
+``[start_r, start_r + size_r)`` of the packed layer and every rank ends up with the full
+``y[N, M]``.  Two exchanges are provided:
+
+* ``"p2p"`` (default on GPUs): the GEMV / GEMM epilogue stores each value into every
+  rank's output buffer (peer stores over NVLink to IPC-mapped ``cudaMalloc`` memory), then
+  a one-CTA barrier kernel publishes completion and waits, bounded, for the peers.  Output
+  buffers are double-buffered by call parity so a fast rank never overwrites data a slow
+  rank is still reading (a captured CUDA graph should hold an even number of forwards so
+  that the parity sequence repeats from replay to replay).
+* ``"collective"``: each rank computes ``[N, M/g]`` and the slices are exchanged with
+  ``torch.distributed.all_gather_into_tensor`` (NCCL on GPUs; gloo in the CPU tests),
+  then laid out as ``[N, M]``.
+
+The reference has nothing distributed; the per-tensor absmean scale is computed on the
+full tensor before splitting so that results do not depend on the number of ranks.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from . import _cabi
+from ._cabi import QUATERNARY, TERNARY
+
+MAX_PEERS = 8
+
+
+# ---- pure host logic (exercised on CPU with gloo) ---------------------------------------
+def row_partition(m: int, world: int) -> List[Tuple[int, int]]:
+    """(start, size) of every rank's block of output features: sizes differ by at most one
+    32-feature granule so every slice but the last starts on a 128-byte boundary of y."""
+    if world < 1 or world > MAX_PEERS:
+        raise ValueError(f"world size {world} outside 1..{MAX_PEERS}")
+    granule = 32
+    units = (m + granule - 1) // granule
+    base, rem = divmod(units, world)
+    out, start = [], 0
+    for r in range(world):
+        size = min((base + (1 if r < rem else 0)) * granule, max(0, m - start))
+        out.append((start, size))
+        start += size
+    assert start == m
+    return out
+
+
+def wire_row_bytes(kind: int, k: int) -> int:
+    return (k + 4) // 5 if kind == TERNARY else (k + 3) // 4
+
+
+def slice_wire_rows(kind: int, packed, scales, bias, m: int, k: int, start: int, size: int):
+    """Rows [start, start+size) of a layer in the reference wire format (row-major, so a
+    slice of rows is a contiguous slice of bytes)."""
+    rb = wire_row_bytes(kind, k)
+    packed = np.ascontiguousarray(packed, dtype=np.uint8).ravel()
+    scales = np.ascontiguousarray(scales, dtype=np.float32).ravel()
+    if packed.size < m * rb or scales.size < m:
+        raise ValueError("packed / scales shorter than the full layer")
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32).ravel()[start:start + size]
+    return packed[start * rb:(start + size) * rb], scales[start:start + size], b
+
+
+def assemble_gathered(chunks: Sequence, sizes: Sequence[int]):
+    """[g] x [N, size_r] -> [N, M] (works for numpy arrays and torch tensors)."""
+    first = chunks[0]
+    if hasattr(first, "numpy") or type(first).__module__.startswith("torch"):
+        import torch
+
+        return torch.cat([c[:, :s] for c, s in zip(chunks, sizes)], dim=1)
+    return np.concatenate([c[:, :s] for c, s in zip(chunks, sizes)], axis=1)
+
+
+# ---- symmetric buffers --------------------------------------------------------------------
+class _DevView:
+    """Exposes a raw device pointer to torch through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+class ShardContext:
+    """Per-process exchange state shared by all sharded layers: two output buffers
+    [max_tokens, m_total] f32 and a flag array per rank, each mapped into every peer."""
+
+    def __init__(self, rank: int, world: int, m_total: int, max_tokens: int, device: int, dist):
+        import torch
+
+        self.rank, self.world, self.m_total, self.max_tokens = rank, world, m_total, max_tokens
+        self.device, self.dist = device, dist
+        self.lib = _cabi.lib()
+        self.epoch = 0
+        torch.cuda.set_device(device)
+        self.y_bytes = max_tokens * m_total * 4
+        total = 2 * self.y_bytes + 256
+        base = C.c_void_p()
+        _cabi.check(self.lib.kb_symm_alloc(total, C.byref(base)))
+        self.local_base = base.value
+        handle = np.zeros(64, np.uint8)
+        _cabi.check(self.lib.kb_ipc_export(self.local_base, handle.ctypes.data))
+        gathered = [None] * world
+        dist.all_gather_object(gathered, handle.tobytes())
+        self.peer_bases = []
+        for q in range(world):
+            if q == rank:
+                self.peer_bases.append(self.local_base)
+            else:
+                p = C.c_void_p()
+                h = np.frombuffer(gathered[q], np.uint8).copy()
+                _cabi.check(self.lib.kb_ipc_open(h.ctypes.data, C.byref(p)))
+                self.peer_bases.append(p.value)
+        dev = torch.device("cuda", device)
+        # device-side pointer tables: [2][world] output bases, [world] flag arrays
+        ybases = [[b + par * self.y_bytes for b in self.peer_bases] for par in range(2)]
+        self.y_tables = [torch.tensor(t, dtype=torch.int64, device=dev) for t in ybases]
+        self.y_tables_host = [(C.c_void_p * world)(*t) for t in ybases]
+        self.flag_table = torch.tensor([b + 2 * self.y_bytes for b in self.peer_bases], dtype=torch.int64, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.epoch_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.local_y = [torch.as_tensor(_DevView(self.local_base + par * self.y_bytes, (max_tokens, m_total), "<f4"),
+                                        device=dev) for par in range(2)]
+        dist.barrier()
+
+    def close(self):
+        if getattr(self, "local_base", None):
+            import torch
+
+            torch.cuda.synchronize(self.device)
+            self.dist.barrier()
+            for q, b in enumerate(self.peer_bases):
+                if q != self.rank:
+                    self.lib.kb_ipc_close(b)
+            self.dist.barrier()
+            self.lib.kb_symm_free(self.local_base)
+            self.local_base = None
+
+    def next_parity(self) -> int:
+        self.epoch += 1
+        return self.epoch & 1
+
+    def barrier(self, stream_ptr: int):
+        _cabi.check(self.lib.kb_peer_barrier(self.flag_table.data_ptr(), self.world, self.rank,
+                                             self.epoch_counter.data_ptr(), self.status.data_ptr(), stream_ptr))
+
+    def check_status(self):
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise _cabi.KoreError(_cabi.ERR_TIMEOUT, f"peer barrier gave up waiting (device code {code})")
+
+
+class ShardedLinear:
+    """One rank's share of a column-sharded layer.
+
+    ``compute`` replaces the CUDA layer by a callable ``(packed, scales, bias, m, k, x) ->
+    y[N, m]`` — used by the CPU tests of the host logic (gloo), never by the product path.
+    """
+
+    def __init__(self, kind: int, packed, scales, bias, in_features: int, out_features: int, rank: int, world: int,
+                 *, device: int = 0, ctx: Optional[ShardContext] = None, dist=None, exchange: str = "p2p",
+                 compute: Optional[Callable] = None):
+        self.kind, self.k, self.m_total = kind, in_features, out_features
+        self.rank, self.world = rank, world
+        self.parts = row_partition(out_features, world)
+        self.start, self.size = self.parts[rank]
+        self.exchange, self.ctx, self.dist = exchange, ctx, (dist if dist is not None else (ctx.dist if ctx else None))
+        p, s, b = slice_wire_rows(kind, packed, scales, bias, out_features, in_features, self.start, self.size)
+        self._compute = compute
+        self._wire = (p.copy(), s.copy(), None if b is None else b.copy())
+        self.layer = None
+        if compute is None:
+            from . import nn
+
+            cls = nn.BitLinear if kind == TERNARY else nn.QuatLinear
+            self.layer = cls.from_packed(p, s, b, in_features, self.size, device=device)
+        if exchange == "p2p" and compute is None and ctx is None:
+            raise ValueError("the p2p exchange needs a ShardContext")
+
+    # -- product path -------------------------------------------------------------------------
+    def forward(self, x, path: int = _cabi.PATH_AUTO, stream_ptr: Optional[int] = None):
+        """x: CUDA f32 [N, K] (replicated on every rank) -> y [N, M] on this rank."""
+        if self._compute is not None:
+            return self._forward_collective_generic(x)
+        import torch
+
+        n = x.shape[0]
+        if stream_ptr is None:
+            stream_ptr = torch.cuda.current_stream(x.device.index).cuda_stream
+        if self.exchange == "p2p":
+            ctx = self.ctx
+            if n > ctx.max_tokens or self.m_total != ctx.m_total:
+                raise _cabi.KoreError(_cabi.ERR_UNSUPPORTED, "tokens or features exceed the shard context")
+            par = ctx.next_parity()
+            _cabi.check(ctx.lib.kb_linear_forward_sharded(
+                self.layer.handle, x.data_ptr(), n, x.shape[1], ctx.y_tables_host[par], self.world, self.rank,
+                self.m_total, self.start, path, None, 0, stream_ptr))
+            ctx.barrier(stream_ptr)
+            return ctx.local_y[par][:n]
+        # collective: equal-sized staging blocks, NCCL all-gather, then [g, N, s] -> [N, M]
+        smax = max(s for _, s in self.parts)
+        stage = torch.zeros((n, smax), dtype=torch.float32, device=x.device)
+        _cabi.check(_cabi.lib().kb_linear_forward_ex(self.layer.handle, x.data_ptr(), n, x.shape[1], stage.data_ptr(),
+                                                     smax, None, path, None, 0, stream_ptr))
+        out = torch.empty((self.world, n, smax), dtype=torch.float32, device=x.device)
+        self.dist.all_gather_into_tensor(out, stage)
+        if n == 1 and all(s == smax for _, s in self.parts):
+            return out.reshape(1, self.world * smax)
+        return assemble_gathered([out[q] for q in range(self.world)], [s for _, s in self.parts])
+
+    __call__ = forward
+
+    # -- CPU test path: same partition / gather logic, compute injected -------------------------
+    def _forward_collective_generic(self, x):
+        import torch
+
+        p, s, b = self._wire
+        y_local = np.asarray(self._compute(p, s, b, self.size, self.k, np.asarray(x, dtype=np.float32)), dtype=np.float32)
+        n = y_local.shape[0]
+        smax = max(sz for _, sz in self.parts)
+        stage = torch.zeros((n, smax), dtype=torch.float32)
+        stage[:, :self.size] = torch.from_numpy(y_local)
+        chunks = [torch.empty_like(stage) for _ in range(self.world)]
+        self.dist.all_gather(chunks, stage)
+        return assemble_gathered(chunks, [sz for _, sz in self.parts]).numpy()
