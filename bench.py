@@ -7,8 +7,13 @@ Headline workload (N = 1): the batch-1 decode GEMV of BASELINE.json configs[1] â
 ternary 4096x4096 weights (absmean-ternarised N(0, 0.02^2), seed 2001), one f32
 activation row N(0,1) (seed 2002), per-token int8 absmax fused into the kernel.
 A "step" is one pass over a pool of POOL distinct copies of that layer (each copy has
-its own allocation, POOL * 4 MiB > the 126 MB L2, so every weight byte comes from HBM),
+its own allocation, POOL * 4 MiB > the 126 MB L2, so every weight byte comes from HBM).
+Each layer forward is two launches â€” the per-token int8 quantiser of its f32 input and
+the decode GEMV â€” and the layers of the pool, which are independent of one another, are
+spread round-robin over STREAMS CUDA streams; the whole step is captured once and
 replayed as one CUDA graph.  value = algorithmic bytes of the step / device time.
+The same pool as a single stream-ordered chain (what a decoder's dependent layers look
+like) is reported under "extra".
 
 With N > 1 every rank owns a 4096-row shard of a K=4096 x M=4096*N projection (weak
 scaling: per-GPU work is the N = 1 workload), computes its slice and the slices are
@@ -35,6 +40,7 @@ if ROOT not in sys.path:
 
 M_DEC, K_DEC = 4096, 4096
 POOL = 160  # 160 x 4 MiB = 640 MiB of packed weights, five times the L2
+STREAMS = 16
 METRIC, UNIT = "bitlinear_gemv_hbm_gbs", "GB/s"
 
 
@@ -152,9 +158,19 @@ def run_reference_impl(args):
 
 
 # --------------------------------------------------------------------------- GPU arm
-def time_graph(torch, fn, steps, warmup, stream):
-    """Capture fn() (one step) into a CUDA graph, replay warmup + steps, return seconds per step."""
+def time_graph(torch, fn, steps, warmup, stream, hold_s=0.0):
+    """Capture fn() (one step) into a CUDA graph, replay warmup + steps, return seconds per step.
+    hold_s > 0 keeps the same graph replaying (untimed) for that long before and after the
+    timed steps, so that a clock sampler running alongside sees the GPU under this load."""
     g = torch.cuda.CUDAGraph()
+
+    def hold():
+        t_end = time.perf_counter() + hold_s
+        while hold_s > 0 and time.perf_counter() < t_end:
+            for _ in range(20):
+                g.replay()
+            stream.synchronize()
+
     with torch.cuda.stream(stream):
         fn()  # eager warm-up (also sets function attributes outside capture)
         stream.synchronize()
@@ -163,13 +179,38 @@ def time_graph(torch, fn, steps, warmup, stream):
         for _ in range(warmup):
             g.replay()
         stream.synchronize()
+        hold()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(steps):
             g.replay()
         e1.record(stream)
         stream.synchronize()
+        hold()
     return e0.elapsed_time(e1) / 1e3 / steps, g
+
+
+class StreamFan:
+    """Round-robin fan-out of independent launches over several CUDA streams, fork/join'd
+    on a main stream so that the whole step can be captured into one CUDA graph."""
+
+    def __init__(self, torch, main, count):
+        self.torch, self.main = torch, main
+        self.side = [torch.cuda.Stream(device=main.device) for _ in range(count)] if count > 1 else [main]
+
+    def fork(self):
+        if len(self.side) > 1:
+            ev = self.torch.cuda.Event()
+            ev.record(self.main)
+            for st in self.side:
+                st.wait_event(ev)
+
+    def join(self):
+        if len(self.side) > 1:
+            for st in self.side:
+                ev = self.torch.cuda.Event()
+                ev.record(st)
+                self.main.wait_event(ev)
 
 
 def main():
@@ -180,6 +221,7 @@ def main():
     ap.add_argument("--impl", default="kore_b200")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill / quaternary / batch side measurements")
     ap.add_argument("--pool", type=int, default=POOL)
+    ap.add_argument("--streams", type=int, default=STREAMS)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -203,10 +245,10 @@ def main():
         dist = dist_
         dist.init_process_group("nccl", device_id=dev)
     lib = _cabi.lib()
-    pool_n = args.pool
+    pool_n = args.pool + (args.pool & 1)  # even: the sharded double buffering repeats per replay
     peaks = measured_peaks()
 
-    # ---- weights: one seeded layer, POOL separately allocated copies of its shard
+    # ---- weights: one seeded layer, POOL separately allocated copies of this rank's shard
     w = gaussian(2001 + rank, (M_DEC, K_DEC), 0.02)
     proto = nn.BitLinear.new(w, None, 0.3, quantiser="absmean", device=local_rank)
     packed, scales = proto.packed_weights(), proto.scales()
@@ -215,40 +257,64 @@ def main():
     x_pin = torch.from_numpy(x_host).pin_memory()
     x_dev = x_pin.to(dev)
     m_total = M_DEC * world
-    y_full = torch.zeros((1, m_total), dtype=torch.float32, device=dev)
-    stream = torch.cuda.Stream(device=dev)
-    sptr = stream.cuda_stream
+    main_stream = torch.cuda.Stream(device=dev)
+    ld = kernels.act_ld(K_DEC)
 
-    gather = None
-    if world > 1:
+    if world == 1:
+        n_streams = max(1, args.streams)
+        fan = StreamFan(torch, main_stream, n_streams)
+        ys = [torch.zeros((1, M_DEC), dtype=torch.float32, device=dev) for _ in fan.side]
+        xqs = [torch.zeros((1, ld), dtype=torch.int8, device=dev) for _ in fan.side]
+        sxs = [torch.zeros(1, dtype=torch.float32, device=dev) for _ in fan.side]
+        sms = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in fan.side]
+
+        def step():
+            fan.fork()
+            for j, lay in enumerate(pool):
+                i = j % len(fan.side)
+                sp = fan.side[i].cuda_stream
+                _cabi.check(lib.kb_quantize_act_i8(x_dev.data_ptr(), 1, K_DEC, xqs[i].data_ptr(), ld, sxs[i].data_ptr(),
+                                                   sms[i].data_ptr(), sp))
+                _cabi.check(lib.kb_linear_forward_q8(lay.handle, xqs[i].data_ptr(), ld, sxs[i].data_ptr(), sms[i].data_ptr(),
+                                                     1, ys[i].data_ptr(), 0, None, _cabi.PATH_GEMV, sp))
+            fan.join()
+
+        launches_per_step = 2 * pool_n
+        y_view = lambda: ys[(pool_n - 1) % len(fan.side)][0]
+        ctx = None
+    else:
         from kore_b200 import sharded
 
-        gather = sharded.SliceExchange(y_full, rank, world, M_DEC, dist)
+        n_streams = 1
+        ctx = sharded.ShardContext(rank, world, m_total, 8, local_rank, dist)
+        sp = main_stream.cuda_stream
+        last_par = [0]
 
-    def step():
-        for lay in pool:
-            _cabi.check(lib.kb_linear_forward_ex(lay.handle, x_dev.data_ptr(), 1, K_DEC,
-                                                 y_full.data_ptr() + 4 * rank * M_DEC, m_total, None, _cabi.PATH_GEMV,
-                                                 None, 0, sptr))
-            if gather is not None:
-                gather.exchange(stream)
+        def step():
+            for lay in pool:
+                par = ctx.next_parity()
+                last_par[0] = par
+                _cabi.check(lib.kb_linear_forward_sharded(lay.handle, x_dev.data_ptr(), 1, K_DEC, ctx.y_tables_host[par],
+                                                          world, rank, m_total, rank * M_DEC, _cabi.PATH_GEMV, None, 0, sp))
+                ctx.barrier(sp)
 
-    launches_per_step = pool_n * (1 if gather is None else 1 + gather.launches_per_exchange)
+        launches_per_step = 2 * pool_n
+        y_view = lambda: ctx.local_y[last_par[0]][0, rank * M_DEC:(rank + 1) * M_DEC]
+
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
     with ClockSampler(local_rank) as clocks:
-        sec_per_step, graph = time_graph(torch, step, args.steps, args.warmup, stream)
+        sec_per_step, graph = time_graph(torch, step, args.steps, args.warmup, main_stream, hold_s=0.7)
     torch.cuda.synchronize()
     if dist is not None:
         t = torch.tensor([sec_per_step], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         sec_per_step = float(t.item())
+        ctx.check_status()
     step_bytes = pool_n * gemv_bytes(M_DEC, K_DEC, 1) * world
     value = step_bytes / sec_per_step / 1e9
-
-    # correctness spot check of what was just timed (cheap, outside the timed region)
-    y_chk = y_full[0, rank * M_DEC:(rank + 1) * M_DEC].cpu().numpy()
+    y_chk = y_view().cpu().numpy().copy()  # what the timed path produced for the last layer
 
     # ---- end to end: host buffers through the C ABI, copies inside the timed region
     y_host = np.zeros((1, M_DEC), np.float32)
@@ -274,12 +340,13 @@ def main():
         e2e_sec = float(t.item())
     e2e = {"value": step_bytes / e2e_sec / 1e9, "unit": UNIT, "h2d_bytes_per_step": pool_n * 4 * K_DEC,
            "d2h_bytes_per_step": pool_n * 4 * M_DEC, "ms_per_step": e2e_sec * 1e3,
-           "note": "kb_linear_forward_host per layer: pinned x -> device, fused quantiser+GEMV, y -> host, synchronise"}
+           "note": "kb_linear_forward_host per layer: pinned x -> device, quantiser + GEMV, y -> host, synchronise"}
     assert (y_host[0] == y_chk).all(), "host entry point and graph replay disagree"
 
     if rank != 0:
         if dist is not None:
             dist.barrier()
+            ctx.close()
             dist.destroy_process_group()
         return
 
@@ -287,7 +354,8 @@ def main():
     achieved = gemv_bytes(M_DEC, K_DEC, 1) / per_launch_s / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["src"],
-                "kernel": "gemv_kernel<1,4,fused>", "us_per_launch": per_launch_s * 1e6,
+                "kernel": "gemv_kernel<1,4,2,q8>", "us_per_layer": per_launch_s * 1e6,
+                "note": "step time / layers: launches of independent layers overlap across streams",
                 "frac_of_nominal_8000": achieved / 8000.0}
     tpath = os.path.join(ROOT, "profiles", "gemv_traffic.json")
     if os.path.exists(tpath):
@@ -299,7 +367,7 @@ def main():
     extras = {}
     if not args.no_extras and world == 1:
         try:
-            extras = side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args)
+            extras = side_measurements(torch, lib, _cabi, nn, kernels, dev, main_stream, peaks, args, pool, x_dev)
         except Exception as exc:  # side numbers must never cost the headline line
             extras = {"error": repr(exc)}
 
@@ -309,9 +377,10 @@ def main():
         "dtype": "int8", "data": "synthetic",
         "config": {"workload": "decode_gemv_ternary_4096x4096_batch1" if world == 1 else
                    f"decode_gemv_ternary_K4096_M{m_total}_batch1_column_sharded_{world}x4096",
-                   "pool": pool_n, "pool_bytes": pool_n * M_DEC * K_DEC // 4,
+                   "pool": pool_n, "pool_bytes": pool_n * M_DEC * K_DEC // 4, "streams": n_streams,
                    "l2": "inputs larger than L2 (pool of separately allocated weight copies)",
-                   "quantiser": "absmean per-tensor", "timing": "CUDA events around CUDA-graph replays of the step"},
+                   "quantiser": "absmean per-tensor", "timing": "CUDA events around CUDA-graph replays of the step",
+                   "exchange": None if world == 1 else "epilogue peer stores over NVLink + flag barrier"},
         "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks.summary(),
     }
     if cpu is not None:
@@ -321,16 +390,59 @@ def main():
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
+        ctx.close()
         dist.destroy_process_group()
 
 
-def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args):
+def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, pool, x_dev):
     """Other configurations of BASELINE.json, measured briefly: quaternary GEMV, batch-8 GEMV,
     prefill GEMM (2048 tokens, 4096 -> 11008 and 11008 -> 4096) with a library int8 GEMM
     timed beside it as a local ceiling."""
     out = {}
     sptr = stream.cuda_stream
     steps, warm = 10, 3
+
+    # the headline pool as one stream-ordered chain (each layer waits for the previous one)
+    y1 = torch.empty((1, M_DEC), dtype=torch.float32, device=dev)
+    xq, sx, sumq = kernels.quantize_act_i8(x_dev)
+
+    def chain_fused():
+        for lay in pool:
+            _cabi.check(lib.kb_linear_forward_ex(lay.handle, x_dev.data_ptr(), 1, K_DEC, y1.data_ptr(), 0, None,
+                                                 _cabi.PATH_GEMV, None, 0, sptr))
+
+    def chain_q8():
+        for lay in pool:
+            _cabi.check(lib.kb_linear_forward_q8(lay.handle, xq.data_ptr(), xq.stride(0), sx.data_ptr(), sumq.data_ptr(), 1,
+                                                 y1.data_ptr(), 0, None, _cabi.PATH_GEMV, sptr))
+
+    for name, fn in (("chain_fused_quantiser_1_launch_per_layer", chain_fused), ("chain_prequantised_input", chain_q8)):
+        sec, _ = time_graph(torch, fn, steps, warm, stream)
+        gbs = len(pool) * gemv_bytes(M_DEC, K_DEC, 1) / sec / 1e9
+        out[f"gemv_4096x4096_batch1_{name}"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                                                 "us_per_layer": sec / len(pool) * 1e6}
+
+    # the 70B-class FFN shape on one GPU (58.7 MB per layer: launch overheads amortise)
+    wbig = (torch.randn((28672, 8192), generator=torch.Generator().manual_seed(5001)) * 0.02).numpy()
+    big = nn.BitLinear.new(wbig, None, 0.3, quantiser="absmean", device=dev.index)
+    bp, bs = big.packed_weights(), big.scales()
+    bigpool = [big] + [nn.BitLinear.from_packed(bp, bs, None, 8192, 28672, device=dev.index) for _ in range(3)]
+    del wbig
+    for nb in (1, 8):
+        xb = torch.from_numpy(gaussian(5002, (nb, 8192), 1.0)).to(dev)
+        yb = torch.empty((nb, 28672), dtype=torch.float32, device=dev)
+        xqb, sxb, smb = kernels.quantize_act_i8(xb)
+
+        def bigstep():
+            for lay in bigpool:
+                _cabi.check(lib.kb_linear_forward_q8(lay.handle, xqb.data_ptr(), xqb.stride(0), sxb.data_ptr(), smb.data_ptr(),
+                                                     nb, yb.data_ptr(), 0, None, _cabi.PATH_GEMV, sptr))
+
+        sec, _ = time_graph(torch, bigstep, steps, warm, stream)
+        gbs = len(bigpool) * gemv_bytes(28672, 8192, nb) / sec / 1e9
+        out[f"gemv_8192x28672_batch{nb}_chain_prequantised"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                                                                "us_per_layer": sec / len(bigpool) * 1e6}
+    del bigpool, big
 
     # quaternary twin of the headline layer, same pool scheme
     w = gaussian(2001, (M_DEC, K_DEC), 0.02)

@@ -144,6 +144,40 @@ static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim
     return rc;
 }
 
+// Per-thread device staging for the host-pointer entry point: grown on demand, reused by
+// later calls of the same thread, released when the thread ends.
+struct HostStaging {
+    int device = -1;
+    void *dx = nullptr, *dy = nullptr;
+    size_t dx_cap = 0, dy_cap = 0;
+    ~HostStaging() { release(); }
+    void release() {
+        if (dx) cudaFree(dx);
+        if (dy) cudaFree(dy);
+        dx = dy = nullptr;
+        dx_cap = dy_cap = 0;
+    }
+    int ensure(int dev, size_t xb, size_t yb) {
+        if (dev != device) { release(); device = dev; }
+        if (xb > dx_cap) {
+            if (dx) cudaFree(dx);
+            dx = nullptr; dx_cap = 0;
+            cudaError_t e = cudaMalloc(&dx, xb);
+            if (e != cudaSuccess) return cuda_fail(e, "activation staging");
+            dx_cap = xb;
+        }
+        if (yb > dy_cap) {
+            if (dy) cudaFree(dy);
+            dy = nullptr; dy_cap = 0;
+            cudaError_t e = cudaMalloc(&dy, yb);
+            if (e != cudaSuccess) return cuda_fail(e, "output staging");
+            dy_cap = yb;
+        }
+        return KB_OK;
+    }
+};
+static thread_local HostStaging g_staging;
+
 // x [n,k] host -> y [n,m] host, on this thread's private stream
 static int forward_host_impl(const Linear *L, const float *x, size_t n, size_t in_dim, float *y) {
     if (in_dim != L->k)
@@ -151,18 +185,15 @@ static int forward_host_impl(const Linear *L, const float *x, size_t n, size_t i
     if (!x || !y) return fail(KB_ERR_INVALID, "null activation or output pointer");
     if (n == 0) return KB_OK;
     cudaStream_t st = cudaStreamPerThread;
-    float *dx = nullptr, *dy = nullptr;
-    KB_CUDA(cudaMallocAsync(reinterpret_cast<void **>(&dx), n * L->k * sizeof(float), st));
-    cudaError_t e = cudaMallocAsync(reinterpret_cast<void **>(&dy), n * L->m * sizeof(float), st);
-    if (e != cudaSuccess) { cudaFreeAsync(dx, st); return cuda_fail(e, "output allocation"); }
-    int rc = KB_OK;
+    int rc = g_staging.ensure(L->device, n * L->k * sizeof(float), n * L->m * sizeof(float));
+    if (rc) return rc;
+    float *dx = static_cast<float *>(g_staging.dx), *dy = static_cast<float *>(g_staging.dy);
+    cudaError_t e;
     if ((e = cudaMemcpyAsync(dx, x, n * L->k * sizeof(float), cudaMemcpyHostToDevice, st)) != cudaSuccess)
         rc = cuda_fail(e, "activation upload");
     if (rc == KB_OK) rc = forward_impl(L, dx, n, in_dim, dy, 0, nullptr, KB_PATH_AUTO, nullptr, 0, st);
     if (rc == KB_OK && (e = cudaMemcpyAsync(y, dy, n * L->m * sizeof(float), cudaMemcpyDeviceToHost, st)) != cudaSuccess)
         rc = cuda_fail(e, "output download");
-    cudaFreeAsync(dx, st);
-    cudaFreeAsync(dy, st);
     e = cudaStreamSynchronize(st);
     if (rc == KB_OK && e != cudaSuccess) rc = cuda_fail(e, "stream synchronize");
     return rc;

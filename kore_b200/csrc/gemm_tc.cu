@@ -370,18 +370,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 }
                 const int valid = p.n - (n0 + c * 32);  // columns of this chunk that are real tokens
                 const size_t cbase = (size_t)(c * 32) * p.ldy;
+                float outv[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const float sx_i = __shfl_sync(0xffffffffu, sx_cur, i);
                     const int sm_i = __shfl_sync(0xffffffffu, sm_cur, i);
                     const int a = p.mul * (int)v[i] - p.off * sm_i;
-                    const float out = dequant_out(a, sw, sx_i, bias, has_bias);
-                    if (row_ok && i < valid) {
-                        const size_t o = cbase + (size_t)i * p.ldy;
-                        if (arow) arow[o] = a;
-                        if (yrow) {
-                            yrow[o] = out;
-                            for (int q = 0; q < p.n_more; ++q) p.y_more[q][yoff + o] = out;  // peer copies over NVLink
+                    outv[i] = dequant_out(a, sw, sx_i, bias, has_bias);
+                    v[i] = (uint32_t)a;
+                }
+                if (row_ok) {
+                    if (arow) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (i < valid) arow[cbase + (size_t)i * p.ldy] = (int)v[i];
+                    }
+                    if (yrow) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (i < valid) yrow[cbase + (size_t)i * p.ldy] = outv[i];
+                        // column-sharded layers: the same values into every peer's copy (NVLink stores)
+                        for (int q = 0; q < p.n_more; ++q) {
+                            float *peer = p.y_more[q] + yoff + cbase;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < valid) peer[(size_t)i * p.ldy] = outv[i];
                         }
                     }
                 }

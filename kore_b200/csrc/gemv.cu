@@ -346,10 +346,17 @@ static int launch_one(const GemvParams &p, int tok_groups, cudaStream_t stream) 
     }
     // persistent grid: at most one resident wave (SMs x CTAs per SM), rows are grid-strided,
     // so there is no partial last wave and activations are staged once per CTA
-    int occ = 0, dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, smem) != cudaSuccess || occ < 1) occ = 1;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+    // (occupancy and SM count are looked up once per kernel instance, CTA size and smem size)
+    static thread_local int c_threads = 0, c_occ = 0, c_sms = 0;
+    static thread_local size_t c_smem = ~(size_t)0;
+    if (c_threads != threads || c_smem != smem) {
+        int occ_q = 0, dev = 0, sms_q = 148;
+        cudaGetDevice(&dev);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_q, kern, threads, smem) != cudaSuccess || occ_q < 1) occ_q = 1;
+        if (cudaDeviceGetAttribute(&sms_q, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms_q < 1) sms_q = 148;
+        c_threads = threads; c_smem = smem; c_occ = occ_q; c_sms = sms_q;
+    }
+    const int occ = c_occ, sms = c_sms;
     int ctas = (row_groups + nwarps - 1) / nwarps;
     if (ctas > sms * occ) ctas = sms * occ;
     cudaLaunchConfig_t cfg = {};
