@@ -222,6 +222,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill / quaternary / batch side measurements")
     ap.add_argument("--pool", type=int, default=POOL)
     ap.add_argument("--streams", type=int, default=STREAMS)
+    ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "prefill_up", "prefill_down"],
+                    help="run one small case and print its own JSON line (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -240,11 +242,15 @@ def main():
     dev = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout (one JSON line only)
         import torch.distributed as dist_
 
         dist = dist_
         dist.init_process_group("nccl", device_id=dev)
     lib = _cabi.lib()
+    if args.only:
+        return single_case(torch, lib, _cabi, nn, kernels, dev, args)
     pool_n = args.pool + (args.pool & 1)  # even: the sharded double buffering repeats per replay
     peaks = measured_peaks()
 
@@ -285,21 +291,31 @@ def main():
     else:
         from kore_b200 import sharded
 
-        n_streams = 1
-        ctx = sharded.ShardContext(rank, world, m_total, 8, local_rank, dist)
-        sp = main_stream.cuda_stream
-        last_par = [0]
+        # one exchange context (output buffers + flags) per stream, so that independent layers
+        # overlap their exchange latency exactly as the single-GPU step overlaps launches
+        n_streams = max(1, min(args.streams, 8))
+        while pool_n % (2 * n_streams):
+            n_streams -= 1
+        fan = StreamFan(torch, main_stream, n_streams)
+        ctxs = [sharded.ShardContext(rank, world, m_total, 8, local_rank, dist) for _ in fan.side]
+        ctx = ctxs[0]
+        last = [0, 0]
 
         def step():
-            for lay in pool:
-                par = ctx.next_parity()
-                last_par[0] = par
-                _cabi.check(lib.kb_linear_forward_sharded(lay.handle, x_dev.data_ptr(), 1, K_DEC, ctx.y_tables_host[par],
-                                                          world, rank, m_total, rank * M_DEC, _cabi.PATH_GEMV, None, 0, sp))
-                ctx.barrier(sp)
+            fan.fork()
+            for j, lay in enumerate(pool):
+                i = j % len(fan.side)
+                c = ctxs[i]
+                par = c.next_parity()
+                last[0], last[1] = i, par
+                _cabi.check(lib.kb_linear_forward_sharded(lay.handle, x_dev.data_ptr(), 1, K_DEC, c.y_tables_host[par],
+                                                          world, rank, m_total, rank * M_DEC, _cabi.PATH_GEMV, None, 0,
+                                                          c.flag_table.data_ptr(), c.sync_words.data_ptr(),
+                                                          fan.side[i].cuda_stream))
+            fan.join()
 
-        launches_per_step = 2 * pool_n
-        y_view = lambda: ctx.local_y[last_par[0]][0, rank * M_DEC:(rank + 1) * M_DEC]
+        launches_per_step = pool_n
+        y_view = lambda: ctxs[last[0]].local_y[last[1]][0, rank * M_DEC:(rank + 1) * M_DEC]
 
     if dist is not None:
         dist.barrier()
@@ -311,7 +327,8 @@ def main():
         t = torch.tensor([sec_per_step], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         sec_per_step = float(t.item())
-        ctx.check_status()
+        for c in ctxs:
+            c.check_status()
     step_bytes = pool_n * gemv_bytes(M_DEC, K_DEC, 1) * world
     value = step_bytes / sec_per_step / 1e9
     y_chk = y_view().cpu().numpy().copy()  # what the timed path produced for the last layer
@@ -343,10 +360,18 @@ def main():
            "note": "kb_linear_forward_host per layer: pinned x -> device, quantiser + GEMV, y -> host, synchronise"}
     assert (y_host[0] == y_chk).all(), "host entry point and graph replay disagree"
 
+    sharded_extra = None
+    if world > 1 and not args.no_extras:
+        try:
+            sharded_extra = sharded_projection(torch, lib, _cabi, nn, dist, dev, main_stream, rank, world, peaks)
+        except Exception as exc:
+            sharded_extra = {"error": repr(exc)}
+
     if rank != 0:
         if dist is not None:
             dist.barrier()
-            ctx.close()
+            for c in ctxs:
+                c.close()
             dist.destroy_process_group()
         return
 
@@ -385,13 +410,114 @@ def main():
     }
     if cpu is not None:
         line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if sharded_extra:
+        extras["sharded_projection_8192_to_28672"] = sharded_extra
     if extras:
         line["extra"] = extras
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
-        ctx.close()
+        for c in ctxs:
+            c.close()
         dist.destroy_process_group()
+
+
+def single_case(torch, lib, _cabi, nn, kernels, dev, args):
+    """One kernel on one small case, a handful of eager launches: the command profiled with ncu."""
+    shapes = {"gemv_big": (28672, 8192, 1, 3), "gemv_4096": (4096, 4096, 1, 40),
+              "prefill_up": (11008, 4096, 2048, 1), "prefill_down": (4096, 11008, 2048, 1)}
+    m, k, n, copies = shapes[args.only]
+    w = (torch.randn((m, k), generator=torch.Generator().manual_seed(7)) * 0.02).numpy()
+    first = nn.BitLinear.new(w, None, 0.3, quantiser="absmean", device=dev.index)
+    del w
+    pk, sc = first.packed_weights(), first.scales()
+    layers = [first] + [nn.BitLinear.from_packed(pk, sc, None, k, m, device=dev.index) for _ in range(copies - 1)]
+    x = torch.from_numpy(gaussian(8, (n, k), 1.0)).to(dev)
+    y = torch.empty((n, m), dtype=torch.float32, device=dev)
+    xq, sx, sumq = kernels.quantize_act_i8(x)
+    path = _cabi.PATH_GEMV if n == 1 else _cabi.PATH_GEMM_TC
+    sp = torch.cuda.current_stream().cuda_stream
+
+    def once():
+        for lay in layers:
+            _cabi.check(lib.kb_linear_forward_q8(lay.handle, xq.data_ptr(), xq.stride(0), sx.data_ptr(), sumq.data_ptr(), n,
+                                                 y.data_ptr(), 0, None, path, sp))
+
+    for _ in range(max(1, args.warmup)):
+        once()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        once()
+    e1.record()
+    torch.cuda.synchronize()
+    per = e0.elapsed_time(e1) / 1e3 / (args.steps * copies)
+    print(json.dumps({"case": args.only, "m": m, "k": k, "n": n, "copies": copies, "us_per_launch": per * 1e6,
+                      "GB/s": gemv_bytes(m, k, n) / per / 1e9, "TOPS": 2.0 * m * k * n / per / 1e12}), flush=True)
+
+
+def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, peaks):
+    """BASELINE.json configs[4]: ternary K=8192 x M=28672 split by output features over the
+    ranks (strong scaling: the layer is fixed), batch 1 / 8 / 64 / 512, every rank ends with
+    the full y.  Exchange: epilogue peer stores + flag barrier, and NCCL all-gather beside it.
+    A pool of separately allocated copies of the shard (> L2 in total) is cycled."""
+    from kore_b200 import sharded
+
+    m, k = 28672, 8192
+    w = (torch.randn((m, k), generator=torch.Generator().manual_seed(5001)) * 0.02).numpy()
+    full = nn.BitLinear.new(w, None, 0.3, quantiser="absmean", device=dev.index)  # scale from the full tensor
+    del w
+    packed, scales = full.packed_weights(), full.scales()
+    full.close()
+    shard_bytes = (m // world) * k // 4
+    copies = max(2, int(160e6 // shard_bytes) + 1)
+    copies += copies & 1
+    ctx = sharded.ShardContext(rank, world, m, 512, dev.index, dist)
+    layers = [sharded.ShardedLinear(0, packed, scales, None, k, m, rank, world, device=dev.index, ctx=ctx, dist=dist,
+                                    exchange="p2p") for _ in range(copies)]
+    sp = stream.cuda_stream
+    out = {"world": world, "shard_copies": copies}
+    for nb in (1, 8, 64, 512):
+        x = torch.from_numpy(gaussian(5002, (nb, k), 1.0)).to(dev)
+
+        def step_p2p():
+            for lay in layers:
+                lay.forward(x, stream_ptr=sp)
+
+        sec, _ = time_graph(torch, step_p2p, 5, 3, stream)
+        t = torch.tensor([sec / copies], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        per = float(t.item())
+        entry = {"us_per_forward_p2p": per * 1e6, "GB/s": gemv_bytes(m, k, nb) / per / 1e9,
+                 "TOPS": 2.0 * nb * m * k / per / 1e12}
+        # NCCL all-gather variant (eager launches; collectives are not captured here)
+        for lay in layers:
+            lay.exchange = "collective"
+        torch.cuda.synchronize()
+        dist.barrier()
+        with torch.cuda.stream(stream):
+            for lay in layers[:2]:
+                lay.forward(x, stream_ptr=sp)
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(3):
+                for lay in layers:
+                    lay.forward(x, stream_ptr=sp)
+            e1.record(stream)
+            stream.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / 1e3 / (3 * copies)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        entry["us_per_forward_nccl_allgather"] = float(t.item()) * 1e6
+        for lay in layers:
+            lay.exchange = "p2p"
+        out[f"batch{nb}"] = entry
+    ctx.check_status()
+    for lay in layers:
+        lay.layer.close()
+    ctx.close()
+    return out
 
 
 def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, pool, x_dev):

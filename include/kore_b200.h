@@ -189,12 +189,16 @@ int kb_pack_weights_quaternary(const float *w, size_t m, size_t k, uint8_t *pack
  * layer with m_total output features.  y_bases[q] is rank q's full output buffer
  * [N, m_total] f32 as seen from this process: y_bases[rank] is local, the others are
  * peer mappings obtained with kb_ipc_open.  The kernel epilogue stores this rank's
- * slice into all of them (peer stores over NVLink); kb_peer_barrier then publishes
- * completion to the peers and waits (bounded, about a second) for theirs. */
+ * slice into all of them (peer stores over NVLink).  When flag_arrays_dev and
+ * sync_words_dev (three local int32, zero-initialised: epoch, CTA counter, status) are
+ * given, completion is published to the peers and theirs awaited (bounded, about a
+ * second): inside the tail of the GEMV kernel, or by kb_peer_barrier after the GEMM.
+ * With both NULL the caller runs kb_peer_barrier (or any other barrier) itself. */
 int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size_t in_dim,
                               float *const *y_bases, int world, int rank, size_t m_total,
                               size_t col_offset, int path, void *workspace,
-                              size_t workspace_bytes, kb_stream stream);
+                              size_t workspace_bytes, int *const *flag_arrays_dev,
+                              int *sync_words_dev, kb_stream stream);
 /* flag_arrays_dev: device array of `world` pointers, entry q = rank q's int32[world]
  * flag array (local or peer mapping); epoch_counter_dev: one local int32, starts at 0 and
  * is bumped by every barrier (all ranks must issue the same sequence of barriers);

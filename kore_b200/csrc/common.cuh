@@ -77,6 +77,15 @@ int launch_dequantize(int kind, const uint8_t *w2, size_t row_bytes, const float
                       size_t k, float *w, cudaStream_t stream);
 int launch_transpose_f32(const float *src, size_t rows, size_t cols, float *dst, cudaStream_t stream);
 
+// State of the flag barrier between the ranks of a sharded layer (all device pointers).
+struct PeerSync {
+    int *const *flag_arrays;  // [world] -> each rank's int32[world] flag array (local or peer mapping)
+    int *epoch_counter;       // local, bumped once per barrier
+    int *done_counter;        // local, CTAs finished in the current launch (returns to 0)
+    int *status;              // local, 100+q if rank q never arrived
+    int world, rank;
+};
+
 struct FwdArgs {
     const Linear *lin;
     // exactly one of (x) or (xq, sx, sumq) is set
@@ -93,6 +102,8 @@ struct FwdArgs {
     // copies of the full output, mapped into this process) at the same offsets as in y
     float *y_more[MAX_PEERS - 1];
     int n_more;
+    // optional cross-GPU completion barrier fused into the tail of the kernel (GEMV only)
+    const struct PeerSync *sync;
 };
 // decode GEMV; when args.x is set the activation quantiser is fused into its prologue
 int launch_gemv(const FwdArgs &a, cudaStream_t stream);

@@ -50,6 +50,7 @@ struct GemvParams {
     int x_vec4;
     float *y_more[MAX_PEERS - 1];  // further copies of y (peer GPUs), same offsets
     int n_more;
+    PeerSync sync;  // sync.world == 0: no fused barrier
 };
 
 // 16-element group g (k = 16*g .. 16*g+15) <-> shared-memory slot: inside each
@@ -296,7 +297,6 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
                                 const float v = dequant_out(a, my_sw, s_sx[t], my_bias, p.bias != nullptr);
                                 p.y[o] = v;
                                 for (int q = 0; q < p.n_more; ++q) p.y_more[q][o] = v;  // peer copies over NVLink
-                                if (p.n_more) __threadfence_system();
                             }
                         }
                     }
@@ -308,6 +308,41 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
         }
     }
     TL_MARK(4);
+
+    // ---- sharded layers: publish this rank's slice and wait for the peers' ----
+    // Every CTA orders its peer stores at system scope; the last CTA of the launch to get
+    // here bumps the epoch, writes it into slot [rank] of every rank's flag array and waits,
+    // bounded (about a second), until all slots of the local array have reached it.
+    if (p.sync.world > 0) {
+        __shared__ int s_last, s_epoch;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();  // this CTA's peer stores are performed before it is counted
+            const int total = gridDim.x * gridDim.y;
+            const int ticket = atomicAdd(p.sync.done_counter, 1);
+            s_last = (ticket == total - 1);
+            if (s_last) {
+                __threadfence_system();  // cumulative: orders every counted CTA's stores before the flags
+                *p.sync.done_counter = 0;
+                s_epoch = ++(*p.sync.epoch_counter);
+            }
+        }
+        __syncthreads();
+        if (s_last && (int)threadIdx.x < p.sync.world) {
+            const int j = threadIdx.x, epoch = s_epoch;
+            volatile int *remote = p.sync.flag_arrays[j] + p.sync.rank;
+            *remote = epoch;
+            const volatile int *mine = p.sync.flag_arrays[p.sync.rank] + j;
+            const long long t0 = clock64();
+            bool ok = false;
+            for (;;) {
+                if (*mine - epoch >= 0) { ok = true; break; }
+                if (clock64() - t0 > 2000000000ll) break;
+            }
+            __threadfence_system();  // acquire side: later reads of the peers' slices see their data
+            if (!ok) atomicCAS(p.sync.status, 0, 100 + j);
+        }
+    }
 }
 
 #ifdef KB_TIMELINE
@@ -400,6 +435,8 @@ int launch_gemv(const FwdArgs &a, cudaStream_t stream) {
     p.x = a.x; p.xq = a.xq; p.ldq = a.ldq; p.sx = a.sx; p.sumq = a.sumq;
     p.n = (int)a.n; p.y = a.y; p.acc = a.acc; p.ldy = a.ldy ? a.ldy : L->m;
     p.mul = L->mul; p.off = L->off;
+    p.sync = PeerSync{};
+    if (a.sync && a.y) p.sync = *a.sync;
     p.n_more = a.y ? a.n_more : 0;
     for (int q = 0; q < MAX_PEERS - 1; ++q) p.y_more[q] = q < p.n_more ? a.y_more[q] : nullptr;
     p.x_vec4 = a.x && (L->k % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);

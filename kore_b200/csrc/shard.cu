@@ -19,7 +19,7 @@ namespace kb {
 // Every rank runs one CTA.  The epoch is a device-side counter bumped by each barrier, so
 // the same captured launch can be replayed from a CUDA graph (all ranks run the same
 // sequence of barriers, hence agree on the epoch).  Thread j < world publishes the epoch
-// into slot [rank] of rank j's flag array (system-scope release; the slice stores of the
+// into slot [rank] of rank j's flag array (after a system-scope fence; the slice stores of the
 // preceding kernel on this stream are complete before this kernel starts), then waits,
 // bounded, until slot [j] of the local flag array has reached it.
 __global__ void peer_barrier_kernel(int *const *flag_arrays, int world, int rank, int *epoch_counter,
@@ -30,18 +30,17 @@ __global__ void peer_barrier_kernel(int *const *flag_arrays, int world, int rank
     const int epoch = s_epoch;
     const int j = threadIdx.x;
     if (j < world) {
-        __threadfence_system();
-        int *remote = flag_arrays[j] + rank;
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
-        const int *mine = flag_arrays[rank] + j;
+        __threadfence_system();  // release: everything this stream wrote before is performed first
+        volatile int *remote = flag_arrays[j] + rank;
+        *remote = epoch;
+        const volatile int *mine = flag_arrays[rank] + j;
         const long long t0 = clock64();
         bool ok = false;
         for (;;) {
-            int v;
-            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-            if (v - epoch >= 0) { ok = true; break; }
+            if (*mine - epoch >= 0) { ok = true; break; }
             if (clock64() - t0 > max_cycles) break;
         }
+        __threadfence_system();  // acquire: later reads of the peers' slices see their data
         if (!ok) atomicCAS(status, 0, 100 + j);  // peer j never arrived
     }
 }
@@ -105,7 +104,8 @@ int kb_peer_barrier(int *const *flag_arrays_dev, int world, int rank, int *epoch
 
 int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *const *y_bases,
                               int world, int rank, size_t m_total, size_t col_offset, int path, void *workspace,
-                              size_t workspace_bytes, kb_stream stream) {
+                              size_t workspace_bytes, int *const *flag_arrays_dev, int *sync_words_dev,
+                              kb_stream stream) {
     const Linear *L = reinterpret_cast<const Linear *>(h);
     if (!L || L->magic != HANDLE_MAGIC) return fail(KB_ERR_BAD_HANDLE, "null or destroyed kb_linear handle");
     if (!y_bases || !x) return fail(KB_ERR_INVALID, "null pointer");
@@ -132,8 +132,13 @@ int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size
         if (q != rank) a.y_more[a.n_more++] = y_bases[q] + col_offset;
     if (path == KB_PATH_AUTO) path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : KB_PATH_GEMM_TC;
     int rc;
+    // sync_words_dev = {epoch counter, CTA-done counter, status}
+    PeerSync sync = {flag_arrays_dev, sync_words_dev, sync_words_dev ? sync_words_dev + 1 : nullptr,
+                     sync_words_dev ? sync_words_dev + 2 : nullptr, world, rank};
+    const bool want_sync = flag_arrays_dev && sync_words_dev;
     if (path == KB_PATH_GEMV) {
         a.x = x;
+        a.sync = want_sync ? &sync : nullptr;  // barrier fused into the kernel's tail
         rc = launch_gemv(a, st);
     } else {
         const size_t xq_bytes = (n * L->kp + 255) / 256 * 256, vec_bytes = (n * 4 + 255) / 256 * 256;
@@ -159,6 +164,8 @@ int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size
             }
             if (own) cudaFreeAsync(ws, st);
         }
+        if (rc == KB_OK && want_sync)
+            rc = kb_peer_barrier(flag_arrays_dev, world, rank, sync_words_dev, sync_words_dev + 2, stream);
     }
     if (prev != L->device) cudaSetDevice(prev);
     return rc;

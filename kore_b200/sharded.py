@@ -119,8 +119,10 @@ class ShardContext:
         self.y_tables = [torch.tensor(t, dtype=torch.int64, device=dev) for t in ybases]
         self.y_tables_host = [(C.c_void_p * world)(*t) for t in ybases]
         self.flag_table = torch.tensor([b + 2 * self.y_bytes for b in self.peer_bases], dtype=torch.int64, device=dev)
-        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.epoch_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        # {epoch counter, CTA-done counter, status}
+        self.sync_words = torch.zeros(3, dtype=torch.int32, device=dev)
+        self.epoch_counter = self.sync_words[0:1]
+        self.status = self.sync_words[2:3]
         self.local_y = [torch.as_tensor(_DevView(self.local_base + par * self.y_bytes, (max_tokens, m_total), "<f4"),
                                         device=dev) for par in range(2)]
         dist.barrier()
@@ -197,8 +199,8 @@ class ShardedLinear:
             par = ctx.next_parity()
             _cabi.check(ctx.lib.kb_linear_forward_sharded(
                 self.layer.handle, x.data_ptr(), n, x.shape[1], ctx.y_tables_host[par], self.world, self.rank,
-                self.m_total, self.start, path, None, 0, stream_ptr))
-            ctx.barrier(stream_ptr)
+                self.m_total, self.start, path, None, 0, ctx.flag_table.data_ptr(), ctx.sync_words.data_ptr(),
+                stream_ptr))
             return ctx.local_y[par][:n]
         # collective: equal-sized staging blocks, NCCL all-gather, then [g, N, s] -> [N, M]
         smax = max(s for _, s in self.parts)
