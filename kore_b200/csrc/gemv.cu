@@ -403,7 +403,9 @@ static int launch_one(const GemvParams &p, int tok_groups, cudaStream_t stream) 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = env_pdl ? 1 : 0;
+    // no early launch for kernels that end in a cross-GPU wait: a dependent grid parked at its
+    // dependency wait would hold its CTAs resident for the whole exchange latency
+    cfg.numAttrs = (env_pdl && p.sync.world == 0) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "gemv launch");
 }
