@@ -134,6 +134,38 @@ int kb_linear_forward_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const
                          const int32_t *sumq, size_t n, float *y, size_t ldy, int32_t *acc,
                          int path, kb_stream stream);
 
+/* Forward for a decoder step: input either f32 x [N,K] or pre-quantised (xq, sx, sumq),
+ * and an optional residual resid [N,ldy] (may be y itself) added after the bias:
+ * y = ((float(acc) * w_scale) * s + bias) + resid.  Stands in for the project() +
+ * residual_add() pairs of the reference's decoder loop
+ * (crates/kore-edge/src/runtime.rs:197-212,254-265).  With f32 input and the GEMM path a
+ * caller workspace (kb_linear_workspace_bytes) is required; nothing is allocated here. */
+int kb_linear_forward_fused(const kb_linear *h, const float *x, const int8_t *xq, size_t ldq,
+                            const float *sx, const int32_t *sumq, size_t n, const float *resid,
+                            float *y, size_t ldy, int path, void *workspace,
+                            size_t workspace_bytes, kb_stream stream);
+
+/* ---- glue kernels of the decoder step; each ends in the per-token int8 quantiser so the
+ * next projection reads codes.  Device pointers.  xn / h receive the f32 values when
+ * not NULL; xq may be NULL to get only the f32 result. ---- */
+/* RMSNorm (crates/kore-kernels/src/cpu_fused.rs:160-190): (x * (1/sqrt(mean(x^2)+eps))) * gamma */
+int kb_rmsnorm_quant(const float *x, const float *gamma, size_t n, size_t d, float eps, float *xn,
+                     int8_t *xq, size_t ldq, float *sx, int32_t *sumq, kb_stream stream);
+/* SwiGLU (crates/kore-edge/src/runtime.rs:232-252, ops/activation.rs:21-26): rows of
+ * gate_up are [gate(f) | up(f)] with row stride ld; h = (g / (1 + exp(-g))) * u */
+int kb_swiglu_quant(const float *gate_up, size_t n, size_t f, size_t ld, float *h, int8_t *xq,
+                    size_t ldq, float *sx, int32_t *sumq, kb_stream stream);
+/* Half-split RoPE (crates/kore-edge/src/ops/rope.rs:9-36) on the q and k parts of rows
+ * [q|k|v] with cos/sin tables [max_pos][head_dim/2]; k and v go to row cache_rows[t] of
+ * caches laid out [rows][n_heads*head_dim]. */
+int kb_rope_kv(const float *qkv, const int *positions, const long long *cache_rows,
+               const float *cos_table, const float *sin_table, size_t n, int n_heads, int head_dim,
+               float *q_out, float *k_cache, float *v_cache, kb_stream stream);
+/* One query token per sequence against its cache [batch][lmax][n_heads*head_dim]
+ * (crates/kore-edge/src/ops/attention.rs:74-135); lens[b] counts the current token. */
+int kb_attn_decode(const float *q, const float *k_cache, const float *v_cache, const int *lens,
+                   size_t batch, int n_heads, int head_dim, int lmax, float *out, kb_stream stream);
+
 /* ---- forward (host pointers; what a Tensor-in/Tensor-out caller uses) ---- */
 
 /* Copies x to the device, runs kb_linear_forward, copies y back, synchronises.

@@ -38,6 +38,11 @@ SIGNATURES = {
     "kb_linear_forward_ex": (C.c_int, [_vp, _vp, _sz, _sz, _vp, _sz, _vp, C.c_int, _vp, _sz, _vp]),
     "kb_linear_workspace_bytes": (_sz, [_vp, _sz]),
     "kb_linear_forward_q8": (C.c_int, [_vp, _vp, _sz, _vp, _vp, _sz, _vp, _sz, _vp, C.c_int, _vp]),
+    "kb_linear_forward_fused": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, _sz, _vp, _vp, _sz, C.c_int, _vp, _sz, _vp]),
+    "kb_rmsnorm_quant": (C.c_int, [_vp, _vp, _sz, _sz, C.c_float, _vp, _vp, _sz, _vp, _vp, _vp]),
+    "kb_swiglu_quant": (C.c_int, [_vp, _sz, _sz, _sz, _vp, _vp, _sz, _vp, _vp, _vp]),
+    "kb_rope_kv": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
+    "kb_attn_decode": (C.c_int, [_vp, _vp, _vp, _vp, _sz, C.c_int, C.c_int, C.c_int, _vp, _vp]),
     "kb_linear_forward_host": (C.c_int, [_vp, _vp, _sz, _sz, _vp]),
     "kb_linear_forward_static": (C.c_int, [_vp, _vp, _sz, _sz, _vp, _vp]),
     "kb_static_scratch_bytes": (_sz, []),

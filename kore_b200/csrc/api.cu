@@ -446,6 +446,44 @@ int kb_linear_forward_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const
     return fail(KB_ERR_INVALID, "unknown path %d", path);
 }
 
+int kb_linear_forward_fused(const kb_linear *h, const float *x, const int8_t *xq, size_t ldq, const float *sx,
+                            const int32_t *sumq, size_t n, const float *resid, float *y, size_t ldy, int path,
+                            void *workspace, size_t workspace_bytes_, kb_stream stream) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    if (!y || (!x && !(xq && sx && sumq))) return fail(KB_ERR_INVALID, "null pointer");
+    if (ldy != 0 && ldy < L->m) return fail(KB_ERR_INVALID, "ldy %zu smaller than out_features %zu", ldy, L->m);
+    if (n == 0) return KB_OK;
+    DeviceGuard g(L->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (path == KB_PATH_AUTO) path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : KB_PATH_GEMM_TC;
+    FwdArgs a = {};
+    a.lin = L; a.n = n; a.y = y; a.ldy = ldy; a.resid = resid;
+    if (xq) {
+        a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq;
+        if (path == KB_PATH_GEMV) return launch_gemv(a, st);
+        if (path == KB_PATH_GEMM_TC) return launch_gemm_tc(a, st);
+        return fail(KB_ERR_INVALID, "unknown path %d", path);
+    }
+    if (path == KB_PATH_GEMV) {
+        a.x = x;
+        return launch_gemv(a, st);
+    }
+    if (path != KB_PATH_GEMM_TC) return fail(KB_ERR_INVALID, "unknown path %d", path);
+    const size_t need = workspace_bytes(L, n);
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    if (!ws || workspace_bytes_ < need || (reinterpret_cast<uintptr_t>(ws) & 255))
+        return fail(KB_ERR_STORAGE, "workspace too small or misaligned: need %zu bytes (256-byte aligned), got %zu", need,
+                    workspace_bytes_);
+    int8_t *wq = reinterpret_cast<int8_t *>(ws);
+    float *wsx = reinterpret_cast<float *>(ws + round_up(n * L->kp, 256));
+    int32_t *wsum = reinterpret_cast<int32_t *>(ws + round_up(n * L->kp, 256) + round_up(n * 4, 256));
+    int rc = launch_act_quant(x, n, L->k, wq, L->kp, wsx, wsum, st);
+    if (rc) return rc;
+    a.xq = wq; a.ldq = L->kp; a.sx = wsx; a.sumq = wsum;
+    return launch_gemm_tc(a, st);
+}
+
 int kb_linear_forward_host(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *y) {
     const Linear *L = check(h);
     if (!L) return KB_ERR_BAD_HANDLE;

@@ -104,6 +104,8 @@ struct FwdArgs {
     int n_more;
     // optional cross-GPU completion barrier fused into the tail of the kernel (GEMV only)
     const struct PeerSync *sync;
+    // optional residual, same [N][ldy] layout as y (may be y itself): y = dequant(...) + resid
+    const float *resid;
 };
 // decode GEMV; when args.x is set the activation quantiser is fused into its prologue
 int launch_gemv(const FwdArgs &a, cudaStream_t stream);

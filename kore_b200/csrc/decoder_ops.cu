@@ -1,0 +1,250 @@
+// Glue kernels of the decoder step around the quantized-linear path (sm_100a).
+//
+// Each of them ends in the per-token int8 quantiser, so the following projection reads
+// codes instead of f32 activations and no separate quantiser launch is needed:
+//   rmsnorm_quant   y = (x * (1 / sqrt(mean(x^2) + eps))) * gamma            -> int8
+//                   (KORE: crates/kore-kernels/src/cpu_fused.rs:160-190,
+//                    cuda/kernels/rms_norm.cu:17)
+//   swiglu_quant    h = (g / (1 + exp(-g))) * u, g|u = the two halves of a row -> int8
+//                   (crates/kore-edge/src/ops/activation.rs:21-26, runtime.rs:232-265)
+//   rope_kv         half-split rotary embedding of q and k from a [q|k|v] row with
+//                   host-supplied cos/sin tables, k and v appended to the cache
+//                   (crates/kore-edge/src/ops/rope.rs:9-36)
+//   attn_decode     one query token per sequence against its KV cache, softmax in f32
+//                   (crates/kore-edge/src/ops/attention.rs:74-135, causal rule of
+//                    crates/kore-serve/src/layered/engine.rs:734-751)
+// All are HBM/latency-bound elementwise or row-reduction work, one CTA per token (or per
+// sequence-head); none is reshaped into a GEMM.
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace kb {
+
+__device__ __forceinline__ float block_reduce_sum_f(float v, float *scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = lane < nwarps ? scratch[lane] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    return r;
+}
+
+// quantise `vals` (this thread's elements idx = threadIdx.x + i*blockDim.x, i < CNT) of one row
+template <int CNT>
+__device__ __forceinline__ void quantise_row_from_regs(const float (&vals)[CNT], int d, int ldq, int8_t *qrow,
+                                                       float *sx_out, int32_t *sum_out, float *red_f, int *red_i) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) amax = fmaxf(amax, fabsf(vals[i]));
+    amax = block_reduce_max(amax, red_f);
+    const float s = amax < 1e-8f ? 1.0f : __fdiv_rn(amax, 127.0f);
+    const float rs = __frcp_rn(s);
+    int local = 0;
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < ldq) {
+            const int q = idx < d ? quantise_one_fast(vals[i], s, rs) : 0;
+            local += q;
+            qrow[idx] = (int8_t)q;
+        }
+    }
+    local = block_reduce_sum(local, red_i);
+    if (threadIdx.x == 0) {
+        *sx_out = s;
+        if (sum_out) *sum_out = local;
+    }
+}
+
+constexpr int ROW_REGS = 36;  // elements per thread held in registers: rows up to 36 * 256 = 9216
+
+__global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
+                                                            int d, float eps, float *__restrict__ xn,
+                                                            int8_t *__restrict__ xq, int ldq, float *__restrict__ sx,
+                                                            int32_t *__restrict__ sumq) {
+    __shared__ float red_f[32];
+    __shared__ int red_i[32];
+    const size_t t = blockIdx.x;
+    const float *row = x + t * (size_t)d;
+    float v[ROW_REGS];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ROW_REGS; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        v[i] = idx < d ? row[idx] : 0.0f;
+        ss = __fadd_rn(ss, __fmul_rn(v[i], v[i]));
+    }
+    ss = block_reduce_sum_f(ss, red_f);
+    const float rms = sqrtf(__fadd_rn(__fdiv_rn(ss, (float)d), eps));
+    const float inv = __fdiv_rn(1.0f, rms);
+#pragma unroll
+    for (int i = 0; i < ROW_REGS; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < d) {
+            v[i] = __fmul_rn(__fmul_rn(v[i], inv), gamma[idx]);
+            if (xn) xn[t * (size_t)d + idx] = v[i];
+        } else {
+            v[i] = 0.0f;
+        }
+    }
+    if (xq) quantise_row_from_regs<ROW_REGS>(v, d, ldq, xq + t * (size_t)ldq, sx + t, sumq ? sumq + t : nullptr, red_f, red_i);
+}
+
+__global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restrict__ gu, int f, size_t ld,
+                                                           float *__restrict__ h_out, int8_t *__restrict__ xq, int ldq,
+                                                           float *__restrict__ sx, int32_t *__restrict__ sumq) {
+    __shared__ float red_f[32];
+    __shared__ int red_i[32];
+    const size_t t = blockIdx.x;
+    const float *g = gu + t * ld, *u = g + f;
+    float v[ROW_REGS];
+#pragma unroll
+    for (int i = 0; i < ROW_REGS; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < f) {
+            const float gv = g[idx];
+            const float silu = __fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv)));
+            v[i] = __fmul_rn(silu, u[idx]);
+            if (h_out) h_out[t * (size_t)f + idx] = v[i];
+        } else {
+            v[i] = 0.0f;
+        }
+    }
+    if (xq) quantise_row_from_regs<ROW_REGS>(v, f, ldq, xq + t * (size_t)ldq, sx + t, sumq ? sumq + t : nullptr, red_f, red_i);
+}
+
+// one CTA per token: rotate q and k (pairs i, i + hd/2 inside each head), write q to q_out and
+// k, v to row cache_rows[t] of the caches.  cos/sin tables are [max_pos][hd/2].
+__global__ void __launch_bounds__(256) rope_kv_kernel(const float *__restrict__ qkv, const int *__restrict__ positions,
+                                                      const long long *__restrict__ cache_rows,
+                                                      const float *__restrict__ cos_t, const float *__restrict__ sin_t,
+                                                      int n_heads, int hd, float *__restrict__ q_out,
+                                                      float *__restrict__ k_cache, float *__restrict__ v_cache) {
+    const size_t t = blockIdx.x;
+    const int d = n_heads * hd, half = hd / 2;
+    const float *q = qkv + t * (size_t)(3 * d), *k = q + d, *v = k + d;
+    const int pos = positions[t];
+    const size_t crow = (size_t)cache_rows[t] * d;
+    for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx - h * half;
+        const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+        const int a = h * hd + i, b = a + half;
+        const float q0 = q[a], q1 = q[b], k0 = k[a], k1 = k[b];
+        q_out[t * (size_t)d + a] = __fsub_rn(__fmul_rn(q0, c), __fmul_rn(q1, s));
+        q_out[t * (size_t)d + b] = __fadd_rn(__fmul_rn(q0, s), __fmul_rn(q1, c));
+        k_cache[crow + a] = __fsub_rn(__fmul_rn(k0, c), __fmul_rn(k1, s));
+        k_cache[crow + b] = __fadd_rn(__fmul_rn(k0, s), __fmul_rn(k1, c));
+    }
+    for (int idx = threadIdx.x; idx < d; idx += blockDim.x) v_cache[crow + idx] = v[idx];
+}
+
+// one CTA per (sequence, head); kv length = lens[b] (includes the current token)
+__global__ void __launch_bounds__(128) attn_decode_kernel(const float *__restrict__ q, const float *__restrict__ k_cache,
+                                                          const float *__restrict__ v_cache, const int *__restrict__ lens,
+                                                          int n_heads, int hd, int lmax, float *__restrict__ out) {
+    extern __shared__ float sm[];  // [lmax] scores, then [hd] q
+    __shared__ float red_f[32];
+    float *scores = sm, *qs = sm + lmax;
+    const int b = blockIdx.x / n_heads, h = blockIdx.x % n_heads;
+    const int d = n_heads * hd, len = lens[b];
+    const float *qrow = q + (size_t)b * d + h * hd;
+    for (int i = threadIdx.x; i < hd; i += blockDim.x) qs[i] = qrow[i];
+    __syncthreads();
+    const float scale = __fdiv_rn(1.0f, sqrtf((float)hd));
+    const float *kb_ = k_cache + (size_t)b * lmax * d + h * hd;
+    float mx = -INFINITY;
+    for (int j = threadIdx.x; j < len; j += blockDim.x) {
+        const float *kr = kb_ + (size_t)j * d;
+        float dot = 0.0f;
+        for (int p = 0; p < hd; ++p) dot = fmaf(qs[p], kr[p], dot);
+        dot *= scale;
+        scores[j] = dot;
+        mx = fmaxf(mx, dot);
+    }
+    // block max (block_reduce_max clamps at 0, so shift by a large constant first is not
+    // needed: use a dedicated reduction that accepts negative values)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((threadIdx.x & 31) == 0) red_f[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = red_f[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, red_f[w]);
+    __syncthreads();
+    float sum = 0.0f;
+    for (int j = threadIdx.x; j < len; j += blockDim.x) {
+        const float e = expf(scores[j] - mx);
+        scores[j] = e;
+        sum += e;
+    }
+    sum = block_reduce_sum_f(sum, red_f);
+    const float inv = __fdiv_rn(1.0f, sum);
+    const float *vb = v_cache + (size_t)b * lmax * d + h * hd;
+    for (int p = threadIdx.x; p < hd; p += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < len; ++j) acc = fmaf(scores[j], vb[(size_t)j * d + p], acc);
+        out[(size_t)b * d + h * hd + p] = acc * inv;
+    }
+}
+
+}  // namespace kb
+
+using namespace kb;
+
+extern "C" {
+
+int kb_rmsnorm_quant(const float *x, const float *gamma, size_t n, size_t d, float eps, float *xn, int8_t *xq, size_t ldq,
+                     float *sx, int32_t *sumq, kb_stream stream) {
+    if (!x || !gamma || (!xn && !xq) || (xq && !sx)) return fail(KB_ERR_INVALID, "null pointer");
+    if (d == 0 || d > (size_t)ROW_REGS * 256) return fail(KB_ERR_UNSUPPORTED, "rmsnorm: dim %zu outside 1..%d", d, ROW_REGS * 256);
+    if (xq && (ldq < d || ldq > (size_t)ROW_REGS * 256 || ldq % 16)) return fail(KB_ERR_INVALID, "rmsnorm: bad ldq %zu", ldq);
+    if (n == 0) return KB_OK;
+    rmsnorm_quant_kernel<<<(unsigned)n, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, gamma, (int)d, eps, xn, xq, (int)ldq, sx, sumq);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "rmsnorm launch");
+}
+
+int kb_swiglu_quant(const float *gate_up, size_t n, size_t f, size_t ld, float *h, int8_t *xq, size_t ldq, float *sx,
+                    int32_t *sumq, kb_stream stream) {
+    if (!gate_up || (!h && !xq) || (xq && !sx)) return fail(KB_ERR_INVALID, "null pointer");
+    if (f == 0 || f > (size_t)ROW_REGS * 256 || ld < 2 * f) return fail(KB_ERR_UNSUPPORTED, "swiglu: width %zu outside 1..%d", f, ROW_REGS * 256);
+    if (xq && (ldq < f || ldq > (size_t)ROW_REGS * 256 || ldq % 16)) return fail(KB_ERR_INVALID, "swiglu: bad ldq %zu", ldq);
+    if (n == 0) return KB_OK;
+    swiglu_quant_kernel<<<(unsigned)n, 256, 0, static_cast<cudaStream_t>(stream)>>>(gate_up, (int)f, ld, h, xq, (int)ldq, sx, sumq);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "swiglu launch");
+}
+
+int kb_rope_kv(const float *qkv, const int *positions, const long long *cache_rows, const float *cos_table,
+               const float *sin_table, size_t n, int n_heads, int head_dim, float *q_out, float *k_cache, float *v_cache,
+               kb_stream stream) {
+    if (!qkv || !positions || !cache_rows || !cos_table || !sin_table || !q_out || !k_cache || !v_cache)
+        return fail(KB_ERR_INVALID, "null pointer");
+    if (n_heads < 1 || head_dim < 2 || head_dim % 2) return fail(KB_ERR_INVALID, "rope: head_dim must be even");
+    if (n == 0) return KB_OK;
+    rope_kv_kernel<<<(unsigned)n, 256, 0, static_cast<cudaStream_t>(stream)>>>(qkv, positions, cache_rows, cos_table, sin_table,
+                                                                              n_heads, head_dim, q_out, k_cache, v_cache);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "rope launch");
+}
+
+int kb_attn_decode(const float *q, const float *k_cache, const float *v_cache, const int *lens, size_t batch, int n_heads,
+                   int head_dim, int lmax, float *out, kb_stream stream) {
+    if (!q || !k_cache || !v_cache || !lens || !out) return fail(KB_ERR_INVALID, "null pointer");
+    const size_t smem = (size_t)(lmax + head_dim) * sizeof(float);
+    if (smem > 200 * 1024) return fail(KB_ERR_UNSUPPORTED, "attention: cache length %d too long for the score buffer", lmax);
+    if (batch == 0) return KB_OK;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(e, "attention smem attribute");
+    }
+    attn_decode_kernel<<<(unsigned)(batch * n_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(
+        q, k_cache, v_cache, lens, n_heads, head_dim, lmax, out);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "attention launch");
+}
+
+}  // extern "C"

@@ -59,6 +59,7 @@ struct GemmParams {
     int *status;
     float *y_more[MAX_PEERS - 1];  // further copies of y (peer GPUs), same offsets
     int n_more;
+    const float *resid;
 #ifdef KB_GEMM_DEBUG
     int dbg;  // developer build: bit0 skip unpack work, bit1 skip packed TMA, bit2 skip act TMA, bit3 skip MMA
 #endif
@@ -371,12 +372,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 const int valid = p.n - (n0 + c * 32);  // columns of this chunk that are real tokens
                 const size_t cbase = (size_t)(c * 32) * p.ldy;
                 float outv[32];
+                const bool add_resid = p.resid != nullptr && row_ok;
+                if (add_resid) {
+                    const float *rrow = p.resid + yoff + cbase;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) outv[i] = i < valid ? rrow[(size_t)i * p.ldy] : 0.0f;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) outv[i] = 0.0f;
+                }
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
+                    const float r_i = outv[i];
                     const float sx_i = __shfl_sync(0xffffffffu, sx_cur, i);
                     const int sm_i = __shfl_sync(0xffffffffu, sm_cur, i);
                     const int a = p.mul * (int)v[i] - p.off * sm_i;
                     outv[i] = dequant_out(a, sw, sx_i, bias, has_bias);
+                    if (add_resid) outv[i] = __fadd_rn(outv[i], r_i);
                     v[i] = (uint32_t)a;
                 }
                 if (row_ok) {
@@ -477,6 +489,7 @@ int launch_bn(const FwdArgs &a, cudaStream_t stream) {
     p.y = a.y; p.acc = a.acc; p.ldy = a.ldy ? a.ldy : L->m;
     p.n_more = a.y ? a.n_more : 0;
     for (int q = 0; q < MAX_PEERS - 1; ++q) p.y_more[q] = q < p.n_more ? a.y_more[q] : nullptr;
+    p.resid = a.y ? a.resid : nullptr;
     p.mul = L->mul; p.off = L->off; p.status = L->dev_status;
 #ifdef KB_GEMM_DEBUG
     { const char *e = getenv("KB_GEMM_DBG"); p.dbg = e ? atoi(e) : 0; }

@@ -51,6 +51,7 @@ struct GemvParams {
     float *y_more[MAX_PEERS - 1];  // further copies of y (peer GPUs), same offsets
     int n_more;
     PeerSync sync;  // sync.world == 0: no fused barrier
+    const float *resid;
 };
 
 // 16-element group g (k = 16*g .. 16*g+15) <-> shared-memory slot: inside each
@@ -294,7 +295,8 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
                             const size_t o = (size_t)tok * p.ldy + row;
                             if (p.acc) p.acc[o] = a;
                             if (p.y) {
-                                const float v = dequant_out(a, my_sw, s_sx[t], my_bias, p.bias != nullptr);
+                                float v = dequant_out(a, my_sw, s_sx[t], my_bias, p.bias != nullptr);
+                                if (p.resid) v = __fadd_rn(v, p.resid[o]);
                                 p.y[o] = v;
                                 for (int q = 0; q < p.n_more; ++q) p.y_more[q][o] = v;  // peer copies over NVLink
                             }
@@ -437,6 +439,7 @@ int launch_gemv(const FwdArgs &a, cudaStream_t stream) {
     p.x = a.x; p.xq = a.xq; p.ldq = a.ldq; p.sx = a.sx; p.sumq = a.sumq;
     p.n = (int)a.n; p.y = a.y; p.acc = a.acc; p.ldy = a.ldy ? a.ldy : L->m;
     p.mul = L->mul; p.off = L->off;
+    p.resid = a.y ? a.resid : nullptr;
     p.sync = PeerSync{};
     if (a.sync && a.y) p.sync = *a.sync;
     p.n_more = a.y ? a.n_more : 0;

@@ -1,0 +1,158 @@
+"""Decoder-step kernels and the small end-to-end decoder against the CPU restatement."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from oracle import decoder_ref as dr
+from oracle import kbref
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def env():
+    import torch
+
+    from kore_b200 import _cabi, decoder, nn
+
+    assert torch.cuda.is_available()
+    return type("E", (), {"torch": torch, "cabi": _cabi, "lib": _cabi.lib(), "decoder": decoder, "nn": nn,
+                          "sp": torch.cuda.current_stream().cuda_stream})
+
+
+@pytest.mark.parametrize("n,d", [(1, 3200), (5, 128), (3, 8640), (2, 77)])
+def test_rmsnorm_quant(env, n, d):
+    t = env.torch
+    x = cases.gaussian(n + d, (n, d), 1.5)
+    g = (1.0 + cases.gaussian(7, (d,), 0.1)).astype(np.float32)
+    ld = int(env.lib.kb_act_ld(d))
+    xd, gd = t.from_numpy(x).cuda(), t.from_numpy(g).cuda()
+    xn = t.empty((n, d), device="cuda")
+    xq = t.empty((n, ld), dtype=t.int8, device="cuda")
+    sx = t.empty(n, device="cuda")
+    sm = t.empty(n, dtype=t.int32, device="cuda")
+    env.cabi.check(env.lib.kb_rmsnorm_quant(xd.data_ptr(), gd.data_ptr(), n, d, C.c_float(1e-5), xn.data_ptr(), xq.data_ptr(), ld,
+                                            sx.data_ptr(), sm.data_ptr(), env.sp))
+    xn_h = xn.cpu().numpy()
+    ref = dr.rmsnorm(x, g, 1e-5)
+    # float reduction order differs from the sequential CPU sum: 1e-5 relative to the row's largest value
+    assert (np.abs(xn_h - ref) <= 1e-5 * np.abs(ref).max(axis=1, keepdims=True)).all()
+    # the quantiser applied to the kernel's own normalised values is exact
+    q_ref, s_ref, sum_ref = kbref.quantize_act_i8(xn_h, ldq=ld)
+    assert (xq.cpu().numpy() == q_ref).all() and (sx.cpu().numpy() == s_ref).all() and (sm.cpu().numpy() == sum_ref).all()
+
+
+@pytest.mark.parametrize("n,f", [(1, 8640), (4, 256), (2, 100)])
+def test_swiglu_quant(env, n, f):
+    t = env.torch
+    gu = cases.gaussian(n * f, (n, 2 * f), 2.0)
+    ld = int(env.lib.kb_act_ld(f))
+    gud = t.from_numpy(gu).cuda()
+    h = t.empty((n, f), device="cuda")
+    xq = t.empty((n, ld), dtype=t.int8, device="cuda")
+    sx = t.empty(n, device="cuda")
+    sm = t.empty(n, dtype=t.int32, device="cuda")
+    env.cabi.check(env.lib.kb_swiglu_quant(gud.data_ptr(), n, f, 2 * f, h.data_ptr(), xq.data_ptr(), ld, sx.data_ptr(), sm.data_ptr(), env.sp))
+    h_h = h.cpu().numpy()
+    ref = dr.silu_mul(gu[:, :f], gu[:, f:])
+    assert (np.abs(h_h - ref) <= 2e-6 * np.abs(ref).max() + 1e-7).all()  # expf differs from libm in the last bits
+    q_ref, s_ref, sum_ref = kbref.quantize_act_i8(h_h, ldq=ld)
+    assert (xq.cpu().numpy() == q_ref).all() and (sx.cpu().numpy() == s_ref).all() and (sm.cpu().numpy() == sum_ref).all()
+
+
+def test_rope_kv_and_attention(env):
+    t = env.torch
+    cfg = env.decoder.DecoderConfig(n_layers=1, d_model=128, n_heads=4, d_ff=256, vocab=50, max_len=24)
+    cos, sin = env.decoder.rope_tables(cfg)
+    H, hd, d = cfg.n_heads, cfg.head_dim, cfg.d_model
+    batch, lmax = 3, cfg.max_len
+    kc = t.zeros((batch, lmax, d), device="cuda")
+    vc = t.zeros((batch, lmax, d), device="cuda")
+    cosd, sind = t.from_numpy(cos).cuda(), t.from_numpy(sin).cuda()
+    lens = [5, 1, 9]
+    k_ref = [np.zeros((0, H, hd), np.float32) for _ in range(batch)]
+    v_ref = [np.zeros((0, H, hd), np.float32) for _ in range(batch)]
+    q_last = np.zeros((batch, H, hd), np.float32)
+    for b in range(batch):  # fill each sequence token by token
+        for pos in range(lens[b]):
+            qkv = cases.gaussian(1000 * b + pos, (1, 3 * d), 1.0)
+            q_out = t.empty((1, d), device="cuda")
+            qkv_d = t.from_numpy(qkv).cuda()  # named: a temporary would be freed before the kernel runs
+            pos_d = t.tensor([pos], dtype=t.int32, device="cuda")
+            row_d = t.tensor([b * lmax + pos], dtype=t.int64, device="cuda")
+            env.cabi.check(env.lib.kb_rope_kv(qkv_d.data_ptr(), pos_d.data_ptr(), row_d.data_ptr(), cosd.data_ptr(),
+                                              sind.data_ptr(), 1, H, hd, q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), env.sp))
+            t.cuda.synchronize()
+            q_r = dr.rope(qkv[:, :d].reshape(1, H, hd), np.array([pos]), cos, sin)
+            k_r = dr.rope(qkv[:, d:2 * d].reshape(1, H, hd), np.array([pos]), cos, sin)
+            assert (q_out.cpu().numpy().reshape(1, H, hd) == q_r).all()  # same table, same roundings
+            k_ref[b] = np.concatenate([k_ref[b], k_r])
+            v_ref[b] = np.concatenate([v_ref[b], qkv[:, 2 * d:].reshape(1, H, hd)])
+            q_last[b] = q_r[0]
+        assert (kc[b, :lens[b]].cpu().numpy().reshape(-1, H, hd) == k_ref[b]).all()
+        assert (vc[b, :lens[b]].cpu().numpy().reshape(-1, H, hd) == v_ref[b]).all()
+    out = t.empty((batch, d), device="cuda")
+    q_d = t.from_numpy(q_last.reshape(batch, d)).cuda()
+    lens_d = t.tensor(lens, dtype=t.int32, device="cuda")
+    env.cabi.check(env.lib.kb_attn_decode(q_d.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens_d.data_ptr(), batch, H, hd, lmax,
+                                          out.data_ptr(), env.sp))
+    for b in range(batch):
+        ref = dr.attention(q_last[b:b + 1], k_ref[b], v_ref[b], start_pos=lens[b] - 1).reshape(d)
+        assert np.abs(out[b].cpu().numpy() - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("n", [1, 4, 40])
+def test_fused_forward_with_residual(env, n):
+    t = env.torch
+    m, k = 200, 384
+    w = cases.gaussian(5, (m, k), 0.02)
+    packed, scales = cases.make_weights(kbref.TERNARY, "absmean", w)
+    lay = env.nn.BitLinear.from_packed(packed, scales, None, k, m)
+    x = cases.gaussian(6 + n, (n, k), 1.0)
+    resid = cases.gaussian(7, (n, m), 1.0)
+    y_ref = (kbref.q_forward(kbref.TERNARY, packed, scales, None, m, k, x)[0] + resid).astype(np.float32)
+    ws_bytes = int(env.lib.kb_linear_workspace_bytes(lay.handle, n))
+    ws = t.empty(ws_bytes + 256, dtype=t.uint8, device="cuda")
+    ws_ptr = (ws.data_ptr() + 255) // 256 * 256
+    # f32 input, residual updated in place
+    hid = t.from_numpy(resid).cuda()
+    x_d = t.from_numpy(x).cuda()
+    env.cabi.check(env.lib.kb_linear_forward_fused(lay.handle, x_d.data_ptr(), None, 0, None, None, n,
+                                                   hid.data_ptr(), hid.data_ptr(), 0, env.cabi.PATH_AUTO, ws_ptr, ws_bytes, env.sp))
+    assert (hid.cpu().numpy() == y_ref).all()
+    # pre-quantised input, separate output, both kernels
+    from kore_b200 import kernels
+    xq, sx, sm = kernels.quantize_act_i8(x_d)
+    resid_d = t.from_numpy(resid).cuda()
+    for path in (env.cabi.PATH_GEMV, env.cabi.PATH_GEMM_TC):
+        y = t.empty((n, m), device="cuda")
+        env.cabi.check(env.lib.kb_linear_forward_fused(lay.handle, None, xq.data_ptr(), xq.stride(0), sx.data_ptr(), sm.data_ptr(), n,
+                                                       resid_d.data_ptr(), y.data_ptr(), 0, path, None, 0, env.sp))
+        assert (y.cpu().numpy() == y_ref).all()
+
+
+def test_small_decoder_against_cpu_restatement(env):
+    t = env.torch
+    cfg = env.decoder.DecoderConfig(n_layers=2, d_model=128, n_heads=4, d_ff=256, vocab=97, max_len=32)
+    weights = env.decoder.random_weights(cfg, seed=4000)
+    cos, sin = env.decoder.rope_tables(cfg)
+    prompt = np.array([[5, 17, 3, 90, 41, 8], [1, 2, 3, 4, 5, 6]], np.int64)
+    dec = env.decoder.BitNetDecoder(cfg, weights, batch=2)
+    logits = dec.prefill(t.from_numpy(prompt).cuda()).cpu().numpy()
+    refs = [dr.DecoderRef(cfg, weights, cos, sin) for _ in range(2)]
+    ref_logits = np.stack([refs[b].forward(list(prompt[b])) for b in range(2)])
+    # int8 activation codes are discontinuous in the f32 inputs, so a last-bit difference in a
+    # norm or softmax can flip a code: tolerance is 2 % of the largest logit
+    tol = 0.02 * np.abs(ref_logits).max()
+    assert np.abs(logits - ref_logits).max() <= tol
+    toks = logits.argmax(axis=1)
+    dec.tokens.copy_(t.from_numpy(toks).cuda())
+    for step in range(3):
+        dec.decode_step(use_graph=(step > 0))
+        ref_logits = np.stack([refs[b].forward([int(toks[b])]) for b in range(2)])
+        got = dec.logits.cpu().numpy()
+        assert np.abs(got - ref_logits).max() <= tol, step
+        toks = dec.tokens.cpu().numpy()
+    dec.close()
