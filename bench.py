@@ -222,6 +222,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill / quaternary / batch side measurements")
     ap.add_argument("--pool", type=int, default=POOL)
     ap.add_argument("--streams", type=int, default=STREAMS)
+    ap.add_argument("--no-decoder", action="store_true", help="skip the BitNet-3B-shaped decoder measurement")
     ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "prefill_up", "prefill_down"],
                     help="run one small case and print its own JSON line (used for ncu captures)")
     args = ap.parse_args()
@@ -410,6 +411,13 @@ def main():
     }
     if cpu is not None:
         line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if world == 1 and not args.no_extras and not args.no_decoder:
+        del pool
+        torch.cuda.empty_cache()
+        try:
+            extras["bitnet_3b_shaped_decoder"] = decoder_measurement(torch, dev, peaks)
+        except Exception as exc:
+            extras["bitnet_3b_shaped_decoder"] = {"error": repr(exc)}
     if sharded_extra:
         extras["sharded_projection_8192_to_28672"] = sharded_extra
     if extras:
@@ -517,6 +525,59 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
     for lay in layers:
         lay.layer.close()
     ctx.close()
+    return out
+
+
+def decoder_measurement(torch, dev, peaks):
+    """BASELINE.json configs[3]: BitNet-b1.58-3B-shaped decoder (26 layers, d 3200, 32 heads,
+    FFN 8640, vocab 32000), random init, 512-token prompt then 128 greedy steps, batch 1 and 16.
+    Decode steps are CUDA-graph replays timed with CUDA events."""
+    from kore_b200 import decoder
+
+    cfg = decoder.DecoderConfig()
+    t0 = time.perf_counter()
+    weights = decoder.random_weights(cfg, seed=4000, device=dev.index)
+    build_s = time.perf_counter() - t0
+    wbytes = cfg.n_layers * (4 * cfg.d_model ** 2 + 3 * cfg.d_model * cfg.d_ff) // 4
+    out = {"weights_build_s": build_s, "packed_weight_bytes_per_token": wbytes,
+           "dense_parts": "embedding and lm_head are f32 torch matmuls", "prompt": 512, "steps": 128}
+    for batch in (1, 16):
+        dec = decoder.BitNetDecoder(cfg, weights, batch=batch, device=dev.index)
+        g = torch.Generator().manual_seed(4999)
+        prompt = torch.randint(0, cfg.vocab, (batch, 512), generator=g).to(dev)
+        torch.cuda.synchronize()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        logits = dec.prefill(prompt)
+        torch.argmax(logits, dim=1, out=dec.tokens)
+        e1.record()
+        torch.cuda.synchronize()
+        dec.decode_step()  # builds the graph (one eager step + capture), then first replay
+        torch.cuda.synchronize()
+        steps = 127
+        e1.record()
+        for _ in range(steps):
+            dec.decode_step()
+        e2.record()
+        torch.cuda.synchronize()
+        prefill_ms = None
+        dec_s = e1.elapsed_time(e2) / 1e3
+        entry = {"decode_tok_per_s": batch * steps / dec_s, "ms_per_step": dec_s / steps * 1e3,
+                 "weight_stream_GB/s": wbytes * steps / dec_s / 1e9,
+                 "frac_of_measured_hbm": wbytes * steps / dec_s / 1e9 / peaks["hbm_gbs"],
+                 "launches_per_step": dec.launches_per_step}
+        # prefill timed on a second, fresh pass (buffers already allocated)
+        dec2_e0, dec2_e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dec2_e0.record()
+        dec.prefill(prompt)
+        dec2_e1.record()
+        torch.cuda.synchronize()
+        entry["prefill_ms"] = dec2_e0.elapsed_time(dec2_e1)
+        entry["prefill_tok_per_s"] = batch * 512 / (entry["prefill_ms"] / 1e3)
+        out[f"batch{batch}"] = entry
+        dec.close()
+        del dec
+        torch.cuda.empty_cache()
     return out
 
 

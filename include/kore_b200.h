@@ -164,7 +164,11 @@ int kb_rope_kv(const float *qkv, const int *positions, const long long *cache_ro
 /* One query token per sequence against its cache [batch][lmax][n_heads*head_dim]
  * (crates/kore-edge/src/ops/attention.rs:74-135); lens[b] counts the current token. */
 int kb_attn_decode(const float *q, const float *k_cache, const float *v_cache, const int *lens,
-                   size_t batch, int n_heads, int head_dim, int lmax, float *out, kb_stream stream);
+                   size_t batch, int n_heads, int head_dim, int lmax, float *out, float *scratch,
+                   size_t scratch_bytes, kb_stream stream);
+/* scratch (zero-initialised once by the caller, reusable across calls on one stream) lets the
+ * kernel split long caches over several CTAs per head; without it one CTA serves a head. */
+size_t kb_attn_decode_scratch_bytes(size_t batch, int n_heads);
 
 /* ---- forward (host pointers; what a Tensor-in/Tensor-out caller uses) ---- */
 

@@ -9,8 +9,8 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_DIR = os.path.join(_PKG, "_lib")
 LIB_PATH = os.path.join(LIB_DIR, "libkore_b200.so")
-SOURCES = ["api.cu", "quant.cu", "gemv.cu", "gemm_tc.cu", "static_scratch.cu", "shard.cu", "decoder_ops.cu"]
-HEADERS = ["common.cuh", "device_utils.cuh", os.path.join("..", "..", "include", "kore_b200.h")]
+SOURCES = ["api.cu", "quant.cu", "gemv.cu", "gemm_tc.cu", "gemm_tc2.cu", "static_scratch.cu", "shard.cu", "decoder_ops.cu"]
+HEADERS = ["common.cuh", "device_utils.cuh", "tc_ptx.cuh", os.path.join("..", "..", "include", "kore_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

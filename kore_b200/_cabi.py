@@ -42,7 +42,8 @@ SIGNATURES = {
     "kb_rmsnorm_quant": (C.c_int, [_vp, _vp, _sz, _sz, C.c_float, _vp, _vp, _sz, _vp, _vp, _vp]),
     "kb_swiglu_quant": (C.c_int, [_vp, _sz, _sz, _sz, _vp, _vp, _sz, _vp, _vp, _vp]),
     "kb_rope_kv": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
-    "kb_attn_decode": (C.c_int, [_vp, _vp, _vp, _vp, _sz, C.c_int, C.c_int, C.c_int, _vp, _vp]),
+    "kb_attn_decode": (C.c_int, [_vp, _vp, _vp, _vp, _sz, C.c_int, C.c_int, C.c_int, _vp, _vp, _sz, _vp]),
+    "kb_attn_decode_scratch_bytes": (_sz, [_sz, C.c_int]),
     "kb_linear_forward_host": (C.c_int, [_vp, _vp, _sz, _sz, _vp]),
     "kb_linear_forward_static": (C.c_int, [_vp, _vp, _sz, _sz, _vp, _vp]),
     "kb_static_scratch_bytes": (_sz, []),

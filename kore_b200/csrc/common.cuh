@@ -48,8 +48,10 @@ struct Linear {
     float *scales;  // [m_alloc]
     float *bias;    // [m_alloc] or nullptr
     int mul, off;
-    CUtensorMap tmap_w;  // 2-D map over w2 for the GEMM (box 32 B x 128 rows)
+    CUtensorMap tmap_w;    // 2-D map over w2 for the GEMM (box 32 B x 128 rows)
+    CUtensorMap tmap_w64;  // same tensor, box 64 B x 128 rows (CTA-pair GEMM: two K slabs per stage)
     bool has_tmap;
+    bool has_tmap64;
     int *dev_status;  // one int in device memory
 };
 
@@ -111,6 +113,8 @@ struct FwdArgs {
 int launch_gemv(const FwdArgs &a, cudaStream_t stream);
 // tcgen05 int8 GEMM; needs pre-quantised activations
 int launch_gemm_tc(const FwdArgs &a, cudaStream_t stream);
+// same contract, CTA-pair kernel (tcgen05 cta_group::2); chosen by launch_gemm_tc for large token counts
+int launch_gemm_tc2(const FwdArgs &a, cudaStream_t stream);
 bool gemv_supports(const Linear *lin, size_t n);
 bool gemm_tc_supports(const Linear *lin, size_t n);
 int encode_weight_tmap(Linear *lin);

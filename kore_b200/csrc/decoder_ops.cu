@@ -142,51 +142,104 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const float *__restrict__ 
     for (int idx = threadIdx.x; idx < d; idx += blockDim.x) v_cache[crow + idx] = v[idx];
 }
 
-// one CTA per (sequence, head); kv length = lens[b] (includes the current token)
-__global__ void __launch_bounds__(128) attn_decode_kernel(const float *__restrict__ q, const float *__restrict__ k_cache,
-                                                          const float *__restrict__ v_cache, const int *__restrict__ lens,
-                                                          int n_heads, int hd, int lmax, float *__restrict__ out) {
-    extern __shared__ float sm[];  // [lmax] scores, then [hd] q
-    __shared__ float red_f[32];
-    float *scores = sm, *qs = sm + lmax;
-    const int b = blockIdx.x / n_heads, h = blockIdx.x % n_heads;
+// Decode attention, split over the cache length (flash-decoding style): CTA (b, h, s) handles
+// key positions [s*chunk, (s+1)*chunk) of sequence b / head h.  A warp owns one position at a
+// time: its lanes read the key row coalesced (dims lane, lane+32, ...) and reduce the dot with
+// shuffles, keep a running (max, sum) and a running V accumulator with the usual rescaling.
+// Per-warp partials are merged in shared memory, per-CTA partials in `scratch`
+// ([b*h][splits][2 + hd]); the last CTA of a (b, h) — found with a self-resetting counter —
+// merges them and writes the output.
+constexpr int ATT_WARPS = 8;
+constexpr int ATT_MAX_HD = 128;
+
+__global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
+    const float *__restrict__ q, const float *__restrict__ k_cache, const float *__restrict__ v_cache,
+    const int *__restrict__ lens, int n_heads, int hd, int lmax, int splits, float *__restrict__ scratch,
+    int *__restrict__ counters, float *__restrict__ out) {
+    __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS], s_acc[ATT_WARPS][ATT_MAX_HD];
+    __shared__ int s_last;
+    const int bh = blockIdx.x / splits, sp = blockIdx.x % splits;
+    const int b = bh / n_heads, h = bh % n_heads;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int d = n_heads * hd, len = lens[b];
+    const int chunk = (len + splits - 1) / splits;
+    const int j0 = sp * chunk, j1 = min(len, j0 + chunk);
+    constexpr int DPL = ATT_MAX_HD / 32;  // dims per lane
+    float qv[DPL], acc[DPL];
     const float *qrow = q + (size_t)b * d + h * hd;
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) qs[i] = qrow[i];
-    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+        const int p = lane + 32 * i;
+        qv[i] = p < hd ? qrow[p] : 0.0f;
+        acc[i] = 0.0f;
+    }
     const float scale = __fdiv_rn(1.0f, sqrtf((float)hd));
     const float *kb_ = k_cache + (size_t)b * lmax * d + h * hd;
-    float mx = -INFINITY;
-    for (int j = threadIdx.x; j < len; j += blockDim.x) {
-        const float *kr = kb_ + (size_t)j * d;
-        float dot = 0.0f;
-        for (int p = 0; p < hd; ++p) dot = fmaf(qs[p], kr[p], dot);
-        dot *= scale;
-        scores[j] = dot;
-        mx = fmaxf(mx, dot);
-    }
-    // block max (block_reduce_max clamps at 0, so shift by a large constant first is not
-    // needed: use a dedicated reduction that accepts negative values)
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if ((threadIdx.x & 31) == 0) red_f[threadIdx.x >> 5] = mx;
-    __syncthreads();
-    mx = red_f[0];
-    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, red_f[w]);
-    __syncthreads();
-    float sum = 0.0f;
-    for (int j = threadIdx.x; j < len; j += blockDim.x) {
-        const float e = expf(scores[j] - mx);
-        scores[j] = e;
-        sum += e;
-    }
-    sum = block_reduce_sum_f(sum, red_f);
-    const float inv = __fdiv_rn(1.0f, sum);
     const float *vb = v_cache + (size_t)b * lmax * d + h * hd;
-    for (int p = threadIdx.x; p < hd; p += blockDim.x) {
-        float acc = 0.0f;
-        for (int j = 0; j < len; ++j) acc = fmaf(scores[j], vb[(size_t)j * d + p], acc);
-        out[(size_t)b * d + h * hd + p] = acc * inv;
+    float m = -INFINITY, l = 0.0f;
+    for (int j = j0 + warp; j < j1; j += ATT_WARPS) {
+        const float *kr = kb_ + (size_t)j * d, *vr = vb + (size_t)j * d;
+        float dot = 0.0f, vv[DPL];
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int p = lane + 32 * i;
+            dot = fmaf(qv[i], p < hd ? kr[p] : 0.0f, dot);
+            vv[i] = p < hd ? vr[p] : 0.0f;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        dot *= scale;
+        const float m_new = fmaxf(m, dot);
+        const float corr = expf(m - m_new), pj = expf(dot - m_new);
+        l = l * corr + pj;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[i] = fmaf(pj, vv[i], acc[i] * corr);
+        m = m_new;
+    }
+    if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) s_acc[warp][lane + 32 * i] = acc[i];
+    __syncthreads();
+    // merge the warps of this CTA (threads 0..hd-1 each own one output dim)
+    float cm = -INFINITY;
+    for (int w = 0; w < ATT_WARPS; ++w) cm = fmaxf(cm, s_m[w]);
+    float cl = 0.0f, ca = 0.0f;
+    if ((int)threadIdx.x < hd) {
+        for (int w = 0; w < ATT_WARPS; ++w) {
+            const float f = s_m[w] == -INFINITY ? 0.0f : expf(s_m[w] - cm);
+            cl += s_l[w] * f;
+            ca += s_acc[w][threadIdx.x] * f;
+        }
+    }
+    if (splits == 1) {
+        if ((int)threadIdx.x < hd) out[(size_t)b * d + h * hd + threadIdx.x] = ca * __fdiv_rn(1.0f, cl);
+        return;
+    }
+    float *part = scratch + ((size_t)bh * splits + sp) * (2 + ATT_MAX_HD);
+    if (threadIdx.x == 0) { part[0] = cm; part[1] = cl; }
+    if ((int)threadIdx.x < hd) part[2 + threadIdx.x] = ca;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(counters + bh, 1);
+        s_last = (ticket == splits - 1);
+        if (s_last) counters[bh] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float *base = scratch + (size_t)bh * splits * (2 + ATT_MAX_HD);
+    float gm = -INFINITY;
+    for (int s2 = 0; s2 < splits; ++s2) gm = fmaxf(gm, base[s2 * (2 + ATT_MAX_HD)]);
+    if ((int)threadIdx.x < hd) {
+        float gl = 0.0f, ga = 0.0f;
+        for (int s2 = 0; s2 < splits; ++s2) {
+            const float *ps = base + s2 * (2 + ATT_MAX_HD);
+            const float f = ps[0] == -INFINITY ? 0.0f : expf(ps[0] - gm);
+            gl += ps[1] * f;
+            ga += ps[2 + threadIdx.x] * f;
+        }
+        out[(size_t)b * d + h * hd + threadIdx.x] = ga * __fdiv_rn(1.0f, gl);
     }
 }
 
@@ -232,19 +285,28 @@ int kb_rope_kv(const float *qkv, const int *positions, const long long *cache_ro
 }
 
 int kb_attn_decode(const float *q, const float *k_cache, const float *v_cache, const int *lens, size_t batch, int n_heads,
-                   int head_dim, int lmax, float *out, kb_stream stream) {
+                   int head_dim, int lmax, float *out, float *scratch, size_t scratch_bytes, kb_stream stream) {
     if (!q || !k_cache || !v_cache || !lens || !out) return fail(KB_ERR_INVALID, "null pointer");
-    const size_t smem = (size_t)(lmax + head_dim) * sizeof(float);
-    if (smem > 200 * 1024) return fail(KB_ERR_UNSUPPORTED, "attention: cache length %d too long for the score buffer", lmax);
+    if (head_dim < 1 || head_dim > ATT_MAX_HD) return fail(KB_ERR_UNSUPPORTED, "attention: head_dim %d outside 1..%d", head_dim, ATT_MAX_HD);
     if (batch == 0) return KB_OK;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return cuda_fail(e, "attention smem attribute");
-    }
-    attn_decode_kernel<<<(unsigned)(batch * n_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(
-        q, k_cache, v_cache, lens, n_heads, head_dim, lmax, out);
+    // enough CTAs to cover the GPU about twice; splitting needs the caller's scratch
+    const size_t bh = batch * (size_t)n_heads;
+    int splits = (int)((296 + bh - 1) / bh);
+    if (splits > 16) splits = 16;
+    if (splits > lmax) splits = lmax > 0 ? lmax : 1;
+    const size_t need = bh * sizeof(int) + 256 + bh * (size_t)splits * (2 + ATT_MAX_HD) * sizeof(float);
+    if (splits > 1 && (!scratch || scratch_bytes < need)) splits = 1;
+    int *counters = reinterpret_cast<int *>(scratch);
+    float *parts = scratch ? reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + (bh * sizeof(int) + 255) / 256 * 256) : nullptr;
+    attn_decode_kernel<<<(unsigned)(bh * splits), ATT_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        q, k_cache, v_cache, lens, n_heads, head_dim, lmax, splits, parts, counters, out);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "attention launch");
+}
+
+size_t kb_attn_decode_scratch_bytes(size_t batch, int n_heads) {
+    const size_t bh = batch * (size_t)n_heads;
+    return bh * sizeof(int) + 256 + bh * 16 * (2 + ATT_MAX_HD) * sizeof(float);
 }
 
 }  // extern "C"

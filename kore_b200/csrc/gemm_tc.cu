@@ -516,6 +516,9 @@ int encode_weight_tmap(Linear *lin) {
     int rc = encode_2d(&lin->tmap_w, lin->w2, lin->row_bytes, lin->m_alloc, lin->row_bytes, BK / 4, BM,
                        CU_TENSOR_MAP_SWIZZLE_NONE);
     lin->has_tmap = (rc == KB_OK);
+    // the CTA-pair kernel's map is optional: without it the single-CTA kernel serves every size
+    lin->has_tmap64 = rc == KB_OK && encode_2d(&lin->tmap_w64, lin->w2, lin->row_bytes, lin->m_alloc, lin->row_bytes,
+                                               BK / 2, BM, CU_TENSOR_MAP_SWIZZLE_NONE) == KB_OK;
     return rc;
 }
 
@@ -532,6 +535,9 @@ int launch_gemm_tc(const FwdArgs &a, cudaStream_t stream) {
         return fail(KB_ERR_INVALID, "gemm: xq must be 16-byte aligned with ldq >= %zu and ldq %% 16 == 0", L->kp);
     if (a.n <= 64) return launch_bn<64>(a, stream);
     if (a.n <= 128) return launch_bn<128>(a, stream);
+    // full 256-token tiles go to the CTA-pair kernel (KB_GEMM_PAIR=0 keeps the single-CTA one)
+    static const int use_pair = []() { const char *e = getenv("KB_GEMM_PAIR"); return e ? atoi(e) : 1; }();
+    if (use_pair && L->has_tmap64) return launch_gemm_tc2(a, stream);
     return launch_bn<256>(a, stream);
 }
 

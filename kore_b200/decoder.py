@@ -117,6 +117,8 @@ class BitNetDecoder:
         self.cache_rows = (torch.arange(batch, dtype=torch.int64, device=self.dev) * cfg.max_len)
         self.tokens = torch.zeros(batch, dtype=torch.int64, device=self.dev)
         self.logits = torch.zeros((batch, v), dtype=torch.float32, device=self.dev)
+        self.att_bytes = int(self.lib.kb_attn_decode_scratch_bytes(batch, cfg.n_heads))
+        self.att_scratch = torch.zeros(self.att_bytes, dtype=torch.uint8, device=self.dev)
         self.graph = None
         self.launches_per_step = 0
 
@@ -153,7 +155,8 @@ class BitNetDecoder:
                               self.sin.data_ptr(), n, H, hd, B["q"].data_ptr(), self.kc[li].data_ptr(), self.vc[li].data_ptr(), sp))
             if prefill_shape is None:
                 ck(lib.kb_attn_decode(B["q"].data_ptr(), self.kc[li].data_ptr(), self.vc[li].data_ptr(), lens.data_ptr(),
-                                      n, H, hd, cfg.max_len, B["attn"].data_ptr(), sp))
+                                      n, H, hd, cfg.max_len, B["attn"].data_ptr(), self.att_scratch.data_ptr(),
+                                      self.att_bytes, sp))
                 launches += 4
             else:
                 b, t = prefill_shape

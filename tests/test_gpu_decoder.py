@@ -96,11 +96,16 @@ def test_rope_kv_and_attention(env):
     out = t.empty((batch, d), device="cuda")
     q_d = t.from_numpy(q_last.reshape(batch, d)).cuda()
     lens_d = t.tensor(lens, dtype=t.int32, device="cuda")
-    env.cabi.check(env.lib.kb_attn_decode(q_d.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens_d.data_ptr(), batch, H, hd, lmax,
-                                          out.data_ptr(), env.sp))
-    for b in range(batch):
-        ref = dr.attention(q_last[b:b + 1], k_ref[b], v_ref[b], start_pos=lens[b] - 1).reshape(d)
-        assert np.abs(out[b].cpu().numpy() - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max())
+    nbytes = int(env.lib.kb_attn_decode_scratch_bytes(batch, H))
+    scratch = t.zeros(nbytes, dtype=t.uint8, device="cuda")
+    for use_scratch in (True, True, False):  # split path twice (counters must reset), then one CTA per head
+        out.zero_()
+        env.cabi.check(env.lib.kb_attn_decode(q_d.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens_d.data_ptr(), batch, H, hd, lmax,
+                                              out.data_ptr(), scratch.data_ptr() if use_scratch else None,
+                                              nbytes if use_scratch else 0, env.sp))
+        for b in range(batch):
+            ref = dr.attention(q_last[b:b + 1], k_ref[b], v_ref[b], start_pos=lens[b] - 1).reshape(d)
+            assert np.abs(out[b].cpu().numpy() - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max())
 
 
 @pytest.mark.parametrize("n", [1, 4, 40])
