@@ -142,6 +142,8 @@ SHAPES = [
     # m, k, n
     (128, 256, 1), (128, 256, 32), (8, 20, 4), (2, 7, 3), (16, 32, 16), (1, 1, 1), (130, 1000, 5),
     (300, 4096, 2), (257, 2304, 8), (64, 5, 9), (200, 640, 70), (129, 384, 130), (256, 512, 300),
+    # CTA-pair GEMM edges: odd number of 128-row blocks, odd number of 128-byte K slabs, ragged tokens
+    (384, 640, 520), (130, 128, 257),
 ]
 
 
@@ -170,6 +172,49 @@ def test_forward_bit_exact(torch, kb, path, kind, quantiser, m, k, n):
     y_r = kbref.linear_forward(kind, packed, scales, bias, m, k, (xq.astype(np.float32) * sx[:, None]).astype(np.float32))
     tol = 1e-5 * np.abs(y_r).max(axis=1, keepdims=True) + 1e-7
     assert (np.abs(y.cpu().numpy() - y_r) <= tol).all()
+
+
+# ---- BASELINE.json's full sizes: size-independent properties + sampled exact rows ---------
+FULL_SIZES = [
+    # name, m, k, n, kind
+    ("decode_4096x4096_b1", 4096, 4096, 1, T),
+    ("decode_4096x4096_b16_quat", 4096, 4096, 16, Q),
+    ("prefill_up_2048tok", 11008, 4096, 2048, T),
+    ("prefill_down_2048tok", 4096, 11008, 2048, T),
+    ("ffn70b_8192x28672_b1", 28672, 8192, 1, T),
+    ("ffn70b_8192x28672_b64", 28672, 8192, 64, T),
+]
+
+
+@pytest.mark.parametrize("name,m,k,n,kind", FULL_SIZES)
+def test_full_size_checksum_and_sampled_rows(torch, kb, name, m, k, n, kind):
+    """At full size the oracle cannot afford every output, so: (1) checksum of checksums —
+    sum over output features of the int32 accumulators equals xq . (column sums of W), an
+    identity that touches every weight and every activation; (2) 48 sampled output features
+    are compared exactly (accumulators and f32 outputs) against the oracle for all tokens."""
+    g = torch.Generator().manual_seed(sum(name.encode()) % 1000)
+    w = (torch.randn((m, k), generator=g) * 0.02).numpy()
+    x = torch.randn((n, k), generator=g).numpy()
+    if kind == T:
+        lay = kb.nn.BitLinear.new(w, None, 0.3, quantiser="absmean")
+    else:
+        lay = kb.nn.QuatLinear.new(w)
+    del w
+    packed, scales = lay.packed_weights(), lay.scales()
+    y, acc = lay.forward(torch.from_numpy(x).cuda(), return_acc=True)
+    torch.cuda.synchronize()
+    st = C.c_int(0)
+    assert kb.cabi.lib().kb_linear_last_device_status(lay.handle, None, C.byref(st)) == 0, st.value
+    acc_h, y_h = acc.cpu().numpy(), y.cpu().numpy()
+    xq, sx, _ = kbref.quantize_act_i8(x)
+    w_i8 = kbref.decode_weights_i8(kind, packed, m, k)
+    colsum = w_i8.astype(np.int64).sum(axis=0)
+    assert (acc_h.astype(np.int64).sum(axis=1) == xq.astype(np.int64) @ colsum).all()
+    rows = np.random.default_rng(1).choice(m, size=48, replace=False)
+    acc_ref = kbref.acc_i32(np.ascontiguousarray(w_i8[rows]), xq, threads=8)
+    assert (acc_h[:, rows] == acc_ref).all()
+    assert (y_h[:, rows] == kbref.dequant_epilogue(acc_ref, scales[rows], sx)).all()
+    assert np.isfinite(y_h).all()
 
 
 def test_auto_path_matches_and_host_entry(torch, kb):
