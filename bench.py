@@ -222,6 +222,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill / quaternary / batch side measurements")
     ap.add_argument("--pool", type=int, default=POOL)
     ap.add_argument("--streams", type=int, default=STREAMS)
+    ap.add_argument("--fused-quant", action="store_true",
+                    help="N=1: run the activation quantiser inside the GEMV prologue (one launch per layer)")
     ap.add_argument("--no-decoder", action="store_true", help="skip the BitNet-3B-shaped decoder measurement")
     ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "prefill_up", "prefill_down"],
                     help="run one small case and print its own JSON line (used for ncu captures)")
@@ -275,18 +277,25 @@ def main():
         sxs = [torch.zeros(1, dtype=torch.float32, device=dev) for _ in fan.side]
         sms = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in fan.side]
 
+        # several independent layers are in flight at once: the GEMV grid sized for sharing the SMs
+        gemv_path = _cabi.PATH_GEMV_SHARED if n_streams > 1 else _cabi.PATH_GEMV
+
         def step():
             fan.fork()
             for j, lay in enumerate(pool):
                 i = j % len(fan.side)
                 sp = fan.side[i].cuda_stream
+                if args.fused_quant:  # quantiser in the GEMV prologue: one launch per layer
+                    _cabi.check(lib.kb_linear_forward_ex(lay.handle, x_dev.data_ptr(), 1, K_DEC, ys[i].data_ptr(), 0, None,
+                                                         _cabi.PATH_GEMV, None, 0, sp))
+                    continue
                 _cabi.check(lib.kb_quantize_act_i8(x_dev.data_ptr(), 1, K_DEC, xqs[i].data_ptr(), ld, sxs[i].data_ptr(),
                                                    sms[i].data_ptr(), sp))
                 _cabi.check(lib.kb_linear_forward_q8(lay.handle, xqs[i].data_ptr(), ld, sxs[i].data_ptr(), sms[i].data_ptr(),
-                                                     1, ys[i].data_ptr(), 0, None, _cabi.PATH_GEMV, sp))
+                                                     1, ys[i].data_ptr(), 0, None, gemv_path, sp))
             fan.join()
 
-        launches_per_step = 2 * pool_n
+        launches_per_step = (1 if args.fused_quant else 2) * pool_n
         y_view = lambda: ys[(pool_n - 1) % len(fan.side)][0]
         ctx = None
     else:

@@ -55,8 +55,12 @@ enum {
     KB_QUANT_ABSMEAN = 1    /* ternary only: per-tensor s = mean|W|, clamp(rne(W/s),-1,1) */
 };
 
-/* kernel choice for kb_linear_forward_ex (test hook; AUTO picks by N) */
-enum { KB_PATH_AUTO = 0, KB_PATH_GEMV = 1, KB_PATH_GEMM_TC = 2 };
+/* kernel choice for the forward entry points that take `path` (AUTO picks by N).
+ * KB_PATH_GEMV_SHARED is the GEMV launched with about half the CTAs (two row groups per warp):
+ * a single launch finishes later, but independent layers issued on several streams share the
+ * SMs better and their aggregate bandwidth is higher.  Use it when several GEMVs are in
+ * flight at once; use KB_PATH_GEMV (or AUTO) for a chain of dependent layers. */
+enum { KB_PATH_AUTO = 0, KB_PATH_GEMV = 1, KB_PATH_GEMM_TC = 2, KB_PATH_GEMV_SHARED = 3 };
 
 typedef struct kb_linear kb_linear; /* opaque: device-resident 2-bit weights + scales + bias */
 typedef void *kb_stream;            /* a cudaStream_t; NULL = the legacy default stream */

@@ -115,6 +115,7 @@ static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim
     if (path == KB_PATH_AUTO) path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : KB_PATH_GEMM_TC;
     FwdArgs a = {};
     a.lin = L; a.n = n; a.y = y; a.acc = acc; a.ldy = ldy;
+    if (path == KB_PATH_GEMV_SHARED) { a.shared_grid = true; path = KB_PATH_GEMV; }
     if (path == KB_PATH_GEMV) {
         a.x = x;
         return launch_gemv(a, stream);
@@ -441,6 +442,7 @@ int kb_linear_forward_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const
     if (path == KB_PATH_AUTO) path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : KB_PATH_GEMM_TC;
     FwdArgs a = {};
     a.lin = L; a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq; a.n = n; a.y = y; a.acc = acc; a.ldy = ldy;
+    if (path == KB_PATH_GEMV_SHARED) { a.shared_grid = true; path = KB_PATH_GEMV; }
     if (path == KB_PATH_GEMV) return launch_gemv(a, static_cast<cudaStream_t>(stream));
     if (path == KB_PATH_GEMM_TC) return launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
     return fail(KB_ERR_INVALID, "unknown path %d", path);
@@ -459,6 +461,7 @@ int kb_linear_forward_fused(const kb_linear *h, const float *x, const int8_t *xq
     if (path == KB_PATH_AUTO) path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : KB_PATH_GEMM_TC;
     FwdArgs a = {};
     a.lin = L; a.n = n; a.y = y; a.ldy = ldy; a.resid = resid;
+    if (path == KB_PATH_GEMV_SHARED) { a.shared_grid = true; path = KB_PATH_GEMV; }
     if (xq) {
         a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq;
         if (path == KB_PATH_GEMV) return launch_gemv(a, st);

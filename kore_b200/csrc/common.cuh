@@ -108,6 +108,8 @@ struct FwdArgs {
     const struct PeerSync *sync;
     // optional residual, same [N][ldy] layout as y (may be y itself): y = dequant(...) + resid
     const float *resid;
+    // GEMV only: size the grid for launches that overlap with other streams' GEMVs
+    bool shared_grid;
 };
 // decode GEMV; when args.x is set the activation quantiser is fused into its prologue
 int launch_gemv(const FwdArgs &a, cudaStream_t stream);

@@ -15,10 +15,40 @@
 //                    crates/kore-serve/src/layered/engine.rs:734-751)
 // All are HBM/latency-bound elementwise or row-reduction work, one CTA per token (or per
 // sequence-head); none is reshaped into a GEMM.
+//
+// Every kernel is launched with programmatic stream serialization: it lets its successor
+// start at once (griddepcontrol.launch_dependents — the following GEMV streams its first
+// weights meanwhile) and reads its own inputs only after griddepcontrol.wait, which returns
+// when the predecessor grid has completed and its writes are visible.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "device_utils.cuh"
 
 namespace kb {
+
+__device__ __forceinline__ void pdl_release_and_wait() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+    static const bool pdl = [] {
+        const char *v = getenv("KB_GEMV_PDL");
+        return !(v && *v == '0');
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 
 __device__ __forceinline__ float block_reduce_sum_f(float v, float *scratch) {
 #pragma unroll
@@ -70,25 +100,33 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const float *__restr
     __shared__ int red_i[32];
     const size_t t = blockIdx.x;
     const float *row = x + t * (size_t)d;
-    float v[ROW_REGS];
-    float ss = 0.0f;
+    // every global load of the row (and of gamma) is issued before the first use, so the
+    // single CTA pays one memory round trip instead of one per element
+    float v[ROW_REGS], gm[ROW_REGS];
+#pragma unroll
+    for (int i = 0; i < ROW_REGS; ++i) {  // gamma is a constant of the layer: fetched before the wait
+        const int idx = threadIdx.x + i * blockDim.x;
+        gm[i] = idx < d ? gamma[idx] : 0.0f;
+    }
+    pdl_release_and_wait();
 #pragma unroll
     for (int i = 0; i < ROW_REGS; ++i) {
         const int idx = threadIdx.x + i * blockDim.x;
         v[i] = idx < d ? row[idx] : 0.0f;
-        ss = __fadd_rn(ss, __fmul_rn(v[i], v[i]));
     }
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ROW_REGS; ++i) ss = __fadd_rn(ss, __fmul_rn(v[i], v[i]));
     ss = block_reduce_sum_f(ss, red_f);
     const float rms = sqrtf(__fadd_rn(__fdiv_rn(ss, (float)d), eps));
     const float inv = __fdiv_rn(1.0f, rms);
 #pragma unroll
-    for (int i = 0; i < ROW_REGS; ++i) {
-        const int idx = threadIdx.x + i * blockDim.x;
-        if (idx < d) {
-            v[i] = __fmul_rn(__fmul_rn(v[i], inv), gamma[idx]);
-            if (xn) xn[t * (size_t)d + idx] = v[i];
-        } else {
-            v[i] = 0.0f;
+    for (int i = 0; i < ROW_REGS; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], inv), gm[i]);
+    if (xn) {
+#pragma unroll
+        for (int i = 0; i < ROW_REGS; ++i) {
+            const int idx = threadIdx.x + i * blockDim.x;
+            if (idx < d) xn[t * (size_t)d + idx] = v[i];
         }
     }
     if (xq) quantise_row_from_regs<ROW_REGS>(v, d, ldq, xq + t * (size_t)ldq, sx + t, sumq ? sumq + t : nullptr, red_f, red_i);
@@ -101,24 +139,32 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restri
     __shared__ int red_i[32];
     const size_t t = blockIdx.x;
     const float *g = gu + t * ld, *u = g + f;
-    float v[ROW_REGS];
+    float v[ROW_REGS], uv[ROW_REGS];
+    pdl_release_and_wait();
+#pragma unroll
+    for (int i = 0; i < ROW_REGS; ++i) {  // all loads first: one memory round trip for the row
+        const int idx = threadIdx.x + i * blockDim.x;
+        v[i] = idx < f ? g[idx] : 0.0f;
+        uv[i] = idx < f ? u[idx] : 0.0f;
+    }
 #pragma unroll
     for (int i = 0; i < ROW_REGS; ++i) {
-        const int idx = threadIdx.x + i * blockDim.x;
-        if (idx < f) {
-            const float gv = g[idx];
-            const float silu = __fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv)));
-            v[i] = __fmul_rn(silu, u[idx]);
-            if (h_out) h_out[t * (size_t)f + idx] = v[i];
-        } else {
-            v[i] = 0.0f;
+        const float silu = __fdiv_rn(v[i], __fadd_rn(1.0f, expf(-v[i])));
+        v[i] = __fmul_rn(silu, uv[i]);
+    }
+    if (h_out) {
+#pragma unroll
+        for (int i = 0; i < ROW_REGS; ++i) {
+            const int idx = threadIdx.x + i * blockDim.x;
+            if (idx < f) h_out[t * (size_t)f + idx] = v[i];
         }
     }
     if (xq) quantise_row_from_regs<ROW_REGS>(v, f, ldq, xq + t * (size_t)ldq, sx + t, sumq ? sumq + t : nullptr, red_f, red_i);
 }
 
-// one CTA per token: rotate q and k (pairs i, i + hd/2 inside each head), write q to q_out and
-// k, v to row cache_rows[t] of the caches.  cos/sin tables are [max_pos][hd/2].
+// grid (token, chunk): thread handles one (head, i) pair of q and k and one or two elements of
+// v, so every load of a token is in flight at once.  Rotation pairs are (i, i + hd/2) inside
+// each head; k and v go to row cache_rows[t] of the caches; cos/sin tables are [max_pos][hd/2].
 __global__ void __launch_bounds__(256) rope_kv_kernel(const float *__restrict__ qkv, const int *__restrict__ positions,
                                                       const long long *__restrict__ cache_rows,
                                                       const float *__restrict__ cos_t, const float *__restrict__ sin_t,
@@ -127,19 +173,22 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const float *__restrict__ 
     const size_t t = blockIdx.x;
     const int d = n_heads * hd, half = hd / 2;
     const float *q = qkv + t * (size_t)(3 * d), *k = q + d, *v = k + d;
+    pdl_release_and_wait();
     const int pos = positions[t];
     const size_t crow = (size_t)cache_rows[t] * d;
-    for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+    const int idx = blockIdx.y * blockDim.x + threadIdx.x;  // pair index, 0 .. n_heads*half-1
+    if (idx < n_heads * half) {
         const int h = idx / half, i = idx - h * half;
         const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
         const int a = h * hd + i, b = a + half;
-        const float q0 = q[a], q1 = q[b], k0 = k[a], k1 = k[b];
+        const float q0 = q[a], q1 = q[b], k0 = k[a], k1 = k[b], va = v[a], vb2 = v[b];
         q_out[t * (size_t)d + a] = __fsub_rn(__fmul_rn(q0, c), __fmul_rn(q1, s));
         q_out[t * (size_t)d + b] = __fadd_rn(__fmul_rn(q0, s), __fmul_rn(q1, c));
         k_cache[crow + a] = __fsub_rn(__fmul_rn(k0, c), __fmul_rn(k1, s));
         k_cache[crow + b] = __fadd_rn(__fmul_rn(k0, s), __fmul_rn(k1, c));
+        v_cache[crow + a] = va;
+        v_cache[crow + b] = vb2;
     }
-    for (int idx = threadIdx.x; idx < d; idx += blockDim.x) v_cache[crow + idx] = v[idx];
 }
 
 // Decode attention, split over the cache length (flash-decoding style): CTA (b, h, s) handles
@@ -151,6 +200,7 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const float *__restrict__ 
 // merges them and writes the output.
 constexpr int ATT_WARPS = 8;
 constexpr int ATT_MAX_HD = 128;
+constexpr int ATT_UNROLL = 4;
 
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
     const float *__restrict__ q, const float *__restrict__ k_cache, const float *__restrict__ v_cache,
@@ -161,6 +211,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
     const int bh = blockIdx.x / splits, sp = blockIdx.x % splits;
     const int b = bh / n_heads, h = bh % n_heads;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_release_and_wait();
     const int d = n_heads * hd, len = lens[b];
     const int chunk = (len + splits - 1) / splits;
     const int j0 = sp * chunk, j1 = min(len, j0 + chunk);
@@ -177,24 +228,38 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
     const float *kb_ = k_cache + (size_t)b * lmax * d + h * hd;
     const float *vb = v_cache + (size_t)b * lmax * d + h * hd;
     float m = -INFINITY, l = 0.0f;
-    for (int j = j0 + warp; j < j1; j += ATT_WARPS) {
-        const float *kr = kb_ + (size_t)j * d, *vr = vb + (size_t)j * d;
-        float dot = 0.0f, vv[DPL];
+    // ATT_UNROLL positions per warp iteration: all their key and value loads are issued before
+    // the first use, so a warp pays one memory round trip per ATT_UNROLL positions
+    for (int jb = j0 + warp; jb < j1; jb += ATT_WARPS * ATT_UNROLL) {
+        float kk[ATT_UNROLL][DPL], vv[ATT_UNROLL][DPL];
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-            const int p = lane + 32 * i;
-            dot = fmaf(qv[i], p < hd ? kr[p] : 0.0f, dot);
-            vv[i] = p < hd ? vr[p] : 0.0f;
+        for (int u = 0; u < ATT_UNROLL; ++u) {
+            const int j = jb + u * ATT_WARPS;
+            const bool ok = j < j1;
+            const float *kr = kb_ + (size_t)(ok ? j : j0) * d, *vr = vb + (size_t)(ok ? j : j0) * d;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                const int p = lane + 32 * i;
+                kk[u][i] = (ok && p < hd) ? kr[p] : 0.0f;
+                vv[u][i] = (ok && p < hd) ? vr[p] : 0.0f;
+            }
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        dot *= scale;
-        const float m_new = fmaxf(m, dot);
-        const float corr = expf(m - m_new), pj = expf(dot - m_new);
-        l = l * corr + pj;
+        for (int u = 0; u < ATT_UNROLL; ++u) {
+            if (jb + u * ATT_WARPS >= j1) break;  // uniform over the warp
+            float dot = 0.0f;
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) acc[i] = fmaf(pj, vv[i], acc[i] * corr);
-        m = m_new;
+            for (int i = 0; i < DPL; ++i) dot = fmaf(qv[i], kk[u][i], dot);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            dot *= scale;
+            const float m_new = fmaxf(m, dot);
+            const float corr = expf(m - m_new), pj = expf(dot - m_new);
+            l = l * corr + pj;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) acc[i] = fmaf(pj, vv[u][i], acc[i] * corr);
+            m = m_new;
+        }
     }
     if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
 #pragma unroll
@@ -255,8 +320,8 @@ int kb_rmsnorm_quant(const float *x, const float *gamma, size_t n, size_t d, flo
     if (d == 0 || d > (size_t)ROW_REGS * 256) return fail(KB_ERR_UNSUPPORTED, "rmsnorm: dim %zu outside 1..%d", d, ROW_REGS * 256);
     if (xq && (ldq < d || ldq > (size_t)ROW_REGS * 256 || ldq % 16)) return fail(KB_ERR_INVALID, "rmsnorm: bad ldq %zu", ldq);
     if (n == 0) return KB_OK;
-    rmsnorm_quant_kernel<<<(unsigned)n, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, gamma, (int)d, eps, xn, xq, (int)ldq, sx, sumq);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(rmsnorm_quant_kernel, dim3((unsigned)n), dim3(256), static_cast<cudaStream_t>(stream), x, gamma,
+                               (int)d, eps, xn, xq, (int)ldq, sx, sumq);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "rmsnorm launch");
 }
 
@@ -266,8 +331,8 @@ int kb_swiglu_quant(const float *gate_up, size_t n, size_t f, size_t ld, float *
     if (f == 0 || f > (size_t)ROW_REGS * 256 || ld < 2 * f) return fail(KB_ERR_UNSUPPORTED, "swiglu: width %zu outside 1..%d", f, ROW_REGS * 256);
     if (xq && (ldq < f || ldq > (size_t)ROW_REGS * 256 || ldq % 16)) return fail(KB_ERR_INVALID, "swiglu: bad ldq %zu", ldq);
     if (n == 0) return KB_OK;
-    swiglu_quant_kernel<<<(unsigned)n, 256, 0, static_cast<cudaStream_t>(stream)>>>(gate_up, (int)f, ld, h, xq, (int)ldq, sx, sumq);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(swiglu_quant_kernel, dim3((unsigned)n), dim3(256), static_cast<cudaStream_t>(stream), gate_up,
+                               (int)f, ld, h, xq, (int)ldq, sx, sumq);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "swiglu launch");
 }
 
@@ -278,9 +343,9 @@ int kb_rope_kv(const float *qkv, const int *positions, const long long *cache_ro
         return fail(KB_ERR_INVALID, "null pointer");
     if (n_heads < 1 || head_dim < 2 || head_dim % 2) return fail(KB_ERR_INVALID, "rope: head_dim must be even");
     if (n == 0) return KB_OK;
-    rope_kv_kernel<<<(unsigned)n, 256, 0, static_cast<cudaStream_t>(stream)>>>(qkv, positions, cache_rows, cos_table, sin_table,
-                                                                              n_heads, head_dim, q_out, k_cache, v_cache);
-    cudaError_t e = cudaGetLastError();
+    const unsigned chunks = (unsigned)((n_heads * (head_dim / 2) + 255) / 256);
+    cudaError_t e = launch_pdl(rope_kv_kernel, dim3((unsigned)n, chunks), dim3(256), static_cast<cudaStream_t>(stream), qkv,
+                               positions, cache_rows, cos_table, sin_table, n_heads, head_dim, q_out, k_cache, v_cache);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "rope launch");
 }
 
@@ -298,9 +363,9 @@ int kb_attn_decode(const float *q, const float *k_cache, const float *v_cache, c
     if (splits > 1 && (!scratch || scratch_bytes < need)) splits = 1;
     int *counters = reinterpret_cast<int *>(scratch);
     float *parts = scratch ? reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + (bh * sizeof(int) + 255) / 256 * 256) : nullptr;
-    attn_decode_kernel<<<(unsigned)(bh * splits), ATT_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        q, k_cache, v_cache, lens, n_heads, head_dim, lmax, splits, parts, counters, out);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(attn_decode_kernel, dim3((unsigned)(bh * splits)), dim3(ATT_WARPS * 32),
+                               static_cast<cudaStream_t>(stream), q, k_cache, v_cache, lens, n_heads, head_dim, lmax, splits,
+                               parts, counters, out);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "attention launch");
 }
 

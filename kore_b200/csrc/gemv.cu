@@ -361,19 +361,21 @@ bool gemv_supports(const Linear *lin, size_t n) {
     return gemv_smem_bytes(lin->kp, nt) <= 200 * 1024;
 }
 
-// tuning overrides, read once: KB_GEMV_THREADS (128|256), KB_GEMV_PDL (0|1), KB_GEMV_PF (2|4)
+// tuning overrides, read once: KB_GEMV_THREADS (64..256, multiple of 32), KB_GEMV_PDL (0|1), KB_GEMV_PF (2|4),
+// KB_GEMV_MAXCTAS (cap on the grid's x extent; rows are grid-strided)
 static int env_int(const char *name, int dflt) {
     const char *v = getenv(name);
     return v && *v ? atoi(v) : dflt;
 }
 
 template <int NT, int R, int PF, bool FUSED>
-static int launch_one(const GemvParams &p, int tok_groups, cudaStream_t stream) {
+static int launch_one(const GemvParams &p, int tok_groups, bool shared_grid, cudaStream_t stream) {
     static const int env_threads = env_int("KB_GEMV_THREADS", 0);
     static const int env_pdl = env_int("KB_GEMV_PDL", 1);
+    static const int env_maxctas = env_int("KB_GEMV_MAXCTAS", 0);
     const int row_groups = (p.m + R - 1) / R;
     int threads = 256;
-    if (env_threads == 128 || env_threads == 256) threads = env_threads;
+    if (env_threads >= 64 && env_threads <= 256 && env_threads % 32 == 0) threads = env_threads;
     const int nwarps = threads / 32;
     const size_t smem = gemv_smem_bytes((size_t)p.kp, NT);
     auto kern = gemv_kernel<NT, R, PF, FUSED>;
@@ -394,8 +396,12 @@ static int launch_one(const GemvParams &p, int tok_groups, cudaStream_t stream) 
         c_threads = threads; c_smem = smem; c_occ = occ_q; c_sms = sms_q;
     }
     const int occ = c_occ, sms = c_sms;
-    int ctas = (row_groups + nwarps - 1) / nwarps;
+    // shared_grid: two row groups per warp, so a launch leaves room for other streams' launches
+    // and each CTA stages the activations once for twice the weight bytes
+    const int groups_per_cta = shared_grid ? 2 * nwarps : nwarps;
+    int ctas = (row_groups + groups_per_cta - 1) / groups_per_cta;
     if (ctas > sms * occ) ctas = sms * occ;
+    if (env_maxctas > 0 && ctas > env_maxctas) ctas = env_maxctas;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ctas, (unsigned)tok_groups, 1);
     cfg.blockDim = dim3((unsigned)threads, 1, 1);
@@ -413,18 +419,18 @@ static int launch_one(const GemvParams &p, int tok_groups, cudaStream_t stream) 
 }
 
 template <bool FUSED>
-static int dispatch(const GemvParams &p, cudaStream_t stream) {
+static int dispatch(const GemvParams &p, bool sg, cudaStream_t stream) {
     const int n = p.n;
     static const int env_pf = env_int("KB_GEMV_PF", 0);
     if (n == 1) {
         // two chunks in flight per warp at two CTAs per SM measured faster than four chunks at
         // one CTA per SM (register pressure) on 8192-wide rows; the deep variant stays selectable
         const bool deep = env_pf == 4;
-        return deep ? launch_one<1, 4, 4, FUSED>(p, 1, stream) : launch_one<1, 4, 2, FUSED>(p, 1, stream);
+        return deep ? launch_one<1, 4, 4, FUSED>(p, 1, sg, stream) : launch_one<1, 4, 2, FUSED>(p, 1, sg, stream);
     }
-    if (n == 2) return launch_one<2, 4, 2, FUSED>(p, 1, stream);
-    if (n <= 4) return launch_one<4, 2, 2, FUSED>(p, 1, stream);
-    return launch_one<8, 1, 2, FUSED>(p, (n + 7) / 8, stream);
+    if (n == 2) return launch_one<2, 4, 2, FUSED>(p, 1, sg, stream);
+    if (n <= 4) return launch_one<4, 2, 2, FUSED>(p, 1, sg, stream);
+    return launch_one<8, 1, 2, FUSED>(p, (n + 7) / 8, sg, stream);
 }
 
 int launch_gemv(const FwdArgs &a, cudaStream_t stream) {
@@ -445,10 +451,10 @@ int launch_gemv(const FwdArgs &a, cudaStream_t stream) {
     p.n_more = a.y ? a.n_more : 0;
     for (int q = 0; q < MAX_PEERS - 1; ++q) p.y_more[q] = q < p.n_more ? a.y_more[q] : nullptr;
     p.x_vec4 = a.x && (L->k % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
-    if (a.x) return dispatch<true>(p, stream);
+    if (a.x) return dispatch<true>(p, a.shared_grid, stream);
     if ((reinterpret_cast<uintptr_t>(a.xq) & 15) || (a.ldq % 16) || a.ldq < L->kp)
         return fail(KB_ERR_INVALID, "gemv: xq must be 16-byte aligned with ldq >= %zu and ldq %% 16 == 0", L->kp);
-    return dispatch<false>(p, stream);
+    return dispatch<false>(p, a.shared_grid, stream);
 }
 
 }  // namespace kb

@@ -147,11 +147,11 @@ SHAPES = [
 ]
 
 
-@pytest.mark.parametrize("path", ["gemv", "gemm_tc"])
+@pytest.mark.parametrize("path", ["gemv", "gemv_shared", "gemm_tc"])
 @pytest.mark.parametrize("kind,quantiser", [(T, "reference"), (T, "absmean"), (Q, "reference")])
 @pytest.mark.parametrize("m,k,n", SHAPES)
 def test_forward_bit_exact(torch, kb, path, kind, quantiser, m, k, n):
-    if path == "gemv" and n > 40:
+    if path.startswith("gemv") and n > 40:
         pytest.skip("decode kernel is exercised up to a few token groups")
     w = cases.gaussian(1000 + m + k, (m, k), 0.02)
     packed, scales = cases.make_weights(kind, quantiser, w)
@@ -159,7 +159,7 @@ def test_forward_bit_exact(torch, kb, path, kind, quantiser, m, k, n):
     x = cases.gaussian(2000 + n + k, (n, k), 1.0)
     y_ref, acc_ref = kbref.q_forward(kind, packed, scales, bias, m, k, x, threads=4)
     lay = _layer(kb, kind, packed, scales, bias, m, k)
-    p = kb.cabi.PATH_GEMV if path == "gemv" else kb.cabi.PATH_GEMM_TC
+    p = {"gemv": kb.cabi.PATH_GEMV, "gemv_shared": kb.cabi.PATH_GEMV_SHARED, "gemm_tc": kb.cabi.PATH_GEMM_TC}[path]
     y, acc = lay.forward(torch.from_numpy(x).cuda(), path=p, return_acc=True)
     torch.cuda.synchronize()
     st = C.c_int(0)
