@@ -59,8 +59,10 @@ enum {
  * KB_PATH_GEMV_SHARED is the GEMV launched with about half the CTAs (two row groups per warp):
  * a single launch finishes later, but independent layers issued on several streams share the
  * SMs better and their aggregate bandwidth is higher.  Use it when several GEMVs are in
- * flight at once; use KB_PATH_GEMV (or AUTO) for a chain of dependent layers. */
-enum { KB_PATH_AUTO = 0, KB_PATH_GEMV = 1, KB_PATH_GEMM_TC = 2, KB_PATH_GEMV_SHARED = 3 };
+ * flight at once; use KB_PATH_GEMV (or AUTO) for a chain of dependent layers.
+ * KB_PATH_GEMV_MMA is the small-batch kernel (up to 32 tokens whose int8 activations fit in
+ * shared memory): weights stream global -> registers -> warp-level int8 MMA. */
+enum { KB_PATH_AUTO = 0, KB_PATH_GEMV = 1, KB_PATH_GEMM_TC = 2, KB_PATH_GEMV_SHARED = 3, KB_PATH_GEMV_MMA = 4 };
 
 typedef struct kb_linear kb_linear; /* opaque: device-resident 2-bit weights + scales + bias */
 typedef void *kb_stream;            /* a cudaStream_t; NULL = the legacy default stream */

@@ -112,7 +112,7 @@ static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim
     if (!x || (!y && !acc)) return fail(KB_ERR_INVALID, "null activation or output pointer");
     if (ldy != 0 && ldy < L->m) return fail(KB_ERR_INVALID, "ldy %zu smaller than out_features %zu", ldy, L->m);
     if (n == 0) return KB_OK;
-    if (path == KB_PATH_AUTO) path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : KB_PATH_GEMM_TC;
+    if (path == KB_PATH_AUTO) path = auto_path(L, n, false);
     FwdArgs a = {};
     a.lin = L; a.n = n; a.y = y; a.acc = acc; a.ldy = ldy;
     if (path == KB_PATH_GEMV_SHARED) { a.shared_grid = true; path = KB_PATH_GEMV; }
@@ -120,7 +120,7 @@ static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim
         a.x = x;
         return launch_gemv(a, stream);
     }
-    if (path != KB_PATH_GEMM_TC) return fail(KB_ERR_INVALID, "unknown path %d", path);
+    if (path != KB_PATH_GEMM_TC && path != KB_PATH_GEMV_MMA) return fail(KB_ERR_INVALID, "unknown path %d", path);
     const size_t need = workspace_bytes(L, n);
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     bool own = false;
@@ -136,7 +136,7 @@ static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim
     int rc = launch_act_quant(x, n, L->k, xq, L->kp, sx, sumq, stream);
     if (rc == KB_OK) {
         a.xq = xq; a.ldq = L->kp; a.sx = sx; a.sumq = sumq;
-        rc = launch_gemm_tc(a, stream);
+        rc = path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, stream) : launch_gemm_tc(a, stream);
     }
     if (own) {
         cudaError_t e = cudaFreeAsync(ws, stream);
@@ -439,11 +439,12 @@ int kb_linear_forward_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const
     if (ldy != 0 && ldy < L->m) return fail(KB_ERR_INVALID, "ldy %zu smaller than out_features %zu", ldy, L->m);
     if (n == 0) return KB_OK;
     DeviceGuard g(L->device);
-    if (path == KB_PATH_AUTO) path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : KB_PATH_GEMM_TC;
+    if (path == KB_PATH_AUTO) path = auto_path(L, n, true);
     FwdArgs a = {};
     a.lin = L; a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq; a.n = n; a.y = y; a.acc = acc; a.ldy = ldy;
     if (path == KB_PATH_GEMV_SHARED) { a.shared_grid = true; path = KB_PATH_GEMV; }
     if (path == KB_PATH_GEMV) return launch_gemv(a, static_cast<cudaStream_t>(stream));
+    if (path == KB_PATH_GEMV_MMA) return launch_gemv_mma(a, static_cast<cudaStream_t>(stream));
     if (path == KB_PATH_GEMM_TC) return launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
     return fail(KB_ERR_INVALID, "unknown path %d", path);
 }
@@ -458,13 +459,14 @@ int kb_linear_forward_fused(const kb_linear *h, const float *x, const int8_t *xq
     if (n == 0) return KB_OK;
     DeviceGuard g(L->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (path == KB_PATH_AUTO) path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : KB_PATH_GEMM_TC;
+    if (path == KB_PATH_AUTO) path = auto_path(L, n, xq != nullptr);
     FwdArgs a = {};
     a.lin = L; a.n = n; a.y = y; a.ldy = ldy; a.resid = resid;
     if (path == KB_PATH_GEMV_SHARED) { a.shared_grid = true; path = KB_PATH_GEMV; }
     if (xq) {
         a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq;
         if (path == KB_PATH_GEMV) return launch_gemv(a, st);
+        if (path == KB_PATH_GEMV_MMA) return launch_gemv_mma(a, st);
         if (path == KB_PATH_GEMM_TC) return launch_gemm_tc(a, st);
         return fail(KB_ERR_INVALID, "unknown path %d", path);
     }
@@ -472,7 +474,7 @@ int kb_linear_forward_fused(const kb_linear *h, const float *x, const int8_t *xq
         a.x = x;
         return launch_gemv(a, st);
     }
-    if (path != KB_PATH_GEMM_TC) return fail(KB_ERR_INVALID, "unknown path %d", path);
+    if (path != KB_PATH_GEMM_TC && path != KB_PATH_GEMV_MMA) return fail(KB_ERR_INVALID, "unknown path %d", path);
     const size_t need = workspace_bytes(L, n);
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     if (!ws || workspace_bytes_ < need || (reinterpret_cast<uintptr_t>(ws) & 255))
@@ -484,7 +486,7 @@ int kb_linear_forward_fused(const kb_linear *h, const float *x, const int8_t *xq
     int rc = launch_act_quant(x, n, L->k, wq, L->kp, wsx, wsum, st);
     if (rc) return rc;
     a.xq = wq; a.ldq = L->kp; a.sx = wsx; a.sumq = wsum;
-    return launch_gemm_tc(a, st);
+    return path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, st) : launch_gemm_tc(a, st);
 }
 
 int kb_linear_forward_host(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *y) {

@@ -111,6 +111,14 @@ struct FwdArgs {
     // GEMV only: size the grid for launches that overlap with other streams' GEMVs
     bool shared_grid;
 };
+// kernel choice for `n` tokens when the caller passes KB_PATH_AUTO: the dp4a GEMV for one or two
+// tokens (up to four when it also has to quantise, which it does in its prologue), the
+// small-batch MMA kernel up to 32 tokens while their activations fit in shared memory, the
+// tensor-core GEMM above
+int auto_path(const Linear *lin, size_t n, bool prequantised);
+// small-batch kernel on the warp-level MMA (pre-quantised activations, up to 32 tokens)
+bool gemv_mma_supports(const Linear *lin, size_t n);
+int launch_gemv_mma(const FwdArgs &a, cudaStream_t stream);
 // decode GEMV; when args.x is set the activation quantiser is fused into its prologue
 int launch_gemv(const FwdArgs &a, cudaStream_t stream);
 // tcgen05 int8 GEMM; needs pre-quantised activations

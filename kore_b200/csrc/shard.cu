@@ -130,7 +130,10 @@ int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size
     a.n_more = 0;
     for (int q = 0; q < world; ++q)
         if (q != rank) a.y_more[a.n_more++] = y_bases[q] + col_offset;
-    if (path == KB_PATH_AUTO) path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : KB_PATH_GEMM_TC;
+    // up to 8 tokens the GEMV ends in the fused barrier; above, the small-batch kernel or the GEMM
+    // store to the peers and a barrier kernel follows
+    if (path == KB_PATH_AUTO)
+        path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : (gemv_mma_supports(L, n) ? KB_PATH_GEMV_MMA : KB_PATH_GEMM_TC);
     int rc;
     // sync_words_dev = {epoch counter, CTA-done counter, status}
     PeerSync sync = {flag_arrays_dev, sync_words_dev, sync_words_dev ? sync_words_dev + 1 : nullptr,
@@ -160,7 +163,7 @@ int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size
             rc = launch_act_quant(x, n, L->k, xq, L->kp, sx, sumq, st);
             if (rc == KB_OK) {
                 a.xq = xq; a.ldq = L->kp; a.sx = sx; a.sumq = sumq;
-                rc = launch_gemm_tc(a, st);
+                rc = path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, st) : launch_gemm_tc(a, st);
             }
             if (own) cudaFreeAsync(ws, st);
         }

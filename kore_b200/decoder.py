@@ -177,7 +177,7 @@ class BitNetDecoder:
             ck(lib.kb_linear_forward_fused(L["down"].handle, None, B["xq_f"].data_ptr(), self.ld_f, B["sx"].data_ptr(),
                                            B["sum"].data_ptr(), n, B["hidden"].data_ptr(), B["hidden"].data_ptr(), 0,
                                            _cabi.PATH_AUTO, None, 0, sp))
-            launches += 5 + (1 if n > 8 else 0)
+            launches += 5 + (1 if n > 4 else 0)
         self.launches_per_step = launches + 3
         return B
 

@@ -142,24 +142,29 @@ SHAPES = [
     # m, k, n
     (128, 256, 1), (128, 256, 32), (8, 20, 4), (2, 7, 3), (16, 32, 16), (1, 1, 1), (130, 1000, 5),
     (300, 4096, 2), (257, 2304, 8), (64, 5, 9), (200, 640, 70), (129, 384, 130), (256, 512, 300),
+    # small-batch kernel: K steps fewer / more than its 16 warps, ragged rows and tokens
+    (50, 8640, 16), (3200, 3200, 12), (17, 4352, 27),
     # CTA-pair GEMM edges: odd number of 128-row blocks, odd number of 128-byte K slabs, ragged tokens
     (384, 640, 520), (130, 128, 257),
 ]
 
 
-@pytest.mark.parametrize("path", ["gemv", "gemv_shared", "gemm_tc"])
+@pytest.mark.parametrize("path", ["gemv", "gemv_shared", "gemv_mma", "gemm_tc"])
 @pytest.mark.parametrize("kind,quantiser", [(T, "reference"), (T, "absmean"), (Q, "reference")])
 @pytest.mark.parametrize("m,k,n", SHAPES)
 def test_forward_bit_exact(torch, kb, path, kind, quantiser, m, k, n):
     if path.startswith("gemv") and n > 40:
         pytest.skip("decode kernel is exercised up to a few token groups")
+    if path == "gemv_mma" and n > 32:
+        pytest.skip("small-batch kernel takes up to 32 tokens")
     w = cases.gaussian(1000 + m + k, (m, k), 0.02)
     packed, scales = cases.make_weights(kind, quantiser, w)
     bias = cases.gaussian(3, (m,), 0.1) if (m + n) % 2 else None
     x = cases.gaussian(2000 + n + k, (n, k), 1.0)
     y_ref, acc_ref = kbref.q_forward(kind, packed, scales, bias, m, k, x, threads=4)
     lay = _layer(kb, kind, packed, scales, bias, m, k)
-    p = {"gemv": kb.cabi.PATH_GEMV, "gemv_shared": kb.cabi.PATH_GEMV_SHARED, "gemm_tc": kb.cabi.PATH_GEMM_TC}[path]
+    p = {"gemv": kb.cabi.PATH_GEMV, "gemv_shared": kb.cabi.PATH_GEMV_SHARED, "gemv_mma": kb.cabi.PATH_GEMV_MMA,
+         "gemm_tc": kb.cabi.PATH_GEMM_TC}[path]
     y, acc = lay.forward(torch.from_numpy(x).cuda(), path=p, return_acc=True)
     torch.cuda.synchronize()
     st = C.c_int(0)
