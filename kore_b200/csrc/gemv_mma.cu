@@ -60,28 +60,35 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// all threads of the CTA; reached once per row block by every warp, from whichever unrolled
-// copy of the loop body the warp happens to be in
-__device__ __forceinline__ void cta_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory"); }
+// the 16 warps of a group; reached once per row block by every warp of the group, from
+// whichever unrolled copy of the loop body the warp happens to be in
+__device__ __forceinline__ void group_barrier(int grp) {
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(WARPS * 32) : "memory");
+}
 
-template <int NB>  // blocks of 8 tokens
-__global__ void __launch_bounds__(WARPS * 32) gemv_mma_kernel(const MmaGemvParams p) {
+// NB = blocks of 8 tokens; G = groups of 16 warps per CTA.  The groups work on different row
+// blocks and share one staged copy of the activations, which halves the activation traffic
+// from L2 per weight byte compared with two separate CTAs on the SM.
+template <int NB, int G>
+__global__ void __launch_bounds__(G * WARPS * 32, 1) gemv_mma_kernel(const MmaGemvParams p) {
     constexpr int NTOK = NB * 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __shared__ float s_sx[NTOK];
     __shared__ int s_sum[NTOK];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, grp = threadIdx.x / (WARPS * 32), warp = (threadIdx.x >> 5) % WARPS;
+    const int gtid = threadIdx.x % (WARPS * 32);  // thread index inside the group
+    const int vblock = blockIdx.x * G + grp, vgrid = gridDim.x * G;  // the group's place in the row-block rotation
     const int g = lane >> 2, q = lane & 3;
     const int nsteps = (p.kp + 255) >> 8;
     const int chunks = nsteps * 16;
     uint4 *xs = reinterpret_cast<uint4 *>(smem_raw);                               // [chunks][NTOK]
-    int4 *part = reinterpret_cast<int4 *>(smem_raw + (size_t)chunks * NTOK * 16);  // [2][WARPS][NB][32]
+    int4 *part = reinterpret_cast<int4 *>(smem_raw + (size_t)chunks * NTOK * 16) + (size_t)grp * 2 * WARPS * NB * 32;  // [G][2][WARPS][16 * NTOK ints]
     const int row_blocks = (p.m + 15) >> 4;
     const bool has_steps = warp < nsteps;  // this warp's steps of a block: warp, warp + WARPS, ...
 
     // ---- weight pipeline: PF steps x (row g, row g + 8) in registers ----
     uint4 buf[PF][2];
-    int lrb = blockIdx.x, lks = warp;  // load cursor over (row block, step)
+    int lrb = vblock, lks = warp;  // load cursor over (row block, step)
     auto issue = [&](uint4(&dst)[2]) {
         const int kbyte = lks * 64 + q * 16;  // byte offset inside the packed row
         const bool ok = has_steps && lrb < row_blocks && kbyte * 4 < p.kp;
@@ -89,7 +96,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_mma_kernel(const MmaGemvParam
         dst[0] = ok ? ld_stream_v4(src) : make_uint4(0, 0, 0, 0);
         dst[1] = ok ? ld_stream_v4(src + 8 * p.row_bytes) : make_uint4(0, 0, 0, 0);
         lks += WARPS;
-        if (lks >= nsteps) { lks = warp; lrb += gridDim.x; }
+        if (lks >= nsteps) { lks = warp; lrb += vgrid; }
     };
 #pragma unroll
     for (int s = 0; s < PF; ++s) issue(buf[s]);
@@ -97,14 +104,32 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_mma_kernel(const MmaGemvParam
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    // ---- activations -> shared memory ----
-    for (int idx = threadIdx.x; idx < chunks * NTOK; idx += blockDim.x) {
-        const int n_lo = idx & 7, rest = idx >> 3;
-        const int c = rest % chunks, nb = rest / chunks;
-        const int n = nb * 8 + n_lo;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (n < p.n && c * 16 < p.kp) v = *reinterpret_cast<const uint4 *>(p.xq + (size_t)n * p.ldq + (size_t)c * 16);
-        xs[c * NTOK + (n ^ (2 * ((c >> 2) & 3)))] = v;
+    // ---- activations -> shared memory (loads of four items in flight per thread) ----
+    {
+        const int total = chunks * NTOK;
+        constexpr int U = 4;
+        const unsigned rot = total > 0 ? (unsigned)((blockIdx.x * 2654435761u) % (unsigned)total) & ~7u : 0u;
+        for (int base = threadIdx.x; base < total; base += U * G * WARPS * 32) {
+            uint4 v[U];
+            int slot[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                // every CTA copies the same bytes: each starts at a different offset, so that at any
+                // moment the SMs ask different L2 lines instead of queueing on one
+                const int lin = base + u * G * WARPS * 32;
+                const int idx = lin < total ? (int)(((unsigned)lin + rot) % (unsigned)total) : total;
+                const int n_lo = idx & 7, rest = idx >> 3;
+                const int c = rest % chunks, nb = rest / chunks;
+                const int n = nb * 8 + n_lo;
+                v[u] = make_uint4(0, 0, 0, 0);
+                slot[u] = idx < total ? c * NTOK + (n ^ (2 * ((c >> 2) & 3))) : -1;
+                if (idx < total && n < p.n && c * 16 < p.kp)
+                    v[u] = *reinterpret_cast<const uint4 *>(p.xq + (size_t)n * p.ldq + (size_t)c * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (slot[u] >= 0) xs[slot[u]] = v[u];
+        }
     }
     if (threadIdx.x < NTOK) {
         s_sx[threadIdx.x] = (int)threadIdx.x < p.n ? p.sx[threadIdx.x] : 1.0f;
@@ -120,9 +145,11 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_mma_kernel(const MmaGemvParam
     // barrier per block), and the threads share the epilogue: thread o < 16 * NTOK owns output
     // (row o % 16, token o / 16) of every block.  Its row scale, bias and residual are fetched
     // when the block starts, so the epilogue itself waits on no global load.
-    const int row_l = threadIdx.x & 15, tok = threadIdx.x >> 4;
-    const bool owner = (int)threadIdx.x < 16 * NTOK && tok < p.n;
-    const int src_word = (((tok >> 3) * 32 + (row_l & 7) * 4 + ((tok & 7) >> 1)) << 2) + (tok & 1) + 2 * (row_l >> 3);
+    const int row_l = gtid & 15, tok = gtid >> 4;
+    const bool owner = gtid < 16 * NTOK && tok < p.n;
+    // partials are stored [warp][token][row ^ 8 * ((token >> 1) & 1)]: the fragment stores are
+    // two-way conflicted at worst and the epilogue reads are conflict-free
+    const int src_word = tok * 16 + (row_l ^ (8 * ((tok >> 1) & 1)));
     const float my_sx = owner ? s_sx[tok] : 1.0f;
     const int my_sum = owner ? s_sum[tok] : 0;
     float e_sw = 0.0f, e_bias = 0.0f, e_res = 0.0f;
@@ -136,19 +163,25 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_mma_kernel(const MmaGemvParam
     };
     int parity = 0;
     auto finish_block = [&](int rb) {
-        int4 *mine = part + ((size_t)(parity * WARPS + warp) * NB) * 32;
+        int *mine = reinterpret_cast<int *>(part) + (size_t)(parity * WARPS + warp) * (16 * NTOK);
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-            mine[nb * 32 + lane] = make_int4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
+            // lane (g, q) holds rows g, g + 8 x tokens nb * 8 + 2q, + 1
+            int *dst = mine + (nb * 8 + 2 * q) * 16;
+            const int r0 = g ^ (8 * (q & 1)), r1 = (g + 8) ^ (8 * (q & 1));
+            dst[r0] = acc[nb][0];
+            dst[16 + r0] = acc[nb][1];
+            dst[r1] = acc[nb][2];
+            dst[16 + r1] = acc[nb][3];
             acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0;
         }
-        cta_barrier();
+        group_barrier(grp);
         const int row = rb * 16 + row_l;
         if (owner && row < p.m) {
-            const int *pi = reinterpret_cast<const int *>(part + (size_t)parity * WARPS * NB * 32) + src_word;
+            const int *pi = reinterpret_cast<const int *>(part) + (size_t)parity * WARPS * (16 * NTOK) + src_word;
             int sum = 0;
 #pragma unroll
-            for (int w = 0; w < WARPS; ++w) sum += pi[w * NB * 128];
+            for (int w = 0; w < WARPS; ++w) sum += pi[w * (16 * NTOK)];
             const int a = p.mul * sum - p.off * my_sum;
             const size_t off = (size_t)tok * p.ldy + row;
             if (p.acc) p.acc[off] = a;
@@ -160,11 +193,11 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_mma_kernel(const MmaGemvParam
             }
         }
         parity ^= 1;
-        prefetch_epilogue(rb + gridDim.x);
+        prefetch_epilogue(rb + vgrid);
     };
-    prefetch_epilogue(blockIdx.x);
+    prefetch_epilogue(vblock);
 
-    int crb = blockIdx.x, cks = warp;  // consume cursor
+    int crb = vblock, cks = warp;  // consume cursor
     while (crb < row_blocks) {
 #pragma unroll
         for (int s = 0; s < PF; ++s) {
@@ -192,7 +225,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_mma_kernel(const MmaGemvParam
                 if (!has_steps || cks >= nsteps) {
                     finish_block(crb);
                     cks = warp;
-                    crb += gridDim.x;
+                    crb += vgrid;
                 }
             }
         }
@@ -200,14 +233,17 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_mma_kernel(const MmaGemvParam
     if (p.n_more) __threadfence_system();
 }
 
+constexpr int groups_for(int nb) { return nb == 1 ? 2 : 1; }  // 16 tokens and more need the registers
+
 size_t mma_smem_bytes(size_t kp, int nb) {
     const size_t nsteps = (kp + 255) / 256;
-    return nsteps * 256 * (size_t)(nb * 8) + (size_t)nb * 2 * WARPS * 512;
+    return nsteps * 256 * (size_t)(nb * 8) + (size_t)groups_for(nb) * nb * 2 * WARPS * 512;
 }
 
 template <int NB>
 int launch_nb(const MmaGemvParams &p, cudaStream_t stream) {
-    auto kern = gemv_mma_kernel<NB>;
+    constexpr int G = groups_for(NB);
+    auto kern = gemv_mma_kernel<NB, G>;
     const size_t smem = mma_smem_bytes((size_t)p.kp, NB);
     if (smem > 40 * 1024) {  // the static arrays count toward the 48 KB default limit too
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -218,15 +254,18 @@ int launch_nb(const MmaGemvParams &p, cudaStream_t stream) {
     if (c_smem != smem) {
         int occ = 0, dev = 0, sms = 148;
         cudaGetDevice(&dev);
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, WARPS * 32, smem) != cudaSuccess || occ < 1) occ = 1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, G * WARPS * 32, smem) != cudaSuccess || occ < 1) occ = 1;
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
         c_smem = smem; c_occ = occ; c_sms = sms;
     }
     const int row_blocks = (p.m + 15) / 16;
-    int ctas = row_blocks < c_sms * c_occ ? row_blocks : c_sms * c_occ;
+    const int want = (row_blocks + G - 1) / G;
+    int ctas = want < c_sms * c_occ ? want : c_sms * c_occ;
+    static const int env_maxctas = [] { const char *v = getenv("KB_MMA_MAXCTAS"); return v && *v ? atoi(v) : 0; }();
+    if (env_maxctas > 0 && ctas > env_maxctas) ctas = env_maxctas;  // tuning override
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ctas, 1, 1);
-    cfg.blockDim = dim3(WARPS * 32, 1, 1);
+    cfg.blockDim = dim3(G * WARPS * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
