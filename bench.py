@@ -225,7 +225,7 @@ def main():
     ap.add_argument("--fused-quant", action="store_true",
                     help="N=1: run the activation quantiser inside the GEMV prologue (one launch per layer)")
     ap.add_argument("--no-decoder", action="store_true", help="skip the BitNet-3B-shaped decoder measurement")
-    ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "prefill_up", "prefill_down"],
+    ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "small_batch", "prefill_up", "prefill_down"],
                     help="run one small case and print its own JSON line (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -441,7 +441,7 @@ def main():
 
 def single_case(torch, lib, _cabi, nn, kernels, dev, args):
     """One kernel on one small case, a handful of eager launches: the command profiled with ncu."""
-    shapes = {"gemv_big": (28672, 8192, 1, 3), "gemv_4096": (4096, 4096, 1, 40),
+    shapes = {"gemv_big": (28672, 8192, 1, 3), "gemv_4096": (4096, 4096, 1, 40), "small_batch": (28672, 8192, 16, 3),
               "prefill_up": (11008, 4096, 2048, 1), "prefill_down": (4096, 11008, 2048, 1)}
     m, k, n, copies = shapes[args.only]
     w = (torch.randn((m, k), generator=torch.Generator().manual_seed(7)) * 0.02).numpy()
@@ -452,7 +452,7 @@ def single_case(torch, lib, _cabi, nn, kernels, dev, args):
     x = torch.from_numpy(gaussian(8, (n, k), 1.0)).to(dev)
     y = torch.empty((n, m), dtype=torch.float32, device=dev)
     xq, sx, sumq = kernels.quantize_act_i8(x)
-    path = _cabi.PATH_GEMV if n == 1 else _cabi.PATH_GEMM_TC
+    path = _cabi.PATH_GEMV if n == 1 else (_cabi.PATH_GEMV_MMA if n <= 32 else _cabi.PATH_GEMM_TC)
     sp = torch.cuda.current_stream().cuda_stream
 
     def once():
