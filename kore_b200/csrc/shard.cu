@@ -130,10 +130,9 @@ int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size
     a.n_more = 0;
     for (int q = 0; q < world; ++q)
         if (q != rank) a.y_more[a.n_more++] = y_bases[q] + col_offset;
-    // up to 8 tokens the GEMV ends in the fused barrier; above, the small-batch kernel or the GEMM
-    // store to the peers and a barrier kernel follows
-    if (path == KB_PATH_AUTO)
-        path = (n <= 8 && gemv_supports(L, n)) ? KB_PATH_GEMV : (gemv_mma_supports(L, n) ? KB_PATH_GEMV_MMA : KB_PATH_GEMM_TC);
+    // the GEMV (a few tokens) ends in the fused barrier; the small-batch kernel and the GEMM store
+    // to the peers and a barrier kernel follows
+    if (path == KB_PATH_AUTO) path = auto_path(L, n, false);
     int rc;
     // sync_words_dev = {epoch counter, CTA-done counter, status}
     PeerSync sync = {flag_arrays_dev, sync_words_dev, sync_words_dev ? sync_words_dev + 1 : nullptr,
