@@ -215,6 +215,14 @@ int kb_ternary_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scal
 int kb_quat_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scales, size_t scales_len,
                    const float *b, float *c, size_t m, size_t n, size_t k);
 
+/* ternary_ternary_matmul (cpu_ternary_matmul.rs:131-193): both operands base-243 rows,
+ * a [M, ceil(K/5)] with a_scales [M], b [N, ceil(K/5)] with b_scales [N], integer dot product,
+ * c[m,n] = float(dot) * a_scale[m] * b_scale[n], c [M,N] f32 (host pointers).  Too-short inputs
+ * return the storage error "packed arrays too small" (:142-146). */
+int kb_ternary_ternary_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scales,
+                              const uint8_t *b_packed, size_t b_len, const float *b_scales, float *c,
+                              size_t m, size_t n, size_t k);
+
 /* pack_weights_ternary (cpu_ternary_matmul.rs:198-240) and pack_weights_quaternary
  * (cpu_quat_matmul.rs:174-214), computed on the device: f32 [M,K] host in,
  * wire-format bytes and per-row scales out (host). */

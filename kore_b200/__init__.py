@@ -6,7 +6,7 @@ kore-kernels function API.  There is no CPU implementation in this package.
 """
 from . import _cabi
 from ._cabi import KoreError
-from .nn import BitLinear, QuatLinear
+from .nn import BitLinear, QLoraLinear, QuatLinear
 
-__all__ = ["BitLinear", "QuatLinear", "KoreError", "_cabi"]
+__all__ = ["BitLinear", "QuatLinear", "QLoraLinear", "KoreError", "_cabi"]
 __version__ = "0.1.0"

@@ -49,6 +49,7 @@ SIGNATURES = {
     "kb_static_scratch_bytes": (_sz, []),
     "kb_ternary_matmul": (C.c_int, [_vp, _sz, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
     "kb_quat_matmul": (C.c_int, [_vp, _sz, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
+    "kb_ternary_ternary_matmul": (C.c_int, [_vp, _sz, _vp, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
     "kb_pack_weights_ternary": (C.c_int, [_vp, _sz, _sz, C.c_float, _vp, _sz, _vp, _sz, C.c_int]),
     "kb_pack_weights_quaternary": (C.c_int, [_vp, _sz, _sz, _vp, _sz, _vp, _sz, C.c_int]),
     "kb_linear_forward_sharded": (C.c_int, [_vp, _vp, _sz, _sz, _vp, C.c_int, C.c_int, _sz, _sz, C.c_int, _vp, _sz, _vp, _vp, _vp]),

@@ -291,6 +291,49 @@ static int one_shot(int kind, const uint8_t *a_packed, size_t a_len, const float
     return rc;
 }
 
+// C[M,N] = (sum_k a[m,k] * b[n,k]) * a_scale[m] * b_scale[n], both operands base-243 rows: B's
+// trits take the place of the int8 activations (scale b_scale[n], code sum = sum of trits), so
+// the integer accumulation and the two separately rounded multiplies are the forward path's own.
+static int ternary_ternary(const uint8_t *a_packed, size_t a_len, const float *a_scales, const uint8_t *b_packed,
+                           size_t b_len, const float *b_scales, float *c, size_t m, size_t n, size_t k) {
+    if (!a_packed || !a_scales || !b_packed || !b_scales || !c) return fail(KB_ERR_INVALID, "null pointer");
+    const size_t kpw = (k + 4) / 5;
+    if (a_len < m * kpw || b_len < n * kpw) return fail(KB_ERR_STORAGE, "packed arrays too small");
+    if (m == 0 || n == 0) return KB_OK;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    Linear *L = nullptr;
+    int rc = create_from_wire(KB_TERNARY, a_packed, a_len, a_scales, m, nullptr, m, k, device, &L);
+    if (rc) return rc;
+    cudaStream_t st = cudaStreamPerThread;
+    uint8_t *dwire = nullptr;
+    int8_t *xq = nullptr;
+    float *sx = nullptr, *dy = nullptr, *dc = nullptr;
+    int32_t *sumq = nullptr;
+    const size_t yb = n * m * sizeof(float);
+    if ((e = cudaMalloc(&dwire, n * kpw)) != cudaSuccess || (e = cudaMalloc(&xq, n * L->kp)) != cudaSuccess ||
+        (e = cudaMalloc(&sx, n * sizeof(float))) != cudaSuccess || (e = cudaMalloc(&sumq, n * sizeof(int32_t))) != cudaSuccess ||
+        (e = cudaMalloc(&dy, yb)) != cudaSuccess || (e = cudaMalloc(&dc, yb)) != cudaSuccess)
+        rc = cuda_fail(e, "one-shot allocation");
+    if (rc == KB_OK && (e = cudaMemcpyAsync(dwire, b_packed, n * kpw, cudaMemcpyHostToDevice, st)) != cudaSuccess) rc = cuda_fail(e, "b upload");
+    if (rc == KB_OK && (e = cudaMemcpyAsync(sx, b_scales, n * sizeof(float), cudaMemcpyHostToDevice, st)) != cudaSuccess) rc = cuda_fail(e, "scale upload");
+    if (rc == KB_OK) rc = launch_decode_trits_i8(dwire, n, k, xq, L->kp, sumq, st);
+    if (rc == KB_OK) {
+        FwdArgs a = {};
+        a.lin = L; a.xq = xq; a.ldq = L->kp; a.sx = sx; a.sumq = sumq; a.n = n; a.y = dy; a.ldy = 0;
+        const int path = auto_path(L, n, true);
+        rc = path == KB_PATH_GEMV ? launch_gemv(a, st) : (path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, st) : launch_gemm_tc(a, st));
+    }
+    if (rc == KB_OK) rc = launch_transpose_f32(dy, n, m, dc, st);  // [N,M] -> [M,N]
+    if (rc == KB_OK && (e = cudaMemcpyAsync(c, dc, yb, cudaMemcpyDeviceToHost, st)) != cudaSuccess) rc = cuda_fail(e, "c download");
+    e = cudaStreamSynchronize(st);
+    if (rc == KB_OK && e != cudaSuccess) rc = cuda_fail(e, "stream synchronize");
+    cudaFree(dwire); cudaFree(xq); cudaFree(sx); cudaFree(sumq); cudaFree(dy); cudaFree(dc);
+    free_linear(L);
+    return rc;
+}
+
 static int pack_weights(int kind, const float *w, size_t m, size_t k, float threshold, uint8_t *packed,
                         size_t packed_len, float *scales, size_t scales_len, int device) {
     if (!w || !packed || !scales) return fail(KB_ERR_INVALID, "null pointer");
@@ -499,6 +542,11 @@ int kb_linear_forward_host(const kb_linear *h, const float *x, size_t n, size_t 
 int kb_ternary_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scales, size_t scales_len,
                       const float *b, float *c, size_t m, size_t n, size_t k) {
     return one_shot(KB_TERNARY, a_packed, a_len, a_scales, scales_len, b, c, m, n, k);
+}
+
+int kb_ternary_ternary_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scales, const uint8_t *b_packed,
+                              size_t b_len, const float *b_scales, float *c, size_t m, size_t n, size_t k) {
+    return ternary_ternary(a_packed, a_len, a_scales, b_packed, b_len, b_scales, c, m, n, k);
 }
 
 int kb_quat_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scales, size_t scales_len, const float *b,

@@ -78,6 +78,9 @@ int launch_export_wire(int kind, const uint8_t *w2, size_t row_bytes, size_t m, 
 int launch_dequantize(int kind, const uint8_t *w2, size_t row_bytes, const float *scales, size_t m,
                       size_t k, float *w, cudaStream_t stream);
 int launch_transpose_f32(const float *src, size_t rows, size_t cols, float *dst, cudaStream_t stream);
+// base-243 rows [n][ceil(k/5)] -> int8 trits [n][ldq] (tail zero) + per-row sums
+int launch_decode_trits_i8(const uint8_t *wire, size_t n, size_t k, int8_t *xq, size_t ldq, int32_t *sumq,
+                           cudaStream_t stream);
 
 // State of the flag barrier between the ranks of a sharded layer (all device pointers).
 struct PeerSync {

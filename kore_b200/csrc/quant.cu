@@ -143,6 +143,32 @@ int launch_repack_wire(int kind, const uint8_t *wire, size_t m, size_t k, uint8_
     return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "repack launch");
 }
 
+// base-243 rows -> int8 trits [n][ldq] (tail zero) and their per-row sums: a ternary operand in
+// the role of the quantised activations (both-operands-ternary product).  One CTA per row.
+__global__ void __launch_bounds__(256) decode_trits_i8_kernel(const uint8_t *__restrict__ wire, int k, int kpw,
+                                                              int8_t *__restrict__ xq, int ldq,
+                                                              int32_t *__restrict__ sumq) {
+    __shared__ int red[32];
+    const uint8_t *row = wire + blockIdx.x * (size_t)kpw;
+    int8_t *dst = xq + blockIdx.x * (size_t)ldq;
+    int local = 0;
+    for (int kk = threadIdx.x; kk < ldq; kk += blockDim.x) {
+        const int t = kk < k ? (int)trit_code_of_byte(row[kk / 5], kk % 5) - 1 : 0;
+        dst[kk] = (int8_t)t;
+        local += t;
+    }
+    local = block_reduce_sum(local, red);
+    if (threadIdx.x == 0) sumq[blockIdx.x] = local;
+}
+
+int launch_decode_trits_i8(const uint8_t *wire, size_t n, size_t k, int8_t *xq, size_t ldq, int32_t *sumq,
+                           cudaStream_t stream) {
+    if (n == 0) return KB_OK;
+    decode_trits_i8_kernel<<<(unsigned)n, 256, 0, stream>>>(wire, (int)k, (int)((k + 4) / 5), xq, (int)ldq, sumq);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "trit decode launch");
+}
+
 // per-row max|w| -> scale (mode 0: absmax, mode 1: absmax/3), 1.0 below 1e-8
 __global__ void __launch_bounds__(256) row_scale_kernel(const float *__restrict__ w, int k, int mode,
                                                         float *__restrict__ scales) {

@@ -37,6 +37,21 @@ def quat_matmul(a_packed, a_scales, b, m: int, n: int, k: int) -> np.ndarray:
     return _one_shot(_cabi.lib().kb_quat_matmul, a_packed, a_scales, b, m, n, k)
 
 
+def ternary_ternary_matmul(a_packed, a_scales, b_packed, b_scales, m: int, n: int, k: int) -> np.ndarray:
+    """C[M,N] = (ternary(A)[M,K] . ternary(B)[N,K]) * a_scales[M] * b_scales[N], integer dot products
+    (both operands base-243 rows; cpu_ternary_matmul.rs:131-193)."""
+    a = np.ascontiguousarray(a_packed, dtype=np.uint8).ravel()
+    b = np.ascontiguousarray(b_packed, dtype=np.uint8).ravel()
+    sa = np.ascontiguousarray(a_scales, dtype=np.float32).ravel()
+    sb = np.ascontiguousarray(b_scales, dtype=np.float32).ravel()
+    if sa.size < m or sb.size < n:
+        raise KoreError(_cabi.ERR_STORAGE, "scales too small")
+    c = np.zeros((m, n), np.float32)
+    _cabi.check(_cabi.lib().kb_ternary_ternary_matmul(a.ctypes.data, a.size, sa.ctypes.data, b.ctypes.data, b.size,
+                                                      sb.ctypes.data, c.ctypes.data, m, n, k))
+    return c
+
+
 def pack_weights_ternary(weights, m: int, k: int, threshold: float, device: int = 0):
     """(packed base-243 bytes [M*ceil(K/5)], scales [M]) computed on the device."""
     w = np.ascontiguousarray(weights, dtype=np.float32).reshape(m, k)

@@ -274,3 +274,90 @@ class QuatLinear(_QuantLinear):
     def __repr__(self):  # Display impl, quat_linear.rs:227-238
         return (f"QuatLinear(in={self.in_features}, out={self.out_features}, "
                 f"bias={'true' if self._bias is not None else 'false'}, compression={self.compression_ratio():.1f}x)")
+
+
+def lora_a_init(rank: int, in_features: int) -> np.ndarray:
+    """The deterministic initial ``lora_a`` of ``QLoraLinear`` (lora.rs:219-225,247-253):
+    x_i = ((i * 2654435761 + 1013904223) & 0xFFFFFF) / 0xFFFFFF, a_i = (2 x_i - 1) * sqrt(1 / in)."""
+    i = np.arange(rank * in_features, dtype=np.uint64)
+    h = (i * np.uint64(2654435761) + np.uint64(1013904223)) & np.uint64(0xFFFFFF)
+    x = h.astype(np.float32) / np.float32(0xFFFFFF)
+    a_scale = np.sqrt(np.float32(1.0) / np.float32(in_features)).astype(np.float32)
+    return ((x * np.float32(2.0) - np.float32(1.0)) * a_scale).astype(np.float32).reshape(rank, in_features)
+
+
+class QLoraLinear:
+    """Quantized base + low-rank adapters (``crates/kore-nn/src/lora.rs:190-357``):
+
+        y = base(x) + ((x @ A^T) @ B^T) * (alpha / rank) (+ bias)
+
+    ``base`` is a BitLinear on the CUDA path; the adapter product (two thin dense f32 matmuls,
+    rank columns wide) runs as torch matmuls on the same stream and enters the base
+    projection's epilogue as its residual, so the sum is formed in the reference's order
+    (base output, then the adapter term, then the bias).  ``lora_a`` [rank, in] starts from the
+    reference's deterministic pattern, ``lora_b`` [out, rank] from zero."""
+
+    def __init__(self, base: BitLinear, rank: int, alpha: float, bias=None):
+        import torch
+
+        if base._bias is not None:
+            raise KoreError(_cabi.ERR_INVALID, "the base layer of QLoraLinear carries no bias; pass it to QLoraLinear")
+        self.base, self.rank, self.alpha = base, int(rank), float(alpha)
+        self.in_features, self.out_features = base.in_features, base.out_features
+        dev = f"cuda:{base.device}"
+        self.lora_a = torch.from_numpy(lora_a_init(self.rank, self.in_features)).to(dev)
+        self.lora_b = torch.zeros((self.out_features, self.rank), dtype=torch.float32, device=dev)
+        self.bias = None if bias is None else torch.as_tensor(np.asarray(bias, np.float32)).to(dev)
+        self.training = True
+
+    @classmethod
+    def from_linear(cls, weight, bias, rank: int, alpha: float, threshold: float, *, device: int = 0):
+        """lora.rs:207-240: quantise a dense layer's weight [out, in] with the reference rule"""
+        return cls(BitLinear.new(weight, None, threshold, device=device), rank, alpha, bias)
+
+    @classmethod
+    def from_bit_linear(cls, base: BitLinear, rank: int, alpha: float):
+        return cls(base, rank, alpha, None)
+
+    def trainable_params(self) -> int:
+        return self.rank * self.in_features + self.out_features * self.rank + (0 if self.bias is None else self.bias.numel())
+
+    def base_compression_ratio(self) -> float:
+        return self.base.compression_ratio()
+
+    def forward(self, x):
+        """x: CUDA float32 tensor [..., in] -> [..., out]"""
+        import torch
+
+        if not _is_torch(x) or not x.is_cuda or x.dtype != torch.float32:
+            raise KoreError(_cabi.ERR_DTYPE, "QLoraLinear.forward expects a CUDA float32 tensor")
+        if x.dim() == 0 or x.shape[-1] != self.in_features:
+            raise KoreError(_cabi.ERR_SHAPE, f"shape mismatch: expected [{self.in_features}], got {list(x.shape)}")
+        lead = tuple(x.shape[:-1])
+        x2 = x.reshape(-1, self.in_features).contiguous()
+        n = x2.shape[0]
+        scaling = self.alpha / self.rank
+        lora_out = ((x2 @ self.lora_a.t()) @ self.lora_b.t()) * scaling
+        y = torch.empty((n, self.out_features), dtype=torch.float32, device=x.device)
+        lib = _cabi.lib()
+        ws_bytes = max(int(lib.kb_linear_workspace_bytes(self.base.handle, n)), 256)
+        ws = torch.empty(ws_bytes + 256, dtype=torch.uint8, device=x.device)
+        ws_ptr = (ws.data_ptr() + 255) // 256 * 256
+        _cabi.check(lib.kb_linear_forward_fused(self.base.handle, x2.data_ptr(), None, 0, None, None, n, lora_out.data_ptr(),
+                                                y.data_ptr(), 0, PATH_AUTO, ws_ptr, ws_bytes,
+                                                _current_stream_ptr(x.device.index)))
+        if self.bias is not None:
+            y += self.bias
+        return y.reshape(*lead, self.out_features)
+
+    __call__ = forward
+
+    def parameters(self):
+        return [self.lora_a, self.lora_b] + ([] if self.bias is None else [self.bias])
+
+    def named_parameters(self):
+        return [("lora_a", self.lora_a), ("lora_b", self.lora_b)] + ([] if self.bias is None else [("bias", self.bias)])
+
+    def __repr__(self):  # Display impl, lora.rs:360-372
+        return (f"QLoraLinear(in={self.in_features}, out={self.out_features}, rank={self.rank}, alpha={self.alpha:g}, "
+                f"base_compression={self.base_compression_ratio():.1f}x, trainable={self.trainable_params()})")

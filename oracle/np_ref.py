@@ -133,3 +133,27 @@ def dequant(acc, sw, sx, bias=None):
     if bias is not None:
         y = (y + np.asarray(bias, f32)[None, :]).astype(f32)
     return y
+
+
+def qlora_forward(base_out, x, lora_a, lora_b, alpha, rank, bias=None):
+    """QLoraLinear::forward after the base projection (crates/kore-nn/src/lora.rs:296-317):
+    output = base_out + ((x @ A^T) @ B^T) * (alpha / rank), then + bias.  f32 throughout; the
+    two dense products are summed in numpy's order, so comparisons against another f32
+    implementation of them need a tolerance."""
+    f32 = np.float32
+    scaling = f32(alpha) / f32(rank)
+    lora = ((np.asarray(x, f32) @ np.asarray(lora_a, f32).T).astype(f32) @ np.asarray(lora_b, f32).T).astype(f32) * scaling
+    out = (np.asarray(base_out, f32) + lora.astype(f32)).astype(f32)
+    if bias is not None:
+        out = (out + np.asarray(bias, f32)).astype(f32)
+    return out
+
+
+def lora_a_init(rank, in_features):
+    """lora.rs:219-225 with Python integers (pure loop; small sizes only)"""
+    a_scale = np.sqrt(np.float32(1.0) / np.float32(in_features)).astype(np.float32)
+    out = np.zeros(rank * in_features, np.float32)
+    for i in range(rank * in_features):
+        x = np.float32((i * 2654435761 + 1013904223) & 0xFFFFFF) / np.float32(0xFFFFFF)
+        out[i] = (x * np.float32(2.0) - np.float32(1.0)) * a_scale
+    return out.reshape(rank, in_features)

@@ -372,3 +372,32 @@ def test_concurrent_forward_from_many_threads(torch, kb):
     [t.join() for t in ts]
     for o, r in zip(outs, refs):
         assert (o == r).all()
+
+
+# ---- both operands ternary (cpu_ternary_matmul.rs:131-193) ---------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(2, 2, 2), (8, 4, 20), (16, 16, 32), (130, 70, 1000), (300, 3, 77), (64, 200, 640), (5, 1, 1)])
+def test_ternary_ternary_matmul(kb, m, n, k):
+    a = cases.gaussian(7000 + m + k, (m, k), 0.02)
+    b = cases.gaussian(7100 + n + k, (n, k), 0.02)
+    if (m, n, k) == (2, 2, 2):  # the reference's own case (:293-307)
+        a = np.array([[1.0, -1.0], [0.0, 1.0]], np.float32)
+        b = np.array([[1.0, 0.0], [-1.0, 1.0]], np.float32)
+    pa, sa = kbref.pack_weights_ternary(a, m, k, 0.3)
+    pb, sb = kbref.pack_weights_ternary(b, n, k, 0.3)
+    c_ref = kbref.ternary_ternary_matmul(pa, sa, pb, sb, m, n, k)
+    c = kb.kernels.ternary_ternary_matmul(pa, sa, pb, sb, m, n, k)
+    assert c.shape == (m, n)
+    assert (c == c_ref).all()
+    if (m, n, k) == (2, 2, 2):
+        assert (c == np.array([[1, -2], [0, 1]], np.float32)).all()
+
+
+@pytest.mark.gpu
+def test_ternary_ternary_matmul_errors(kb):
+    from kore_b200 import KoreError
+
+    pa, sa = kbref.pack_weights_ternary(cases.gaussian(1, (4, 10), 0.02), 4, 10, 0.3)
+    with pytest.raises(KoreError) as e:
+        kb.kernels.ternary_ternary_matmul(pa[:-1], sa, pa, sa, 4, 4, 10)
+    assert "packed arrays too small" in str(e.value)  # :142-146
