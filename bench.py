@@ -624,7 +624,8 @@ def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, 
     bp, bs = big.packed_weights(), big.scales()
     bigpool = [big] + [nn.BitLinear.from_packed(bp, bs, None, 8192, 28672, device=dev.index) for _ in range(3)]
     del wbig
-    for nb in (1, 8):
+    # batch 1: dp4a GEMV; 8 and 16: the kernel KB_PATH_AUTO picks (small-batch MMA kernel)
+    for nb in (1, 8, 16):
         xb = torch.from_numpy(gaussian(5002, (nb, 8192), 1.0)).to(dev)
         yb = torch.empty((nb, 28672), dtype=torch.float32, device=dev)
         xqb, sxb, smb = kernels.quantize_act_i8(xb)
@@ -632,7 +633,7 @@ def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, 
         def bigstep():
             for lay in bigpool:
                 _cabi.check(lib.kb_linear_forward_q8(lay.handle, xqb.data_ptr(), xqb.stride(0), sxb.data_ptr(), smb.data_ptr(),
-                                                     nb, yb.data_ptr(), 0, None, _cabi.PATH_GEMV, sptr))
+                                                     nb, yb.data_ptr(), 0, None, _cabi.PATH_AUTO, sptr))
 
         sec, _ = time_graph(torch, bigstep, steps, warm, stream)
         gbs = len(bigpool) * gemv_bytes(28672, 8192, nb) / sec / 1e9
@@ -648,11 +649,14 @@ def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, 
     for nb in (1, 8):
         x = torch.from_numpy(gaussian(2002, (nb, K_DEC), 1.0)).to(dev)
         y = torch.empty((nb, M_DEC), dtype=torch.float32, device=dev)
+        ws_bytes = max(int(lib.kb_linear_workspace_bytes(qproto.handle, nb)), 256)
+        ws = torch.empty(ws_bytes + 256, dtype=torch.uint8, device=dev)
+        ws_ptr = (ws.data_ptr() + 255) // 256 * 256
 
         def qstep():
             for lay in qpool:
                 _cabi.check(lib.kb_linear_forward_ex(lay.handle, x.data_ptr(), nb, K_DEC, y.data_ptr(), 0, None,
-                                                     _cabi.PATH_GEMV, None, 0, sptr))
+                                                     _cabi.PATH_AUTO, ws_ptr, ws_bytes, sptr))
 
         sec, _ = time_graph(torch, qstep, steps, warm, stream)
         gbs = len(qpool) * gemv_bytes(M_DEC, K_DEC, nb) / sec / 1e9
