@@ -151,6 +151,25 @@ int kb_linear_forward_fused(const kb_linear *h, const float *x, const int8_t *xq
                             float *y, size_t ldy, int path, void *workspace,
                             size_t workspace_bytes, kb_stream stream);
 
+/* ---- projections fused with their neighbours in a decode step (1..8 tokens, GEMV kernel) ----
+ *
+ * kb_linear_forward_rmsnorm: y = W . quantise(rmsnorm(x) * gamma) — the RMSNorm of
+ * crates/kore-kernels/src/cpu_fused.rs:160-190 and the activation quantiser run in the GEMV's
+ * prologue (every CTA normalises the L2-resident row itself), so norm + projection is one
+ * launch.  With swiglu != 0 (1 or 2 tokens) the weight rows must alternate gate_i, up_i
+ * (runtime.rs:232-252 computes the two projections separately); the epilogue writes
+ * h_i = silu(gate_i) * up_i into y [N][M/2] and, when absmax_out is given, folds max|h| of each
+ * token into absmax_out[N] with an atomic max — the caller keeps that word at zero beforehand.
+ *
+ * kb_linear_forward_scaled: the projection of f32 activations whose per-token max|x| is already
+ * known (x_absmax[N], e.g. from the SwiGLU epilogue above): the prologue quantises without its
+ * own reduction.  resid as in kb_linear_forward_fused.  clear_words (nullable): N floats the
+ * launch sets to zero, so two absmax arrays can alternate between layers without a memset. */
+int kb_linear_forward_rmsnorm(const kb_linear *h, const float *x, const float *gamma, float eps, size_t n,
+                              float *y, size_t ldy, int swiglu, float *absmax_out, kb_stream stream);
+int kb_linear_forward_scaled(const kb_linear *h, const float *x, const float *x_absmax, size_t n,
+                             const float *resid, float *y, size_t ldy, float *clear_words, kb_stream stream);
+
 /* ---- glue kernels of the decoder step; each ends in the per-token int8 quantiser so the
  * next projection reads codes.  Device pointers.  xn / h receive the f32 values when
  * not NULL; xq may be NULL to get only the f32 result. ---- */
@@ -161,6 +180,10 @@ int kb_rmsnorm_quant(const float *x, const float *gamma, size_t n, size_t d, flo
  * gate_up are [gate(f) | up(f)] with row stride ld; h = (g / (1 + exp(-g))) * u */
 int kb_swiglu_quant(const float *gate_up, size_t n, size_t f, size_t ld, float *h, int8_t *xq,
                     size_t ldq, float *sx, int32_t *sumq, kb_stream stream);
+/* the same for rows that alternate gate_0, up_0, gate_1, up_1, ... (the output of a projection
+ * whose weight rows are interleaved for the SwiGLU epilogue of kb_linear_forward_rmsnorm) */
+int kb_swiglu_quant_pairs(const float *gate_up, size_t n, size_t f, size_t ld, float *h, int8_t *xq,
+                          size_t ldq, float *sx, int32_t *sumq, kb_stream stream);
 /* Half-split RoPE (crates/kore-edge/src/ops/rope.rs:9-36) on the q and k parts of rows
  * [q|k|v] with cos/sin tables [max_pos][head_dim/2]; k and v go to row cache_rows[t] of
  * caches laid out [rows][n_heads*head_dim]. */

@@ -41,6 +41,7 @@ SIGNATURES = {
     "kb_linear_forward_fused": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, _sz, _vp, _vp, _sz, C.c_int, _vp, _sz, _vp]),
     "kb_rmsnorm_quant": (C.c_int, [_vp, _vp, _sz, _sz, C.c_float, _vp, _vp, _sz, _vp, _vp, _vp]),
     "kb_swiglu_quant": (C.c_int, [_vp, _sz, _sz, _sz, _vp, _vp, _sz, _vp, _vp, _vp]),
+    "kb_swiglu_quant_pairs": (C.c_int, [_vp, _sz, _sz, _sz, _vp, _vp, _sz, _vp, _vp, _vp]),
     "kb_rope_kv": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
     "kb_attn_decode": (C.c_int, [_vp, _vp, _vp, _vp, _sz, C.c_int, C.c_int, C.c_int, _vp, _vp, _sz, _vp]),
     "kb_attn_decode_scratch_bytes": (_sz, [_sz, C.c_int]),
@@ -48,6 +49,8 @@ SIGNATURES = {
     "kb_linear_forward_static": (C.c_int, [_vp, _vp, _sz, _sz, _vp, _vp]),
     "kb_static_scratch_bytes": (_sz, []),
     "kb_ternary_matmul": (C.c_int, [_vp, _sz, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
+    "kb_linear_forward_rmsnorm": (C.c_int, [_vp, _vp, _vp, C.c_float, _sz, _vp, _sz, C.c_int, _vp, _vp]),
+    "kb_linear_forward_scaled": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, _sz, _vp, _vp]),
     "kb_quat_matmul": (C.c_int, [_vp, _sz, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
     "kb_ternary_ternary_matmul": (C.c_int, [_vp, _sz, _vp, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
     "kb_pack_weights_ternary": (C.c_int, [_vp, _sz, _sz, C.c_float, _vp, _sz, _vp, _sz, C.c_int]),

@@ -532,6 +532,38 @@ int kb_linear_forward_fused(const kb_linear *h, const float *x, const int8_t *xq
     return path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, st) : launch_gemm_tc(a, st);
 }
 
+int kb_linear_forward_rmsnorm(const kb_linear *h, const float *x, const float *gamma, float eps, size_t n, float *y,
+                              size_t ldy, int swiglu, float *absmax_out, kb_stream stream) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    if (!x || !gamma || !y) return fail(KB_ERR_INVALID, "null pointer");
+    if (n == 0) return KB_OK;
+    const size_t width = swiglu ? L->m / 2 : L->m;
+    if (ldy != 0 && ldy < width) return fail(KB_ERR_INVALID, "ldy %zu smaller than the output width %zu", ldy, width);
+    if (n > (swiglu ? 2u : 8u) || !gemv_supports(L, n))
+        return fail(KB_ERR_UNSUPPORTED, "the fused RMSNorm projection takes up to %d tokens", swiglu ? 2 : 8);
+    DeviceGuard g(L->device);
+    FwdArgs a = {};
+    a.lin = L; a.x = x; a.n = n; a.y = y; a.ldy = ldy;
+    a.gamma = gamma; a.eps = eps; a.swiglu = swiglu != 0; a.absmax_out = absmax_out;
+    return launch_gemv(a, static_cast<cudaStream_t>(stream));
+}
+
+int kb_linear_forward_scaled(const kb_linear *h, const float *x, const float *x_absmax, size_t n, const float *resid,
+                             float *y, size_t ldy, float *clear_word, kb_stream stream) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    if (!x || !x_absmax || !y) return fail(KB_ERR_INVALID, "null pointer");
+    if (n == 0) return KB_OK;
+    if (ldy != 0 && ldy < L->m) return fail(KB_ERR_INVALID, "ldy %zu smaller than out_features %zu", ldy, L->m);
+    if (n > 8 || !gemv_supports(L, n)) return fail(KB_ERR_UNSUPPORTED, "the pre-scaled projection takes up to 8 tokens");
+    DeviceGuard g(L->device);
+    FwdArgs a = {};
+    a.lin = L; a.x = x; a.n = n; a.y = y; a.ldy = ldy; a.resid = resid;
+    a.x_absmax = x_absmax; a.clear_word = clear_word;
+    return launch_gemv(a, static_cast<cudaStream_t>(stream));
+}
+
 int kb_linear_forward_host(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *y) {
     const Linear *L = check(h);
     if (!L) return KB_ERR_BAD_HANDLE;

@@ -113,6 +113,16 @@ struct FwdArgs {
     const float *resid;
     // GEMV only: size the grid for launches that overlap with other streams' GEMVs
     bool shared_grid;
+    // GEMV with f32 input only (decoder fusions): RMSNorm in the prologue (gamma, eps), a known
+    // per-token max|x| instead of the prologue's reduction, SiLU(gate) * up in the epilogue for
+    // weights whose rows alternate gate_i, up_i (y is then [N][M / 2]) with the per-token max|h|
+    // collected by atomic max, and N floats the launch zeroes
+    const float *gamma;
+    float eps;
+    const float *x_absmax;
+    bool swiglu;
+    float *absmax_out;
+    float *clear_word;
 };
 // kernel choice for `n` tokens when the caller passes KB_PATH_AUTO: the dp4a GEMV for one or two
 // tokens (up to four when it also has to quantise, which it does in its prologue), the

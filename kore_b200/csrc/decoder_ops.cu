@@ -132,6 +132,8 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const float *__restr
     if (xq) quantise_row_from_regs<ROW_REGS>(v, d, ldq, xq + t * (size_t)ldq, sx + t, sumq ? sumq + t : nullptr, red_f, red_i);
 }
 
+// PAIRS: the row alternates gate_i, up_i instead of holding the two halves one after the other
+template <bool PAIRS>
 __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restrict__ gu, int f, size_t ld,
                                                            float *__restrict__ h_out, int8_t *__restrict__ xq, int ldq,
                                                            float *__restrict__ sx, int32_t *__restrict__ sumq) {
@@ -144,8 +146,14 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restri
 #pragma unroll
     for (int i = 0; i < ROW_REGS; ++i) {  // all loads first: one memory round trip for the row
         const int idx = threadIdx.x + i * blockDim.x;
-        v[i] = idx < f ? g[idx] : 0.0f;
-        uv[i] = idx < f ? u[idx] : 0.0f;
+        if (PAIRS) {
+            const float2 gu2 = idx < f ? reinterpret_cast<const float2 *>(g)[idx] : make_float2(0.0f, 0.0f);
+            v[i] = gu2.x;
+            uv[i] = gu2.y;
+        } else {
+            v[i] = idx < f ? g[idx] : 0.0f;
+            uv[i] = idx < f ? u[idx] : 0.0f;
+        }
     }
 #pragma unroll
     for (int i = 0; i < ROW_REGS; ++i) {
@@ -201,6 +209,7 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const float *__restrict__ 
 constexpr int ATT_WARPS = 8;
 constexpr int ATT_MAX_HD = 128;
 constexpr int ATT_UNROLL = 4;
+constexpr int ATT_MAX_SPLITS = 32;
 
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
     const float *__restrict__ q, const float *__restrict__ k_cache, const float *__restrict__ v_cache,
@@ -325,15 +334,29 @@ int kb_rmsnorm_quant(const float *x, const float *gamma, size_t n, size_t d, flo
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "rmsnorm launch");
 }
 
-int kb_swiglu_quant(const float *gate_up, size_t n, size_t f, size_t ld, float *h, int8_t *xq, size_t ldq, float *sx,
-                    int32_t *sumq, kb_stream stream) {
+static int swiglu_quant(bool pairs, const float *gate_up, size_t n, size_t f, size_t ld, float *h, int8_t *xq, size_t ldq,
+                        float *sx, int32_t *sumq, kb_stream stream) {
     if (!gate_up || (!h && !xq) || (xq && !sx)) return fail(KB_ERR_INVALID, "null pointer");
+    if (pairs && ((reinterpret_cast<uintptr_t>(gate_up) & 7) || (ld & 1)))
+        return fail(KB_ERR_INVALID, "swiglu: interleaved rows must be 8-byte aligned");
     if (f == 0 || f > (size_t)ROW_REGS * 256 || ld < 2 * f) return fail(KB_ERR_UNSUPPORTED, "swiglu: width %zu outside 1..%d", f, ROW_REGS * 256);
     if (xq && (ldq < f || ldq > (size_t)ROW_REGS * 256 || ldq % 16)) return fail(KB_ERR_INVALID, "swiglu: bad ldq %zu", ldq);
     if (n == 0) return KB_OK;
-    cudaError_t e = launch_pdl(swiglu_quant_kernel, dim3((unsigned)n), dim3(256), static_cast<cudaStream_t>(stream), gate_up,
-                               (int)f, ld, h, xq, (int)ldq, sx, sumq);
+    cudaError_t e = pairs ? launch_pdl(swiglu_quant_kernel<true>, dim3((unsigned)n), dim3(256), static_cast<cudaStream_t>(stream),
+                                       gate_up, (int)f, ld, h, xq, (int)ldq, sx, sumq)
+                          : launch_pdl(swiglu_quant_kernel<false>, dim3((unsigned)n), dim3(256), static_cast<cudaStream_t>(stream),
+                                       gate_up, (int)f, ld, h, xq, (int)ldq, sx, sumq);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "swiglu launch");
+}
+
+int kb_swiglu_quant(const float *gate_up, size_t n, size_t f, size_t ld, float *h, int8_t *xq, size_t ldq, float *sx,
+                    int32_t *sumq, kb_stream stream) {
+    return swiglu_quant(false, gate_up, n, f, ld, h, xq, ldq, sx, sumq, stream);
+}
+
+int kb_swiglu_quant_pairs(const float *gate_up, size_t n, size_t f, size_t ld, float *h, int8_t *xq, size_t ldq, float *sx,
+                          int32_t *sumq, kb_stream stream) {
+    return swiglu_quant(true, gate_up, n, f, ld, h, xq, ldq, sx, sumq, stream);
 }
 
 int kb_rope_kv(const float *qkv, const int *positions, const long long *cache_rows, const float *cos_table,
@@ -354,11 +377,13 @@ int kb_attn_decode(const float *q, const float *k_cache, const float *v_cache, c
     if (!q || !k_cache || !v_cache || !lens || !out) return fail(KB_ERR_INVALID, "null pointer");
     if (head_dim < 1 || head_dim > ATT_MAX_HD) return fail(KB_ERR_UNSUPPORTED, "attention: head_dim %d outside 1..%d", head_dim, ATT_MAX_HD);
     if (batch == 0) return KB_OK;
-    // enough CTAs to cover the GPU about twice; splitting needs the caller's scratch
+    // one batch of loads per warp where possible (a CTA covers 8 warps x 4 positions), as long as
+    // the grid stays within a couple of thousand CTAs; splitting needs the caller's scratch
     const size_t bh = batch * (size_t)n_heads;
-    int splits = (int)((296 + bh - 1) / bh);
-    if (splits > 16) splits = 16;
-    if (splits > lmax) splits = lmax > 0 ? lmax : 1;
+    int splits = (lmax + 31) / 32;
+    if (splits > ATT_MAX_SPLITS) splits = ATT_MAX_SPLITS;
+    if (splits < 1) splits = 1;
+    while (splits > 1 && bh * (size_t)splits > 2048) splits = (splits + 1) / 2;
     const size_t need = bh * sizeof(int) + 256 + bh * (size_t)splits * (2 + ATT_MAX_HD) * sizeof(float);
     if (splits > 1 && (!scratch || scratch_bytes < need)) splits = 1;
     int *counters = reinterpret_cast<int *>(scratch);
@@ -371,7 +396,7 @@ int kb_attn_decode(const float *q, const float *k_cache, const float *v_cache, c
 
 size_t kb_attn_decode_scratch_bytes(size_t batch, int n_heads) {
     const size_t bh = batch * (size_t)n_heads;
-    return bh * sizeof(int) + 256 + bh * 16 * (2 + ATT_MAX_HD) * sizeof(float);
+    return bh * sizeof(int) + 256 + bh * ATT_MAX_SPLITS * (2 + ATT_MAX_HD) * sizeof(float);
 }
 
 }  // extern "C"

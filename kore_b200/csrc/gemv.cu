@@ -52,6 +52,12 @@ struct GemvParams {
     int n_more;
     PeerSync sync;  // sync.world == 0: no fused barrier
     const float *resid;
+    // decoder fusions (fused-quantiser launches only):
+    const float *gamma;     // RMSNorm weight: the prologue normalises the row before quantising it
+    float eps;
+    const float *x_absmax;  // per-token max|x| already known: the prologue skips its reduction
+    float *absmax_out;      // SwiGLU epilogue: per-token max|h| (atomic max on the float bits)
+    float *clear_word;      // n floats the launch sets to zero (the other parity's absmax slots)
 };
 
 // 16-element group g (k = 16*g .. 16*g+15) <-> shared-memory slot: inside each
@@ -79,7 +85,22 @@ __device__ __forceinline__ void tl_mark(int i) {
 
 constexpr int XR = 8;  // float4 registers per thread for the single-pass fused quantiser
 
-template <int NT, int R, int PF, bool FUSED>
+__device__ __forceinline__ float block_reduce_sum_float(float v, float *scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = lane < nwarps ? scratch[lane] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    return r;
+}
+
+// EPI 0: y = dequantised output (+ residual).  EPI 1 (SwiGLU): weight rows alternate gate_i,
+// up_i; the output is h_i = silu(gate_i) * up_i, M / 2 values per token.
+template <int NT, int R, int PF, bool FUSED, int EPI = 0>
 __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     uint4 *xs = reinterpret_cast<uint4 *>(smem_raw);  // [NT][slots] permuted 16-byte slots
@@ -129,6 +150,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     TL_MARK(2);
+    if (FUSED && p.clear_word && blockIdx.x == 0 && blockIdx.y == 0 && (int)threadIdx.x < p.n) p.clear_word[threadIdx.x] = 0.0f;
 
     // ---- prologue: activations -> shared memory (int8, permuted) ----
     if (FUSED) {
@@ -157,9 +179,36 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
                     const int src = xs_group_of_slot(widx >> 2) * 4 + (widx & 3);
                     v[i] = (widx < slots * 4 && src < nv4) ? reinterpret_cast<const float4 *>(row)[src]
                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
                 }
-                amax = block_reduce_max(amax, red_f);
+                if (p.gamma) {
+                    // RMSNorm of the row: (x * (1 / sqrt(mean(x^2) + eps))) * gamma
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < XR; ++i)
+                        ss += __fmul_rn(v[i].x, v[i].x) + __fmul_rn(v[i].y, v[i].y) + __fmul_rn(v[i].z, v[i].z) + __fmul_rn(v[i].w, v[i].w);
+                    ss = block_reduce_sum_float(ss, red_f);
+                    const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(ss, (float)p.k), p.eps)));
+#pragma unroll
+                    for (int i = 0; i < XR; ++i) {
+                        const int widx = threadIdx.x + i * blockDim.x;
+                        const int src = xs_group_of_slot(widx >> 2) * 4 + (widx & 3);
+                        if (widx < slots * 4 && src < nv4) {
+                            const float4 gm = reinterpret_cast<const float4 *>(p.gamma)[src];
+                            v[i].x = __fmul_rn(__fmul_rn(v[i].x, inv), gm.x);
+                            v[i].y = __fmul_rn(__fmul_rn(v[i].y, inv), gm.y);
+                            v[i].z = __fmul_rn(__fmul_rn(v[i].z, inv), gm.z);
+                            v[i].w = __fmul_rn(__fmul_rn(v[i].w, inv), gm.w);
+                        }
+                    }
+                }
+                if (p.x_absmax) {
+                    amax = p.x_absmax[tok];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < XR; ++i)
+                        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+                    amax = block_reduce_max(amax, red_f);
+                }
                 s = amax < 1e-8f ? 1.0f : __fdiv_rn(amax, 127.0f);
                 rs = __frcp_rn(s);
                 uint32_t *dstw = reinterpret_cast<uint32_t *>(dst);
@@ -176,7 +225,9 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
                 }
             } else {
                 float amax = 0.0f;
-                if (p.x_vec4) {
+                if (p.x_absmax) {
+                    amax = p.x_absmax[tok];
+                } else if (p.x_vec4) {
                     const float4 *row4 = reinterpret_cast<const float4 *>(row);
                     for (int i = threadIdx.x; i < (p.k >> 2); i += blockDim.x) {
                         float4 v = row4[i];
@@ -185,7 +236,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
                 } else {
                     for (int i = threadIdx.x; i < p.k; i += blockDim.x) amax = fmaxf(amax, fabsf(row[i]));
                 }
-                amax = block_reduce_max(amax, red_f);
+                if (!p.x_absmax) amax = block_reduce_max(amax, red_f);
                 s = amax < 1e-8f ? 1.0f : __fdiv_rn(amax, 127.0f);
                 rs = __frcp_rn(s);
                 for (int d = threadIdx.x; d < slots; d += blockDim.x) {
@@ -287,7 +338,22 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
                             if (lane == r * NT + t) mine = v;
                             acc[r][t][0] = acc[r][t][1] = acc[r][t][2] = acc[r][t][3] = 0;
                         }
-                    if (lane < R * NT) {
+                    if (EPI == 1) {
+                        // lanes r*NT+t hold rows gate (r even) / up (r odd) of token t: the gate lane
+                        // fetches its partner's value and writes h = silu(g) * u
+                        const int r = lane / NT, t = lane - r * NT;
+                        const int row = cg * R + r, tok = tok0 + t;
+                        float v = 0.0f;
+                        if (lane < R * NT && row < p.m && tok < p.n)
+                            v = dequant_out(p.mul * mine - p.off * s_sum[t], my_sw, s_sx[t], my_bias, p.bias != nullptr);
+                        const float u = __shfl_down_sync(0xffffffffu, v, NT);
+                        if (lane < R * NT && (r & 1) == 0 && row + 1 < p.m && tok < p.n) {
+                            const float silu = __fdiv_rn(v, __fadd_rn(1.0f, expf(-v)));
+                            const float h = __fmul_rn(silu, u);
+                            p.y[(size_t)tok * p.ldy + (row >> 1)] = h;
+                            if (p.absmax_out) atomicMax(reinterpret_cast<unsigned int *>(p.absmax_out) + tok, __float_as_uint(fabsf(h)));
+                        }
+                    } else if (lane < R * NT) {
                         const int r = lane / NT, t = lane - r * NT;
                         const int row = cg * R + r, tok = tok0 + t;
                         if (row < p.m && tok < p.n) {
@@ -368,7 +434,7 @@ static int env_int(const char *name, int dflt) {
     return v && *v ? atoi(v) : dflt;
 }
 
-template <int NT, int R, int PF, bool FUSED>
+template <int NT, int R, int PF, bool FUSED, int EPI = 0>
 static int launch_one(const GemvParams &p, int tok_groups, bool shared_grid, cudaStream_t stream) {
     static const int env_threads = env_int("KB_GEMV_THREADS", 0);
     static const int env_pdl = env_int("KB_GEMV_PDL", 1);
@@ -378,7 +444,7 @@ static int launch_one(const GemvParams &p, int tok_groups, bool shared_grid, cud
     if (env_threads >= 64 && env_threads <= 256 && env_threads % 32 == 0) threads = env_threads;
     const int nwarps = threads / 32;
     const size_t smem = gemv_smem_bytes((size_t)p.kp, NT);
-    auto kern = gemv_kernel<NT, R, PF, FUSED>;
+    auto kern = gemv_kernel<NT, R, PF, FUSED, EPI>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return cuda_fail(e, "gemv smem attribute");
@@ -419,6 +485,11 @@ static int launch_one(const GemvParams &p, int tok_groups, bool shared_grid, cud
 }
 
 template <bool FUSED>
+static int dispatch_swiglu(const GemvParams &p, bool sg, cudaStream_t stream) {
+    return p.n == 1 ? launch_one<1, 4, 2, FUSED, 1>(p, 1, sg, stream) : launch_one<2, 4, 2, FUSED, 1>(p, 1, sg, stream);
+}
+
+template <bool FUSED>
 static int dispatch(const GemvParams &p, bool sg, cudaStream_t stream) {
     const int n = p.n;
     static const int env_pf = env_int("KB_GEMV_PF", 0);
@@ -451,6 +522,25 @@ int launch_gemv(const FwdArgs &a, cudaStream_t stream) {
     p.n_more = a.y ? a.n_more : 0;
     for (int q = 0; q < MAX_PEERS - 1; ++q) p.y_more[q] = q < p.n_more ? a.y_more[q] : nullptr;
     p.x_vec4 = a.x && (L->k % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
+    p.gamma = a.x ? a.gamma : nullptr;
+    p.eps = a.eps;
+    p.x_absmax = a.x ? a.x_absmax : nullptr;
+    p.absmax_out = a.swiglu ? a.absmax_out : nullptr;
+    p.clear_word = a.x ? a.clear_word : nullptr;
+    if ((a.gamma || a.x_absmax || a.clear_word) && !a.x)
+        return fail(KB_ERR_INVALID, "gemv: the normalising / pre-scaled prologues take f32 activations");
+    if (p.gamma) {
+        // the normalised row is held in registers: 8 float4 per thread of a 256-thread CTA
+        const int slots = (((int)L->kp >> 4) + 127) & ~127;
+        if (!p.x_vec4 || (reinterpret_cast<uintptr_t>(a.gamma) & 15) || slots * 4 > XR * 256)
+            return fail(KB_ERR_UNSUPPORTED, "gemv: RMSNorm prologue needs K %% 4 == 0, K <= 8192 and 16-byte aligned x and gamma");
+    }
+    if (a.swiglu) {
+        if (a.n > 2 || !a.y || a.acc || a.resid || p.n_more || p.sync.world || (L->m & 1))
+            return fail(KB_ERR_UNSUPPORTED, "gemv: the SwiGLU epilogue takes 1 or 2 tokens, an even number of rows and a plain output");
+        p.ldy = a.ldy ? a.ldy : L->m / 2;
+        return a.x ? dispatch_swiglu<true>(p, a.shared_grid, stream) : dispatch_swiglu<false>(p, a.shared_grid, stream);
+    }
     if (a.x) return dispatch<true>(p, a.shared_grid, stream);
     if ((reinterpret_cast<uintptr_t>(a.xq) & 15) || (a.ldq % 16) || a.ldq < L->kp)
         return fail(KB_ERR_INVALID, "gemv: xq must be 16-byte aligned with ldq >= %zu and ldq %% 16 == 0", L->kp);

@@ -83,6 +83,20 @@ def _concat_rows(parts):
     return (np.concatenate([p[0] for p in parts]), np.concatenate([p[1] for p in parts]), sum(p[2] for p in parts), k)
 
 
+def _interleave_rows(a, b):
+    """Two (packed, scales, m, k) layers of equal shape -> one layer whose rows alternate a_0, b_0,
+    a_1, b_1, ...: gate and up rows side by side, so one warp of the GEMV holds both values of a
+    SwiGLU output."""
+    (pa, sa, m, k), (pb, sb, m2, k2) = a, b
+    assert (m, k) == (m2, k2)
+    row = pa.size // m
+    packed = np.empty((2 * m, row), np.uint8)
+    packed[0::2], packed[1::2] = pa.reshape(m, row), pb.reshape(m, row)
+    scales = np.empty(2 * m, np.float32)
+    scales[0::2], scales[1::2] = sa, sb
+    return (packed.reshape(-1), scales, 2 * m, k)
+
+
 class BitNetDecoder:
     def __init__(self, cfg: DecoderConfig, weights: Dict, batch: int, device: int = 0, max_prefill_tokens: int = 0):
         import torch
@@ -95,7 +109,7 @@ class BitNetDecoder:
         self.layers = []
         for lw in weights["layers"]:
             qkv = _concat_rows([lw["q"], lw["k"], lw["v"]])
-            gu = _concat_rows([lw["gate"], lw["up"]])
+            gu = _interleave_rows(lw["gate"], lw["up"])
             mk = lambda t: nn.BitLinear.from_packed(t[0], t[1], None, t[3], t[2], device=device)
             self.layers.append({
                 "qkv": mk(qkv), "o": mk(lw["o"]), "gu": mk(gu), "down": mk(lw["down"]),
@@ -135,7 +149,8 @@ class BitNetDecoder:
         self._bufs[n] = {
             "hidden": z((n, d)), "qkv": z((n, 3 * d)), "q": z((n, d)), "attn": z((n, d)), "gu": z((n, 2 * f)),
             "xn": z((n, d)), "xq_d": z((n, self.ld_d), torch.int8), "xq_f": z((n, self.ld_f), torch.int8),
-            "sx": z(n), "sum": z(n, torch.int32), "ws": z(ws_bytes + 256, torch.uint8), "ws_bytes": ws_bytes}
+            "sx": z(n), "sum": z(n, torch.int32), "ws": z(ws_bytes + 256, torch.uint8), "ws_bytes": ws_bytes,
+            "h": z((n, f)) if n <= 2 else None, "absmax": z((2, n)) if n <= 2 else None}
 
     # ---- one pass over all layers for n tokens ----------------------------------------------
     def _layers(self, n, tokens, positions, cache_rows, lens, prefill_shape=None):
@@ -146,18 +161,24 @@ class BitNetDecoder:
         ws_ptr = (B["ws"].data_ptr() + 255) // 256 * 256
         torch.index_select(self.embed, 0, tokens, out=B["hidden"])
         launches = 1
+        # one or two decode tokens: norms and the SwiGLU ride in the projections' prologue / epilogue
+        fused = prefill_shape is None and n <= 2
         for li, L in enumerate(self.layers):
-            ck(lib.kb_rmsnorm_quant(B["hidden"].data_ptr(), L["norm1"].data_ptr(), n, d, C.c_float(cfg.eps), None,
-                                    B["xq_d"].data_ptr(), self.ld_d, B["sx"].data_ptr(), B["sum"].data_ptr(), sp))
-            ck(lib.kb_linear_forward_fused(L["qkv"].handle, None, B["xq_d"].data_ptr(), self.ld_d, B["sx"].data_ptr(),
-                                           B["sum"].data_ptr(), n, None, B["qkv"].data_ptr(), 0, _cabi.PATH_AUTO, None, 0, sp))
+            if fused:
+                ck(lib.kb_linear_forward_rmsnorm(L["qkv"].handle, B["hidden"].data_ptr(), L["norm1"].data_ptr(),
+                                                 C.c_float(cfg.eps), n, B["qkv"].data_ptr(), 0, 0, None, sp))
+            else:
+                ck(lib.kb_rmsnorm_quant(B["hidden"].data_ptr(), L["norm1"].data_ptr(), n, d, C.c_float(cfg.eps), None,
+                                        B["xq_d"].data_ptr(), self.ld_d, B["sx"].data_ptr(), B["sum"].data_ptr(), sp))
+                ck(lib.kb_linear_forward_fused(L["qkv"].handle, None, B["xq_d"].data_ptr(), self.ld_d, B["sx"].data_ptr(),
+                                               B["sum"].data_ptr(), n, None, B["qkv"].data_ptr(), 0, _cabi.PATH_AUTO, None, 0, sp))
             ck(lib.kb_rope_kv(B["qkv"].data_ptr(), positions.data_ptr(), cache_rows.data_ptr(), self.cos.data_ptr(),
                               self.sin.data_ptr(), n, H, hd, B["q"].data_ptr(), self.kc[li].data_ptr(), self.vc[li].data_ptr(), sp))
             if prefill_shape is None:
                 ck(lib.kb_attn_decode(B["q"].data_ptr(), self.kc[li].data_ptr(), self.vc[li].data_ptr(), lens.data_ptr(),
                                       n, H, hd, cfg.max_len, B["attn"].data_ptr(), self.att_scratch.data_ptr(),
                                       self.att_bytes, sp))
-                launches += 4
+                launches += 2
             else:
                 b, t = prefill_shape
                 qh = B["q"].view(b, t, H, hd).transpose(1, 2)
@@ -165,19 +186,27 @@ class BitNetDecoder:
                 vh = self.vc[li][:b, :t].view(b, t, H, hd).transpose(1, 2)
                 o = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=True)
                 B["attn"].view(b, t, H, hd).copy_(o.transpose(1, 2))
-                launches += 6
+                launches += 4
             ck(lib.kb_linear_forward_fused(L["o"].handle, B["attn"].data_ptr(), None, 0, None, None, n, B["hidden"].data_ptr(),
                                            B["hidden"].data_ptr(), 0, _cabi.PATH_AUTO, ws_ptr, B["ws_bytes"], sp))
-            ck(lib.kb_rmsnorm_quant(B["hidden"].data_ptr(), L["norm2"].data_ptr(), n, d, C.c_float(cfg.eps), None,
-                                    B["xq_d"].data_ptr(), self.ld_d, B["sx"].data_ptr(), B["sum"].data_ptr(), sp))
-            ck(lib.kb_linear_forward_fused(L["gu"].handle, None, B["xq_d"].data_ptr(), self.ld_d, B["sx"].data_ptr(),
-                                           B["sum"].data_ptr(), n, None, B["gu"].data_ptr(), 0, _cabi.PATH_AUTO, None, 0, sp))
-            ck(lib.kb_swiglu_quant(B["gu"].data_ptr(), n, f, 2 * f, None, B["xq_f"].data_ptr(), self.ld_f,
-                                   B["sx"].data_ptr(), B["sum"].data_ptr(), sp))
-            ck(lib.kb_linear_forward_fused(L["down"].handle, None, B["xq_f"].data_ptr(), self.ld_f, B["sx"].data_ptr(),
-                                           B["sum"].data_ptr(), n, B["hidden"].data_ptr(), B["hidden"].data_ptr(), 0,
-                                           _cabi.PATH_AUTO, None, 0, sp))
-            launches += 5 + (1 if n > 4 else 0)
+            if fused:
+                am = B["absmax"]
+                ck(lib.kb_linear_forward_rmsnorm(L["gu"].handle, B["hidden"].data_ptr(), L["norm2"].data_ptr(),
+                                                 C.c_float(cfg.eps), n, B["h"].data_ptr(), 0, 1, am[li & 1].data_ptr(), sp))
+                ck(lib.kb_linear_forward_scaled(L["down"].handle, B["h"].data_ptr(), am[li & 1].data_ptr(), n,
+                                                B["hidden"].data_ptr(), B["hidden"].data_ptr(), 0, am[(li + 1) & 1].data_ptr(), sp))
+                launches += 4
+            else:
+                ck(lib.kb_rmsnorm_quant(B["hidden"].data_ptr(), L["norm2"].data_ptr(), n, d, C.c_float(cfg.eps), None,
+                                        B["xq_d"].data_ptr(), self.ld_d, B["sx"].data_ptr(), B["sum"].data_ptr(), sp))
+                ck(lib.kb_linear_forward_fused(L["gu"].handle, None, B["xq_d"].data_ptr(), self.ld_d, B["sx"].data_ptr(),
+                                               B["sum"].data_ptr(), n, None, B["gu"].data_ptr(), 0, _cabi.PATH_AUTO, None, 0, sp))
+                ck(lib.kb_swiglu_quant_pairs(B["gu"].data_ptr(), n, f, 2 * f, None, B["xq_f"].data_ptr(), self.ld_f,
+                                             B["sx"].data_ptr(), B["sum"].data_ptr(), sp))
+                ck(lib.kb_linear_forward_fused(L["down"].handle, None, B["xq_f"].data_ptr(), self.ld_f, B["sx"].data_ptr(),
+                                               B["sum"].data_ptr(), n, B["hidden"].data_ptr(), B["hidden"].data_ptr(), 0,
+                                               _cabi.PATH_AUTO, None, 0, sp))
+                launches += 7 + (1 if n > 4 else 0)
         self.launches_per_step = launches + 3
         return B
 
