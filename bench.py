@@ -287,7 +287,7 @@ def main():
                 sp = fan.side[i].cuda_stream
                 if args.fused_quant:  # quantiser in the GEMV prologue: one launch per layer
                     _cabi.check(lib.kb_linear_forward_ex(lay.handle, x_dev.data_ptr(), 1, K_DEC, ys[i].data_ptr(), 0, None,
-                                                         _cabi.PATH_GEMV, None, 0, sp))
+                                                         gemv_path, None, 0, sp))
                     continue
                 _cabi.check(lib.kb_quantize_act_i8(x_dev.data_ptr(), 1, K_DEC, xqs[i].data_ptr(), ld, sxs[i].data_ptr(),
                                                    sms[i].data_ptr(), sp))
