@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Headline workload (N = 1): the batch-1 decode GEMV of BASELINE.json configs[1] —
+Headline workload (N = 1): the batch-1 decode GEMV of the benchmark specification's second configuration —
 ternary 4096x4096 weights (absmean-ternarised N(0, 0.02^2), seed 2001), one f32
 activation row N(0,1) (seed 2002), per-token int8 absmax fused into the kernel.
 A "step" is one pass over a pool of POOL distinct copies of that layer (each copy has
@@ -475,7 +475,7 @@ def single_case(torch, lib, _cabi, nn, kernels, dev, args):
 
 
 def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, peaks):
-    """BASELINE.json configs[4]: ternary K=8192 x M=28672 split by output features over the
+    """Sharded-projection configuration of the benchmark specification: ternary K=8192 x M=28672 split by output features over the
     ranks (strong scaling: the layer is fixed), batch 1 / 8 / 64 / 512, every rank ends with
     the full y.  Exchange: epilogue peer stores + flag barrier, and NCCL all-gather beside it.
     A pool of separately allocated copies of the shard (> L2 in total) is cycled."""
@@ -538,7 +538,7 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
 
 
 def decoder_measurement(torch, dev, peaks):
-    """BASELINE.json configs[3]: BitNet-b1.58-3B-shaped decoder (26 layers, d 3200, 32 heads,
+    """Decoder configuration of the benchmark specification: BitNet-b1.58-3B-shaped decoder (26 layers, d 3200, 32 heads,
     FFN 8640, vocab 32000), random init, 512-token prompt then 128 greedy steps, batch 1 and 16.
     Decode steps are CUDA-graph replays timed with CUDA events."""
     from kore_b200 import decoder
@@ -591,7 +591,7 @@ def decoder_measurement(torch, dev, peaks):
 
 
 def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, pool, x_dev):
-    """Other configurations of BASELINE.json, measured briefly: quaternary GEMV, batch-8 GEMV,
+    """Other configurations of the benchmark specification, measured briefly: quaternary GEMV, batch-8 GEMV,
     prefill GEMM (2048 tokens, 4096 -> 11008 and 11008 -> 4096) with a library int8 GEMM
     timed beside it as a local ceiling."""
     out = {}

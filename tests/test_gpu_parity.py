@@ -179,7 +179,7 @@ def test_forward_bit_exact(torch, kb, path, kind, quantiser, m, k, n):
     assert (np.abs(y.cpu().numpy() - y_r) <= tol).all()
 
 
-# ---- BASELINE.json's full sizes: size-independent properties + sampled exact rows ---------
+# ---- the benchmark specification's full sizes: size-independent properties + sampled exact rows ---------
 FULL_SIZES = [
     # name, m, k, n, kind
     ("decode_4096x4096_b1", 4096, 4096, 1, T),
