@@ -303,11 +303,16 @@ def main():
 
         # one exchange context (output buffers + flags) per stream, so that independent layers
         # overlap their exchange latency exactly as the single-GPU step overlaps launches
-        n_streams = max(1, min(args.streams, 8))
+        n_streams = max(1, min(args.streams, 32))
         while pool_n % (2 * n_streams):
             n_streams -= 1
         fan = StreamFan(torch, main_stream, n_streams)
         ctxs = [sharded.ShardContext(rank, world, m_total, 8, local_rank, dist) for _ in fan.side]
+        shard_path = _cabi.PATH_GEMV if os.environ.get("KB_BENCH_SHARD_PATH") == "gemv" else _cabi.PATH_GEMV_SHARED
+        shard_q8 = os.environ.get("KB_BENCH_SHARD_Q8", "1") != "0"
+        xqs = [torch.zeros((1, ld), dtype=torch.int8, device=dev) for _ in fan.side]
+        sxs = [torch.zeros(1, dtype=torch.float32, device=dev) for _ in fan.side]
+        sms = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in fan.side]
         ctx = ctxs[0]
         last = [0, 0]
 
@@ -318,13 +323,21 @@ def main():
                 c = ctxs[i]
                 par = c.next_parity()
                 last[0], last[1] = i, par
+                sp = fan.side[i].cuda_stream
+                if shard_q8:  # the N = 1 step's two launches: quantiser, then the GEMV on the codes
+                    _cabi.check(lib.kb_quantize_act_i8(x_dev.data_ptr(), 1, K_DEC, xqs[i].data_ptr(), ld, sxs[i].data_ptr(),
+                                                       sms[i].data_ptr(), sp))
+                    _cabi.check(lib.kb_linear_forward_sharded_q8(lay.handle, xqs[i].data_ptr(), ld, sxs[i].data_ptr(),
+                                                                 sms[i].data_ptr(), 1, c.y_tables_host[par], world, rank,
+                                                                 m_total, rank * M_DEC, shard_path, c.flag_table.data_ptr(),
+                                                                 c.sync_words.data_ptr(), sp))
+                    continue
                 _cabi.check(lib.kb_linear_forward_sharded(lay.handle, x_dev.data_ptr(), 1, K_DEC, c.y_tables_host[par],
-                                                          world, rank, m_total, rank * M_DEC, _cabi.PATH_GEMV, None, 0,
-                                                          c.flag_table.data_ptr(), c.sync_words.data_ptr(),
-                                                          fan.side[i].cuda_stream))
+                                                          world, rank, m_total, rank * M_DEC, shard_path, None, 0,
+                                                          c.flag_table.data_ptr(), c.sync_words.data_ptr(), sp))
             fan.join()
 
-        launches_per_step = pool_n
+        launches_per_step = pool_n * (2 if shard_q8 else 1)
         y_view = lambda: ctxs[last[0]].local_y[last[1]][0, rank * M_DEC:(rank + 1) * M_DEC]
 
     if dist is not None:

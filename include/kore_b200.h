@@ -272,6 +272,12 @@ int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size
                               size_t col_offset, int path, void *workspace,
                               size_t workspace_bytes, int *const *flag_arrays_dev,
                               int *sync_words_dev, kb_stream stream);
+/* The same for activations that are already quantised (kb_quantize_act_i8, kb_rmsnorm_quant,
+ * ...): no per-launch quantiser, so a decode step shares one quantisation among its ranks' kernels. */
+int kb_linear_forward_sharded_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const float *sx,
+                                 const int32_t *sumq, size_t n, float *const *y_bases, int world, int rank,
+                                 size_t m_total, size_t col_offset, int path, int *const *flag_arrays_dev,
+                                 int *sync_words_dev, kb_stream stream);
 /* flag_arrays_dev: device array of `world` pointers, entry q = rank q's int32[world]
  * flag array (local or peer mapping); epoch_counter_dev: one local int32, starts at 0 and
  * is bumped by every barrier (all ranks must issue the same sequence of barriers);

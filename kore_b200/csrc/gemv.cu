@@ -464,7 +464,9 @@ static int launch_one(const GemvParams &p, int tok_groups, bool shared_grid, cud
     const int occ = c_occ, sms = c_sms;
     // shared_grid: two row groups per warp, so a launch leaves room for other streams' launches
     // and each CTA stages the activations once for twice the weight bytes
-    const int groups_per_cta = shared_grid ? 2 * nwarps : nwarps;
+    // (four when the launch ends in the cross-GPU barrier: every CTA then also pays a system-scope
+    // fence for its peer stores, and fewer, longer CTAs measured faster)
+    const int groups_per_cta = shared_grid ? (p.sync.world > 0 ? 4 : 2) * nwarps : nwarps;
     int ctas = (row_groups + groups_per_cta - 1) / groups_per_cta;
     if (ctas > sms * occ) ctas = sms * occ;
     if (env_maxctas > 0 && ctas > env_maxctas) ctas = env_maxctas;

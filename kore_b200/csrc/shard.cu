@@ -102,13 +102,14 @@ int kb_peer_barrier(int *const *flag_arrays_dev, int world, int rank, int *epoch
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "peer barrier launch");
 }
 
-int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *const *y_bases,
-                              int world, int rank, size_t m_total, size_t col_offset, int path, void *workspace,
-                              size_t workspace_bytes, int *const *flag_arrays_dev, int *sync_words_dev,
-                              kb_stream stream) {
+// x (f32) or xq/sx/sumq (already quantised) -> this rank's slice of y in every rank's buffer
+static int sharded_forward(const kb_linear *h, const float *x, const int8_t *xq, size_t ldq, const float *sx,
+                           const int32_t *sumq, size_t n, size_t in_dim, float *const *y_bases, int world, int rank,
+                           size_t m_total, size_t col_offset, int path, void *workspace, size_t workspace_bytes,
+                           int *const *flag_arrays_dev, int *sync_words_dev, kb_stream stream) {
     const Linear *L = reinterpret_cast<const Linear *>(h);
     if (!L || L->magic != HANDLE_MAGIC) return fail(KB_ERR_BAD_HANDLE, "null or destroyed kb_linear handle");
-    if (!y_bases || !x) return fail(KB_ERR_INVALID, "null pointer");
+    if (!y_bases || (!x && !(xq && sx && sumq))) return fail(KB_ERR_INVALID, "null pointer");
     if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world)
         return fail(KB_ERR_INVALID, "world %d / rank %d outside 1..%d", world, rank, MAX_PEERS);
     if (in_dim != L->k)
@@ -132,45 +133,68 @@ int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size
         if (q != rank) a.y_more[a.n_more++] = y_bases[q] + col_offset;
     // the GEMV (a few tokens) ends in the fused barrier; the small-batch kernel and the GEMM store
     // to the peers and a barrier kernel follows
-    if (path == KB_PATH_AUTO) path = auto_path(L, n, false);
+    if (path == KB_PATH_AUTO) path = auto_path(L, n, xq != nullptr);
+    if (path == KB_PATH_GEMV_SHARED) { a.shared_grid = true; path = KB_PATH_GEMV; }
     int rc;
     // sync_words_dev = {epoch counter, CTA-done counter, status}
     PeerSync sync = {flag_arrays_dev, sync_words_dev, sync_words_dev ? sync_words_dev + 1 : nullptr,
                      sync_words_dev ? sync_words_dev + 2 : nullptr, world, rank};
     const bool want_sync = flag_arrays_dev && sync_words_dev;
     if (path == KB_PATH_GEMV) {
-        a.x = x;
+        if (xq) { a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq; } else { a.x = x; }
         a.sync = want_sync ? &sync : nullptr;  // barrier fused into the kernel's tail
         rc = launch_gemv(a, st);
     } else {
-        const size_t xq_bytes = (n * L->kp + 255) / 256 * 256, vec_bytes = (n * 4 + 255) / 256 * 256;
-        const size_t need = xq_bytes + 2 * vec_bytes;
-        uint8_t *ws = static_cast<uint8_t *>(workspace);
-        bool own = false;
         rc = KB_OK;
-        if (!ws) {
-            e = cudaMallocAsync(reinterpret_cast<void **>(&ws), need, st);
-            if (e != cudaSuccess) rc = cuda_fail(e, "workspace allocation");
-            own = true;
-        } else if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255)) {
-            rc = fail(KB_ERR_STORAGE, "workspace too small or misaligned: need %zu bytes, got %zu", need, workspace_bytes);
-        }
-        if (rc == KB_OK) {
-            int8_t *xq = reinterpret_cast<int8_t *>(ws);
-            float *sx = reinterpret_cast<float *>(ws + xq_bytes);
-            int32_t *sumq = reinterpret_cast<int32_t *>(ws + xq_bytes + vec_bytes);
-            rc = launch_act_quant(x, n, L->k, xq, L->kp, sx, sumq, st);
-            if (rc == KB_OK) {
-                a.xq = xq; a.ldq = L->kp; a.sx = sx; a.sumq = sumq;
-                rc = path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, st) : launch_gemm_tc(a, st);
+        uint8_t *ws = nullptr;
+        bool own = false;
+        if (xq) {
+            a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq;
+        } else {
+            const size_t xq_bytes = (n * L->kp + 255) / 256 * 256, vec_bytes = (n * 4 + 255) / 256 * 256;
+            const size_t need = xq_bytes + 2 * vec_bytes;
+            ws = static_cast<uint8_t *>(workspace);
+            if (!ws) {
+                e = cudaMallocAsync(reinterpret_cast<void **>(&ws), need, st);
+                if (e != cudaSuccess) rc = cuda_fail(e, "workspace allocation");
+                own = true;
+            } else if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255)) {
+                rc = fail(KB_ERR_STORAGE, "workspace too small or misaligned: need %zu bytes, got %zu", need, workspace_bytes);
             }
-            if (own) cudaFreeAsync(ws, st);
+            if (rc == KB_OK) {
+                int8_t *wq = reinterpret_cast<int8_t *>(ws);
+                float *wsx = reinterpret_cast<float *>(ws + xq_bytes);
+                int32_t *wsum = reinterpret_cast<int32_t *>(ws + xq_bytes + vec_bytes);
+                rc = launch_act_quant(x, n, L->k, wq, L->kp, wsx, wsum, st);
+                a.xq = wq; a.ldq = L->kp; a.sx = wsx; a.sumq = wsum;
+            }
         }
+        if (rc == KB_OK) rc = path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, st) : launch_gemm_tc(a, st);
+        if (own && ws) cudaFreeAsync(ws, st);
         if (rc == KB_OK && want_sync)
             rc = kb_peer_barrier(flag_arrays_dev, world, rank, sync_words_dev, sync_words_dev + 2, stream);
     }
     if (prev != L->device) cudaSetDevice(prev);
     return rc;
+}
+
+int kb_linear_forward_sharded(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *const *y_bases,
+                              int world, int rank, size_t m_total, size_t col_offset, int path, void *workspace,
+                              size_t workspace_bytes, int *const *flag_arrays_dev, int *sync_words_dev,
+                              kb_stream stream) {
+    if (!x) return fail(KB_ERR_INVALID, "null pointer");
+    return sharded_forward(h, x, nullptr, 0, nullptr, nullptr, n, in_dim, y_bases, world, rank, m_total, col_offset, path,
+                           workspace, workspace_bytes, flag_arrays_dev, sync_words_dev, stream);
+}
+
+int kb_linear_forward_sharded_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const float *sx, const int32_t *sumq,
+                                 size_t n, float *const *y_bases, int world, int rank, size_t m_total, size_t col_offset,
+                                 int path, int *const *flag_arrays_dev, int *sync_words_dev, kb_stream stream) {
+    const Linear *L = reinterpret_cast<const Linear *>(h);
+    if (!L || L->magic != HANDLE_MAGIC) return fail(KB_ERR_BAD_HANDLE, "null or destroyed kb_linear handle");
+    if (!xq || !sx || !sumq) return fail(KB_ERR_INVALID, "null pointer");
+    return sharded_forward(h, nullptr, xq, ldq, sx, sumq, n, L->k, y_bases, world, rank, m_total, col_offset, path, nullptr, 0,
+                           flag_arrays_dev, sync_words_dev, stream);
 }
 
 }  // extern "C"

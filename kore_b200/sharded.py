@@ -215,6 +215,25 @@ class ShardedLinear:
 
     __call__ = forward
 
+    def forward_q8(self, xq, sx, sumq, path: int = _cabi.PATH_AUTO, stream_ptr: Optional[int] = None):
+        """The p2p exchange on activations that are already quantised (int8 [N, ld], scales [N],
+        code sums [N], all CUDA tensors replicated on every rank) -> y [N, M] on this rank."""
+        import torch
+
+        ctx, n = self.ctx, xq.shape[0]
+        if self.exchange != "p2p" or ctx is None:
+            raise _cabi.KoreError(_cabi.ERR_UNSUPPORTED, "forward_q8 uses the p2p exchange")
+        if n > ctx.max_tokens or self.m_total != ctx.m_total:
+            raise _cabi.KoreError(_cabi.ERR_UNSUPPORTED, "tokens or features exceed the shard context")
+        if stream_ptr is None:
+            stream_ptr = torch.cuda.current_stream(xq.device.index).cuda_stream
+        par = ctx.next_parity()
+        _cabi.check(ctx.lib.kb_linear_forward_sharded_q8(
+            self.layer.handle, xq.data_ptr(), xq.stride(0), sx.data_ptr(), sumq.data_ptr(), n, ctx.y_tables_host[par],
+            self.world, self.rank, self.m_total, self.start, path, ctx.flag_table.data_ptr(), ctx.sync_words.data_ptr(),
+            stream_ptr))
+        return ctx.local_y[par][:n]
+
     # -- CPU test path: same partition / gather logic, compute injected -------------------------
     def _forward_collective_generic(self, x):
         import torch

@@ -50,6 +50,18 @@ def _rank_main(rank, world, port, q):
                         ok &= same
                         if not same:
                             msgs.append(f"rank {rank} kind {kind} {exchange} n={n} rep={rep} differs")
+                if exchange == "p2p":  # the same layer on activations quantised beforehand
+                    from kore_b200 import kernels
+
+                    for n in (1, 2, 7, 40):
+                        x = cases.gaussian(900 + n, (n, k), 1.0)
+                        xq, sx, sumq = kernels.quantize_act_i8(torch.from_numpy(x).cuda())
+                        y = lay.forward_q8(xq, sx, sumq)
+                        torch.cuda.synchronize()
+                        y_ref = kbref.q_forward(kind, packed, scales, bias, m, k, x, threads=2)[0]
+                        if not bool((y.cpu().numpy() == y_ref).all()):
+                            ok = False
+                            msgs.append(f"rank {rank} kind {kind} q8 n={n} differs")
         ctx.check_status()
         ctx.close()
     except Exception as exc:  # report instead of hanging the peers
