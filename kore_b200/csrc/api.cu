@@ -150,12 +150,14 @@ static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim
 struct HostStaging {
     int device = -1;
     void *dx = nullptr, *dy = nullptr;
+    void *hy = nullptr;  // pinned twin of dy: a device -> pageable copy would be staged by the driver anyway
     size_t dx_cap = 0, dy_cap = 0;
     ~HostStaging() { release(); }
     void release() {
         if (dx) cudaFree(dx);
         if (dy) cudaFree(dy);
-        dx = dy = nullptr;
+        if (hy) cudaFreeHost(hy);
+        dx = dy = hy = nullptr;
         dx_cap = dy_cap = 0;
     }
     int ensure(int dev, size_t xb, size_t yb) {
@@ -169,9 +171,12 @@ struct HostStaging {
         }
         if (yb > dy_cap) {
             if (dy) cudaFree(dy);
-            dy = nullptr; dy_cap = 0;
+            if (hy) cudaFreeHost(hy);
+            dy = hy = nullptr; dy_cap = 0;
             cudaError_t e = cudaMalloc(&dy, yb);
             if (e != cudaSuccess) return cuda_fail(e, "output staging");
+            // small results come back through pinned memory; large ones go straight to the caller
+            if (yb <= (4u << 20) && cudaHostAlloc(&hy, yb, cudaHostAllocDefault) != cudaSuccess) { hy = nullptr; cudaGetLastError(); }
             dy_cap = yb;
         }
         return KB_OK;
@@ -193,10 +198,13 @@ static int forward_host_impl(const Linear *L, const float *x, size_t n, size_t i
     if ((e = cudaMemcpyAsync(dx, x, n * L->k * sizeof(float), cudaMemcpyHostToDevice, st)) != cudaSuccess)
         rc = cuda_fail(e, "activation upload");
     if (rc == KB_OK) rc = forward_impl(L, dx, n, in_dim, dy, 0, nullptr, KB_PATH_AUTO, nullptr, 0, st);
-    if (rc == KB_OK && (e = cudaMemcpyAsync(y, dy, n * L->m * sizeof(float), cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+    const size_t yb = n * L->m * sizeof(float);
+    void *landing = (g_staging.hy && yb <= (4u << 20)) ? g_staging.hy : static_cast<void *>(y);
+    if (rc == KB_OK && (e = cudaMemcpyAsync(landing, dy, yb, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
         rc = cuda_fail(e, "output download");
     e = cudaStreamSynchronize(st);
     if (rc == KB_OK && e != cudaSuccess) rc = cuda_fail(e, "stream synchronize");
+    if (rc == KB_OK && landing != y) memcpy(y, landing, yb);
     return rc;
 }
 
