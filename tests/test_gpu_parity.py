@@ -142,6 +142,8 @@ SHAPES = [
     # m, k, n
     (128, 256, 1), (128, 256, 32), (8, 20, 4), (2, 7, 3), (16, 32, 16), (1, 1, 1), (130, 1000, 5),
     (300, 4096, 2), (257, 2304, 8), (64, 5, 9), (200, 640, 70), (129, 384, 130), (256, 512, 300),
+    # GEMV with more row groups than one round of the persistent grid (grid-stride rounds, ragged last one)
+    (14400, 256, 1), (14270, 130, 2), (14500, 384, 8), (28800, 128, 4),
     # small-batch kernel: K steps fewer / more than its 16 warps, ragged rows and tokens
     (50, 8640, 16), (3200, 3200, 12), (17, 4352, 27),
     # CTA-pair GEMM edges: odd number of 128-row blocks, odd number of 128-byte K slabs, ragged tokens
