@@ -261,3 +261,35 @@ def test_small_decoder_against_cpu_restatement(env):
         assert np.abs(got - ref_logits).max() <= tol, step
         toks = dec.tokens.cpu().numpy()
     dec.close()
+
+
+def test_fused_projection_argument_checks(env):
+    """the decode-step projections refuse what they cannot run instead of falling back"""
+    t = env.torch
+    m, k = 64, 256
+    w = cases.gaussian(500, (m, k), 0.02)
+    packed, scales = kbref.pack_weights_ternary_absmean(w, m, k)
+    lay = env.nn.BitLinear.from_packed(packed, scales, None, k, m)
+    x = t.zeros((16, k), device="cuda")
+    g = t.ones(k, device="cuda")
+    y = t.zeros((16, m), device="cuda")
+    am = t.zeros(16, device="cuda")
+    lib, E = env.lib, env.cabi
+    assert lib.kb_linear_forward_rmsnorm(lay.handle, x.data_ptr(), g.data_ptr(), C.c_float(1e-5), 9, y.data_ptr(), 0, 0, None, env.sp) == E.ERR_UNSUPPORTED
+    assert lib.kb_linear_forward_rmsnorm(lay.handle, x.data_ptr(), g.data_ptr(), C.c_float(1e-5), 3, y.data_ptr(), 0, 1, am.data_ptr(), env.sp) == E.ERR_UNSUPPORTED
+    assert "tokens" in lib.kb_last_error().decode()
+    assert lib.kb_linear_forward_rmsnorm(lay.handle, None, g.data_ptr(), C.c_float(1e-5), 1, y.data_ptr(), 0, 0, None, env.sp) == E.ERR_INVALID
+    assert lib.kb_linear_forward_rmsnorm(lay.handle, x.data_ptr(), g.data_ptr(), C.c_float(1e-5), 1, y.data_ptr(), m - 1, 0, None, env.sp) == E.ERR_INVALID
+    assert lib.kb_linear_forward_scaled(lay.handle, x.data_ptr(), am.data_ptr(), 9, None, y.data_ptr(), 0, None, env.sp) == E.ERR_UNSUPPORTED
+    assert lib.kb_linear_forward_scaled(lay.handle, x.data_ptr(), None, 1, None, y.data_ptr(), 0, None, env.sp) == E.ERR_INVALID
+    assert lib.kb_linear_forward_rmsnorm(None, x.data_ptr(), g.data_ptr(), C.c_float(1e-5), 1, y.data_ptr(), 0, 0, None, env.sp) == E.ERR_BAD_HANDLE
+    # zero tokens is a no-op
+    assert lib.kb_linear_forward_rmsnorm(lay.handle, x.data_ptr(), g.data_ptr(), C.c_float(1e-5), 0, y.data_ptr(), 0, 0, None, env.sp) == 0
+    # a SwiGLU epilogue needs an even number of rows
+    w3 = cases.gaussian(501, (63, k), 0.02)
+    p3, s3 = kbref.pack_weights_ternary_absmean(w3, 63, k)
+    odd = env.nn.BitLinear.from_packed(p3, s3, None, k, 63)
+    assert lib.kb_linear_forward_rmsnorm(odd.handle, x.data_ptr(), g.data_ptr(), C.c_float(1e-5), 1, y.data_ptr(), 0, 1, am.data_ptr(), env.sp) == E.ERR_UNSUPPORTED
+    t.cuda.synchronize()
+    lay.close()
+    odd.close()
