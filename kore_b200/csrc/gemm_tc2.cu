@@ -14,10 +14,7 @@
 // epilogue warps arrive there through shared::cluster addresses.  No multicast loads.
 //
 // A pipeline stage covers 256 bytes of K (two 128-byte swizzle slabs), so every barrier
-// handshake and tcgen05.commit is paid once per eight MMAs.  The copy ring (activations +
-// packed weights, 40 KB per stage) is four stages deep — its depth over the TMA -> unpack ->
-// MMA -> commit round trip bounds the kernel — while the unpacked codes, which live only from
-// the unpack to the end of their MMAs, cycle through two 32 KB buffers.  Warp roles per CTA: 0 TMA,
+// handshake and tcgen05.commit is paid once per eight MMAs.  Warp roles per CTA: 0 TMA,
 // 1 MMA (leader only), 2 TMEM owner, 4-11 unpack (one thread per row and slab), 12-15
 // epilogue.  Every wait is bounded; a wait that gives up records a code in the status word
 // and raises the CTA's abort flag.
@@ -38,18 +35,16 @@ constexpr int BN = 256;   // tokens per pair tile (MMA N)
 constexpr int BNH = 128;  // tokens loaded by each CTA
 constexpr int BK = 128;   // one 128-byte swizzle row of K (a "slab")
 constexpr int SLABS = 2;  // slabs per pipeline stage: barrier traffic is paid once per 256 bytes of K
-constexpr int RS = 4;     // copy ring: stages of raw activations + packed weights
-constexpr int US = 2;     // unpacked-weight buffers
+constexpr int RS = 3;     // pipeline stages: raw (activations + packed weights) + unpacked weights
 constexpr int ACT_SLAB = BNH * BK;                 // 16 KB
 constexpr int ACT_BYTES = SLABS * ACT_SLAB;        // 32 KB
 constexpr int PK_BYTES = BM * (SLABS * BK / 4);    // 8 KB, rows of 64 packed bytes
 constexpr int RAW_BYTES = ACT_BYTES + PK_BYTES;    // 40 KB
 constexpr int UNP_SLAB = BM * BK;                  // 16 KB
 constexpr int UNP_BYTES = SLABS * UNP_SLAB;        // 32 KB
-constexpr int RING_BYTES = RS * RAW_BYTES + US * UNP_BYTES;  // 224 KB
-constexpr int NUM_BARS = 3 * RS + US + 5;
-constexpr int SMEM_BYTES = 1024 + RING_BYTES + 8 * NUM_BARS + 16;
-static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+constexpr int STAGE_BYTES = RAW_BYTES + UNP_BYTES;  // 72 KB
+constexpr int NUM_BARS = 3 * RS + 5;
+constexpr int SMEM_BYTES = 1024 + RS * STAGE_BYTES + 8 * NUM_BARS + 16;
 constexpr int NUM_THREADS = 512;  // warps: 0 TMA, 1 MMA, 2 TMEM, 3 idle, 4-11 unpack, 12-15 epilogue
 constexpr int TMEM_COLS = 2 * BN;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
@@ -122,18 +117,17 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     uint8_t *base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
 
-    auto act_addr = [&](int s) { return base + (uint32_t)s * RAW_BYTES; };
+    auto act_addr = [&](int s) { return base + (uint32_t)s * STAGE_BYTES; };
     auto pk_addr = [&](int s) { return act_addr(s) + ACT_BYTES; };
-    auto unp_addr = [&](int u) { return base + (uint32_t)(RS * RAW_BYTES) + (uint32_t)u * UNP_BYTES; };
-    const uint32_t tail = base + RING_BYTES;
-    auto act_full = [&](int s) { return tail + 8u * s; };              // leader: the pair's activations landed
+    auto unp_addr = [&](int s) { return act_addr(s) + RAW_BYTES; };
+    const uint32_t tail = base + RS * STAGE_BYTES;
+    auto ready = [&](int s) { return tail + 8u * s; };                 // leader: activations landed + weights unpacked
     auto pk_full = [&](int s) { return tail + 8u * (RS + s); };        // local: packed weights landed
     auto empty = [&](int s) { return tail + 8u * (2 * RS + s); };      // local: the stage's MMAs completed
-    auto unp_full = [&](int u) { return tail + 8u * (3 * RS + u); };   // leader: both CTAs' codes written
-    auto tfull = [&](int b) { return tail + 8u * (3 * RS + US + b); };
-    auto tempty = [&](int b) { return tail + 8u * (3 * RS + US + 2 + b); };
-    const uint32_t drain_bar = tail + 8u * (3 * RS + US + 4);
-    uint8_t *tail_ptr = base_ptr + RING_BYTES;
+    auto tfull = [&](int b) { return tail + 8u * (3 * RS + b); };
+    auto tempty = [&](int b) { return tail + 8u * (3 * RS + 2 + b); };
+    const uint32_t drain_bar = tail + 8u * (3 * RS + 4);
+    uint8_t *tail_ptr = base_ptr + RS * STAGE_BYTES;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail_ptr + 8 * NUM_BARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -148,11 +142,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < RS; ++s) {
-            mbar_init(act_full(s), 1);  // leader's producer arrives once carrying the pair's 64 KB of tx
+            // leader's producer arrives once carrying the pair's 64 KB of activation tx;
+            // the 8 unpack warps of each CTA arrive once each
+            mbar_init(ready(s), 17);
             mbar_init(pk_full(s), 1);
             mbar_init(empty(s), 1);  // tcgen05.commit (multicast)
         }
-        for (int u = 0; u < US; ++u) mbar_init(unp_full(u), 16);  // the 8 unpack warps of each CTA
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull(b), 1);      // tcgen05.commit (multicast)
             mbar_init(tempty(b), 8);     // 4 epilogue warps of each CTA (used in the leader)
@@ -188,9 +183,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                     const uint32_t ph = (it / RS) & 1u;
                     if (!(ok = wait_bar<false>(empty(s), ph ^ 1u, abort_flag, p.status, DEV_TIMEOUT_TMA_EMPTY))) break;
                     TRC(0, it);
-                    if (leader) mbar_expect_tx(act_full(s), 2 * ACT_BYTES);
+                    if (leader) mbar_expect_tx(ready(s), 2 * ACT_BYTES);
                     mbar_expect_tx(pk_full(s), PK_BYTES);
-                    const uint32_t lead_bar = mapa(act_full(s), 0);
+                    const uint32_t lead_bar = mapa(ready(s), 0);
 #pragma unroll
                     for (int sl = 0; sl < SLABS; ++sl)
                         tma_load_2d_pair(act_addr(s) + sl * ACT_SLAB, &tmap_x, lead_bar, (kb * SLABS + sl) * BK, nh0);
@@ -220,14 +215,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 GTL2(0, ti);
                 const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % RS, u = it % US;
-                    if (!(ok = wait_bar<false>(act_full(s), (it / RS) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL))) break;
-                    if (!(ok = wait_bar<false>(unp_full(u), (it / US) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL))) break;
+                    const int s = it % RS;
+                    if (!(ok = wait_bar<false>(ready(s), (it / RS) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL))) break;
                     TRC(5, it);
                     tc_fence_after();
 #pragma unroll
                     for (int sl = 0; sl < SLABS; ++sl) {
-                        const uint64_t adesc = umma_desc_sw128(unp_addr(u) + sl * UNP_SLAB);
+                        const uint64_t adesc = umma_desc_sw128(unp_addr(s) + sl * UNP_SLAB);
                         const uint64_t bdesc = umma_desc_sw128(act_addr(s) + sl * ACT_SLAB);
 #pragma unroll
                         for (int k4 = 0; k4 < BK / 32; ++k4)
@@ -253,18 +247,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         bool ok = true;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                const int s = it % RS, u = it % US;
+                const int s = it % RS;
+                // packed weights of round R land only after the producer saw the stage released,
+                // so the unpacked buffer of this stage is free as well
                 if (!(ok = wait_bar<false>(pk_full(s), (it / RS) & 1u, abort_flag, p.status, DEV_TIMEOUT_UNPACK_FULL))) break;
-                // the code buffer is free once the MMAs of iteration it - US have completed: that is
-                // completion number (it - US) / RS of the copy stage they released
-                if (it >= (uint32_t)US) {
-                    const uint32_t prev = it - US;
-                    if (!(ok = wait_bar<false>(empty(prev % RS), (prev / RS) & 1u, abort_flag, p.status, DEV_TIMEOUT_UNPACK_FULL))) break;
-                }
                 if (threadIdx.x == 128) TRC(1, it);
-                if (DBG2(p, 0)) { __syncwarp(); if (lane == 0) mbar_arrive_cluster(mapa(unp_full(u), 0)); continue; }
+                if (DBG2(p, 0)) { __syncwarp(); if (lane == 0) mbar_arrive_cluster(mapa(ready(s), 0)); continue; }
                 const uint8_t *pk = base_ptr + (pk_addr(s) - base) + r * (SLABS * 32) + sl * 32;
-                uint8_t *dst = base_ptr + (unp_addr(u) - base) + sl * UNP_SLAB + r * 128;
+                uint8_t *dst = base_ptr + (unp_addr(s) - base) + sl * UNP_SLAB + r * 128;
                 // the two 16-byte halves are read in an order that spreads a quarter-warp over
                 // all eight 16-byte bank groups (rows are 64 bytes apart)
                 const int first = (r >> 1) & 1;
@@ -283,7 +273,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 }
                 if (!DBG2(p, 1)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(mapa(unp_full(u), 0));
+                if (lane == 0) mbar_arrive_cluster(mapa(ready(s), 0));
                 if (threadIdx.x == 128) TRC(3, it);
             }
         }
