@@ -15,9 +15,12 @@ replayed as one CUDA graph.  value = algorithmic bytes of the step / device time
 The same pool as a single stream-ordered chain (what a decoder's dependent layers look
 like) is reported under "extra".
 
-With N > 1 every rank owns a 4096-row shard of a K=4096 x M=4096*N projection (weak
-scaling: per-GPU work is the N = 1 workload), computes its slice and the slices are
-exchanged so that every rank holds the full y[1, 4096*N].
+With N > 1 the layers of the pool are independent units, so every rank runs the N = 1 step on
+its own pool (weak scaling, no exchange; value = all ranks' bytes / max time over ranks).  What
+does need an exchange is measured beside it under "extra": the same pool as column-sharded
+layers (every rank owns a 4096-row shard of a K=4096 x M=4096*N projection and all ranks end
+each layer with the full y[1, 4096*N]) and the sharded 8192 -> 28672 projection at batch
+1 / 8 / 64 / 512.
 
 All inputs are synthetic (no dataset or checkpoint exists for this path).
 """
@@ -269,76 +272,35 @@ def main():
     main_stream = torch.cuda.Stream(device=dev)
     ld = kernels.act_ld(K_DEC)
 
-    if world == 1:
-        n_streams = max(1, args.streams)
-        fan = StreamFan(torch, main_stream, n_streams)
-        ys = [torch.zeros((1, M_DEC), dtype=torch.float32, device=dev) for _ in fan.side]
-        xqs = [torch.zeros((1, ld), dtype=torch.int8, device=dev) for _ in fan.side]
-        sxs = [torch.zeros(1, dtype=torch.float32, device=dev) for _ in fan.side]
-        sms = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in fan.side]
+    # The headline units are independent layers, so at N > 1 every rank runs the same step on its own
+    # pool (no exchange); the column-sharded variants, which do exchange, are measured under `extra`.
+    n_streams = max(1, args.streams)
+    fan = StreamFan(torch, main_stream, n_streams)
+    ys = [torch.zeros((1, M_DEC), dtype=torch.float32, device=dev) for _ in fan.side]
+    xqs = [torch.zeros((1, ld), dtype=torch.int8, device=dev) for _ in fan.side]
+    sxs = [torch.zeros(1, dtype=torch.float32, device=dev) for _ in fan.side]
+    sms = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in fan.side]
 
-        # several independent layers are in flight at once: the GEMV grid sized for sharing the SMs
-        gemv_path = _cabi.PATH_GEMV_SHARED if n_streams > 1 else _cabi.PATH_GEMV
+    # several independent layers are in flight at once: the GEMV grid sized for sharing the SMs
+    gemv_path = _cabi.PATH_GEMV_SHARED if n_streams > 1 else _cabi.PATH_GEMV
 
-        def step():
-            fan.fork()
-            for j, lay in enumerate(pool):
-                i = j % len(fan.side)
-                sp = fan.side[i].cuda_stream
-                if args.fused_quant:  # quantiser in the GEMV prologue: one launch per layer
-                    _cabi.check(lib.kb_linear_forward_ex(lay.handle, x_dev.data_ptr(), 1, K_DEC, ys[i].data_ptr(), 0, None,
-                                                         gemv_path, None, 0, sp))
-                    continue
-                _cabi.check(lib.kb_quantize_act_i8(x_dev.data_ptr(), 1, K_DEC, xqs[i].data_ptr(), ld, sxs[i].data_ptr(),
-                                                   sms[i].data_ptr(), sp))
-                _cabi.check(lib.kb_linear_forward_q8(lay.handle, xqs[i].data_ptr(), ld, sxs[i].data_ptr(), sms[i].data_ptr(),
-                                                     1, ys[i].data_ptr(), 0, None, gemv_path, sp))
-            fan.join()
+    def step():
+        fan.fork()
+        for j, lay in enumerate(pool):
+            i = j % len(fan.side)
+            sp = fan.side[i].cuda_stream
+            if args.fused_quant:  # quantiser in the GEMV prologue: one launch per layer
+                _cabi.check(lib.kb_linear_forward_ex(lay.handle, x_dev.data_ptr(), 1, K_DEC, ys[i].data_ptr(), 0, None,
+                                                     gemv_path, None, 0, sp))
+                continue
+            _cabi.check(lib.kb_quantize_act_i8(x_dev.data_ptr(), 1, K_DEC, xqs[i].data_ptr(), ld, sxs[i].data_ptr(),
+                                               sms[i].data_ptr(), sp))
+            _cabi.check(lib.kb_linear_forward_q8(lay.handle, xqs[i].data_ptr(), ld, sxs[i].data_ptr(), sms[i].data_ptr(),
+                                                 1, ys[i].data_ptr(), 0, None, gemv_path, sp))
+        fan.join()
 
-        launches_per_step = (1 if args.fused_quant else 2) * pool_n
-        y_view = lambda: ys[(pool_n - 1) % len(fan.side)][0]
-        ctx = None
-    else:
-        from kore_b200 import sharded
-
-        # one exchange context (output buffers + flags) per stream, so that independent layers
-        # overlap their exchange latency exactly as the single-GPU step overlaps launches
-        n_streams = max(1, min(args.streams, 32))
-        while pool_n % (2 * n_streams):
-            n_streams -= 1
-        fan = StreamFan(torch, main_stream, n_streams)
-        ctxs = [sharded.ShardContext(rank, world, m_total, 8, local_rank, dist) for _ in fan.side]
-        shard_path = _cabi.PATH_GEMV if os.environ.get("KB_BENCH_SHARD_PATH") == "gemv" else _cabi.PATH_GEMV_SHARED
-        shard_q8 = os.environ.get("KB_BENCH_SHARD_Q8", "1") != "0"
-        xqs = [torch.zeros((1, ld), dtype=torch.int8, device=dev) for _ in fan.side]
-        sxs = [torch.zeros(1, dtype=torch.float32, device=dev) for _ in fan.side]
-        sms = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in fan.side]
-        ctx = ctxs[0]
-        last = [0, 0]
-
-        def step():
-            fan.fork()
-            for j, lay in enumerate(pool):
-                i = j % len(fan.side)
-                c = ctxs[i]
-                par = c.next_parity()
-                last[0], last[1] = i, par
-                sp = fan.side[i].cuda_stream
-                if shard_q8:  # the N = 1 step's two launches: quantiser, then the GEMV on the codes
-                    _cabi.check(lib.kb_quantize_act_i8(x_dev.data_ptr(), 1, K_DEC, xqs[i].data_ptr(), ld, sxs[i].data_ptr(),
-                                                       sms[i].data_ptr(), sp))
-                    _cabi.check(lib.kb_linear_forward_sharded_q8(lay.handle, xqs[i].data_ptr(), ld, sxs[i].data_ptr(),
-                                                                 sms[i].data_ptr(), 1, c.y_tables_host[par], world, rank,
-                                                                 m_total, rank * M_DEC, shard_path, c.flag_table.data_ptr(),
-                                                                 c.sync_words.data_ptr(), sp))
-                    continue
-                _cabi.check(lib.kb_linear_forward_sharded(lay.handle, x_dev.data_ptr(), 1, K_DEC, c.y_tables_host[par],
-                                                          world, rank, m_total, rank * M_DEC, shard_path, None, 0,
-                                                          c.flag_table.data_ptr(), c.sync_words.data_ptr(), sp))
-            fan.join()
-
-        launches_per_step = pool_n * (2 if shard_q8 else 1)
-        y_view = lambda: ctxs[last[0]].local_y[last[1]][0, rank * M_DEC:(rank + 1) * M_DEC]
+    launches_per_step = (1 if args.fused_quant else 2) * pool_n
+    y_view = lambda: ys[(pool_n - 1) % len(fan.side)][0]
 
     if dist is not None:
         dist.barrier()
@@ -350,8 +312,6 @@ def main():
         t = torch.tensor([sec_per_step], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         sec_per_step = float(t.item())
-        for c in ctxs:
-            c.check_status()
     step_bytes = pool_n * gemv_bytes(M_DEC, K_DEC, 1) * world
     value = step_bytes / sec_per_step / 1e9
     y_chk = y_view().cpu().numpy().copy()  # what the timed path produced for the last layer
@@ -383,8 +343,13 @@ def main():
            "note": "kb_linear_forward_host per layer: pinned x -> device, quantiser + GEMV, y -> host, synchronise"}
     assert (y_host[0] == y_chk).all(), "host entry point and graph replay disagree"
 
-    sharded_extra = None
+    sharded_extra = sharded_step_extra = None
     if world > 1 and not args.no_extras:
+        try:
+            sharded_step_extra = column_sharded_step(torch, lib, _cabi, dist, dev, main_stream, rank, local_rank, world, pool,
+                                                     x_dev, x_pin, args)
+        except Exception as exc:
+            sharded_step_extra = {"error": repr(exc)}
         try:
             sharded_extra = sharded_projection(torch, lib, _cabi, nn, dist, dev, main_stream, rank, world, peaks)
         except Exception as exc:
@@ -393,8 +358,6 @@ def main():
     if rank != 0:
         if dist is not None:
             dist.barrier()
-            for c in ctxs:
-                c.close()
             dist.destroy_process_group()
         return
 
@@ -423,13 +386,13 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "decode_gemv_ternary_4096x4096_batch1" if world == 1 else
-                   f"decode_gemv_ternary_K4096_M{m_total}_batch1_column_sharded_{world}x4096",
+        "config": {"workload": "decode_gemv_ternary_4096x4096_batch1",
                    "pool": pool_n, "pool_bytes": pool_n * M_DEC * K_DEC // 4, "streams": n_streams,
                    "l2": "inputs larger than L2 (pool of separately allocated weight copies)",
                    "quantiser": "absmean per-tensor", "timing": "CUDA events around CUDA-graph replays of the step",
-                   "exchange": None if world == 1 else "epilogue peer stores over NVLink + flag barrier"},
-        "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks.summary(),
+                   "ranks": "every rank runs the step on its own pool of independent layers, no exchange; "
+                            "the column-sharded layers (with their exchange) are under extra" if world > 1 else None},
+        "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps * world, "clocks": clocks.summary(),
     }
     if cpu is not None:
         line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -440,6 +403,8 @@ def main():
             extras["bitnet_3b_shaped_decoder"] = decoder_measurement(torch, dev, peaks)
         except Exception as exc:
             extras["bitnet_3b_shaped_decoder"] = {"error": repr(exc)}
+    if sharded_step_extra:
+        extras["column_sharded_4096_rows_per_rank_step"] = sharded_step_extra
     if sharded_extra:
         extras["sharded_projection_8192_to_28672"] = sharded_extra
     if extras:
@@ -447,8 +412,6 @@ def main():
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
-        for c in ctxs:
-            c.close()
         dist.destroy_process_group()
 
 
@@ -485,6 +448,64 @@ def single_case(torch, lib, _cabi, nn, kernels, dev, args):
     per = e0.elapsed_time(e1) / 1e3 / (args.steps * copies)
     print(json.dumps({"case": args.only, "m": m, "k": k, "n": n, "copies": copies, "us_per_launch": per * 1e6,
                       "GB/s": gemv_bytes(m, k, n) / per / 1e9, "TOPS": 2.0 * m * k * n / per / 1e12}), flush=True)
+
+
+def column_sharded_step(torch, lib, _cabi, dist, dev, main_stream, rank, local_rank, world, pool, x_dev, x_pin, args):
+    """The pool as column-sharded layers: every rank owns a 4096-row shard of a 4096 * world-row layer
+    and all ranks end every layer with the full output (epilogue peer stores over NVLink + the flag
+    barrier fused into the GEMV tail).  Per layer one quantiser launch and one sharded GEMV, one
+    exchange context per stream.  Aggregate GB/s over all ranks, max over ranks."""
+    from kore_b200 import kernels, sharded
+
+    pool_n = len(pool)
+    m_total = M_DEC * world
+    ld = kernels.act_ld(K_DEC)
+    n_streams = max(1, min(args.streams, 32))
+    while pool_n % (2 * n_streams):
+        n_streams -= 1
+    fan = StreamFan(torch, main_stream, n_streams)
+    ctxs = [sharded.ShardContext(rank, world, m_total, 8, local_rank, dist) for _ in fan.side]
+    xqs = [torch.zeros((1, ld), dtype=torch.int8, device=dev) for _ in fan.side]
+    sxs = [torch.zeros(1, dtype=torch.float32, device=dev) for _ in fan.side]
+    sms = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in fan.side]
+    last = [0, 0]
+
+    def step():
+        fan.fork()
+        for j, lay in enumerate(pool):
+            i = j % len(fan.side)
+            c = ctxs[i]
+            par = c.next_parity()
+            last[0], last[1] = i, par
+            sp = fan.side[i].cuda_stream
+            _cabi.check(lib.kb_quantize_act_i8(x_dev.data_ptr(), 1, K_DEC, xqs[i].data_ptr(), ld, sxs[i].data_ptr(),
+                                               sms[i].data_ptr(), sp))
+            _cabi.check(lib.kb_linear_forward_sharded_q8(lay.handle, xqs[i].data_ptr(), ld, sxs[i].data_ptr(),
+                                                         sms[i].data_ptr(), 1, c.y_tables_host[par], world, rank,
+                                                         m_total, rank * M_DEC, _cabi.PATH_GEMV_SHARED,
+                                                         c.flag_table.data_ptr(), c.sync_words.data_ptr(), sp))
+        fan.join()
+
+    dist.barrier()
+    torch.cuda.synchronize()
+    sec, _ = time_graph(torch, step, args.steps, args.warmup, main_stream)
+    torch.cuda.synchronize()
+    t = torch.tensor([sec], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    sec = float(t.item())
+    for c in ctxs:
+        c.check_status()
+    # this rank's slice of the last layer against the host entry point
+    y_host = np.zeros((1, M_DEC), np.float32)
+    _cabi.check(lib.kb_linear_forward_host(pool[-1].handle, x_pin.data_ptr(), 1, K_DEC, y_host.ctypes.data))
+    mine = ctxs[last[0]].local_y[last[1]][0, rank * M_DEC:(rank + 1) * M_DEC].cpu().numpy()
+    ok = bool((mine == y_host[0]).all())
+    dist.barrier()
+    for c in ctxs:
+        c.close()
+    gbs = pool_n * gemv_bytes(M_DEC, K_DEC, 1) * world / sec / 1e9
+    return {"GB/s_all_ranks": gbs, "ms_per_step": sec * 1e3, "us_per_layer": sec / pool_n * 1e6, "streams": n_streams,
+            "matches_host_entry_point": ok, "exchange": "epilogue peer stores over NVLink + flag barrier fused into the GEMV tail"}
 
 
 def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, peaks):
