@@ -442,6 +442,7 @@ static int launch_one(const GemvParams &p, int tok_groups, bool shared_grid, cud
     const int row_groups = (p.m + R - 1) / R;
     int threads = 256;
     if (env_threads >= 64 && env_threads <= 256 && env_threads % 32 == 0) threads = env_threads;
+    if (p.gamma) threads = 256;  // the normalising prologue holds the row in the registers of 256 threads
     const int nwarps = threads / 32;
     const size_t smem = gemv_smem_bytes((size_t)p.kp, NT);
     auto kern = gemv_kernel<NT, R, PF, FUSED, EPI>;
