@@ -211,6 +211,9 @@ constexpr int ATT_MAX_HD = 128;
 constexpr int ATT_UNROLL = 4;
 constexpr int ATT_MAX_SPLITS = 32;
 
+// VEC4 (head_dim a multiple of 4, 16-byte aligned rows): lane l owns dims 4l .. 4l+3 and reads them
+// with one 128-bit load per row; otherwise lane l owns dims l, l + 32, ...
+template <bool VEC4>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
     const float *__restrict__ q, const float *__restrict__ k_cache, const float *__restrict__ v_cache,
     const int *__restrict__ lens, int n_heads, int hd, int lmax, int splits, float *__restrict__ scratch,
@@ -225,14 +228,21 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
     const int chunk = (len + splits - 1) / splits;
     const int j0 = sp * chunk, j1 = min(len, j0 + chunk);
     constexpr int DPL = ATT_MAX_HD / 32;  // dims per lane
-    float qv[DPL], acc[DPL];
-    const float *qrow = q + (size_t)b * d + h * hd;
+    static_assert(DPL == 4, "the vector path reads one float4 per lane");
+    auto dim_of = [&](int i) { return VEC4 ? 4 * lane + i : lane + 32 * i; };
+    auto load_row = [&](const float *row, bool ok, float (&dst)[DPL]) {
+        if (VEC4) {
+            const float4 f = (ok && 4 * lane < hd) ? *reinterpret_cast<const float4 *>(row + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+            dst[0] = f.x; dst[1] = f.y; dst[2] = f.z; dst[3] = f.w;
+        } else {
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) {
-        const int p = lane + 32 * i;
-        qv[i] = p < hd ? qrow[p] : 0.0f;
-        acc[i] = 0.0f;
-    }
+            for (int i = 0; i < DPL; ++i) dst[i] = (ok && lane + 32 * i < hd) ? row[lane + 32 * i] : 0.0f;
+        }
+    };
+    float qv[DPL], acc[DPL];
+    load_row(q + (size_t)b * d + h * hd, true, qv);
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
     const float scale = __fdiv_rn(1.0f, sqrtf((float)hd));
     const float *kb_ = k_cache + (size_t)b * lmax * d + h * hd;
     const float *vb = v_cache + (size_t)b * lmax * d + h * hd;
@@ -245,13 +255,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
         for (int u = 0; u < ATT_UNROLL; ++u) {
             const int j = jb + u * ATT_WARPS;
             const bool ok = j < j1;
-            const float *kr = kb_ + (size_t)(ok ? j : j0) * d, *vr = vb + (size_t)(ok ? j : j0) * d;
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) {
-                const int p = lane + 32 * i;
-                kk[u][i] = (ok && p < hd) ? kr[p] : 0.0f;
-                vv[u][i] = (ok && p < hd) ? vr[p] : 0.0f;
-            }
+            load_row(kb_ + (size_t)(ok ? j : j0) * d, ok, kk[u]);
+            load_row(vb + (size_t)(ok ? j : j0) * d, ok, vv[u]);
         }
 #pragma unroll
         for (int u = 0; u < ATT_UNROLL; ++u) {
@@ -272,7 +277,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
     }
     if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) s_acc[warp][lane + 32 * i] = acc[i];
+    for (int i = 0; i < DPL; ++i)
+        if (dim_of(i) < ATT_MAX_HD) s_acc[warp][dim_of(i)] = acc[i];
     __syncthreads();
     // merge the warps of this CTA (threads 0..hd-1 each own one output dim)
     float cm = -INFINITY;
@@ -388,9 +394,14 @@ int kb_attn_decode(const float *q, const float *k_cache, const float *v_cache, c
     if (splits > 1 && (!scratch || scratch_bytes < need)) splits = 1;
     int *counters = reinterpret_cast<int *>(scratch);
     float *parts = scratch ? reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + (bh * sizeof(int) + 255) / 256 * 256) : nullptr;
-    cudaError_t e = launch_pdl(attn_decode_kernel, dim3((unsigned)(bh * splits)), dim3(ATT_WARPS * 32),
-                               static_cast<cudaStream_t>(stream), q, k_cache, v_cache, lens, n_heads, head_dim, lmax, splits,
-                               parts, counters, out);
+    const bool vec4 = head_dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) |
+                                             reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
+    cudaError_t e = vec4 ? launch_pdl(attn_decode_kernel<true>, dim3((unsigned)(bh * splits)), dim3(ATT_WARPS * 32),
+                                      static_cast<cudaStream_t>(stream), q, k_cache, v_cache, lens, n_heads, head_dim, lmax,
+                                      splits, parts, counters, out)
+                         : launch_pdl(attn_decode_kernel<false>, dim3((unsigned)(bh * splits)), dim3(ATT_WARPS * 32),
+                                      static_cast<cudaStream_t>(stream), q, k_cache, v_cache, lens, n_heads, head_dim, lmax,
+                                      splits, parts, counters, out);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "attention launch");
 }
 

@@ -162,9 +162,10 @@ def test_swiglu_epilogue_and_prescaled_projection(env, n, f, k):
     down.close()
 
 
-def test_rope_kv_and_attention(env):
+@pytest.mark.parametrize("d_model", [128, 120])  # head_dim 32 (128-bit key/value loads) and 30 (scalar loads)
+def test_rope_kv_and_attention(env, d_model):
     t = env.torch
-    cfg = env.decoder.DecoderConfig(n_layers=1, d_model=128, n_heads=4, d_ff=256, vocab=50, max_len=24)
+    cfg = env.decoder.DecoderConfig(n_layers=1, d_model=d_model, n_heads=4, d_ff=256, vocab=50, max_len=24)
     cos, sin = env.decoder.rope_tables(cfg)
     H, hd, d = cfg.n_heads, cfg.head_dim, cfg.d_model
     batch, lmax = 3, cfg.max_len
