@@ -49,9 +49,10 @@ struct Linear {
     float *bias;    // [m_alloc] or nullptr
     int mul, off;
     CUtensorMap tmap_w;    // 2-D map over w2 for the GEMM (box 32 B x 128 rows)
-    CUtensorMap tmap_w64;  // same tensor, box 64 B x 128 rows (CTA-pair GEMM: two K slabs per stage)
+    CUtensorMap tmap_w64;  // same tensor, box 64 B x 128 rows
+    CUtensorMap tmap_w128;  // same tensor, box 128 B x 128 rows, 128-byte swizzle (CTA-pair GEMM: four K slabs per tile)
     bool has_tmap;
-    bool has_tmap64;
+    bool has_tmap64, has_tmap128;
     int *dev_status;  // one int in device memory
 };
 
@@ -138,6 +139,12 @@ int launch_gemv(const FwdArgs &a, cudaStream_t stream);
 int launch_gemm_tc(const FwdArgs &a, cudaStream_t stream);
 // same contract, CTA-pair kernel (tcgen05 cta_group::2); chosen by launch_gemm_tc for large token counts
 int launch_gemm_tc2(const FwdArgs &a, cudaStream_t stream);
+// tcgen05 GEMM for up to 128 tokens with the unpacked weights in tensor memory
+int launch_gemm_tcs(const FwdArgs &a, cudaStream_t stream);
+// 2-D byte tensor map [rows][row_stride bytes] with box [box_inner bytes x box_rows]; SM count of a device
+int encode_2d(CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t rows, uint64_t row_stride, uint32_t box_inner,
+              uint32_t box_rows, CUtensorMapSwizzle swz);
+int sm_count(int device);
 bool gemv_supports(const Linear *lin, size_t n);
 bool gemm_tc_supports(const Linear *lin, size_t n);
 int encode_weight_tmap(Linear *lin);

@@ -449,6 +449,8 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+}  // namespace
+
 // 2-D byte tensor [rows][row_stride bytes], box [box_inner bytes x box_rows]
 int encode_2d(CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t rows, uint64_t row_stride,
               uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swz) {
@@ -475,6 +477,8 @@ int sm_count(int device) {
     }
     return cached[device];
 }
+
+namespace {
 
 template <int BN>
 int launch_bn(const FwdArgs &a, cudaStream_t stream) {
@@ -519,6 +523,10 @@ int encode_weight_tmap(Linear *lin) {
     // the CTA-pair kernel's map is optional: without it the single-CTA kernel serves every size
     lin->has_tmap64 = rc == KB_OK && encode_2d(&lin->tmap_w64, lin->w2, lin->row_bytes, lin->m_alloc, lin->row_bytes,
                                                BK / 2, BM, CU_TENSOR_MAP_SWIZZLE_NONE) == KB_OK;
+    // 128-byte-wide, swizzled tiles for the CTA-pair kernel (rows shorter than 128 bytes keep the single-CTA kernel)
+    lin->has_tmap128 = rc == KB_OK && lin->row_bytes >= 128 &&
+                       encode_2d(&lin->tmap_w128, lin->w2, lin->row_bytes, lin->m_alloc, lin->row_bytes, BK, BM,
+                                 CU_TENSOR_MAP_SWIZZLE_128B) == KB_OK;
     return rc;
 }
 
@@ -533,11 +541,14 @@ int launch_gemm_tc(const FwdArgs &a, cudaStream_t stream) {
     if (!a.xq || !a.sx || !a.sumq) return fail(KB_ERR_INVALID, "gemm: needs pre-quantised activations");
     if ((reinterpret_cast<uintptr_t>(a.xq) & 15) || (a.ldq % 16) || a.ldq < L->kp)
         return fail(KB_ERR_INVALID, "gemm: xq must be 16-byte aligned with ldq >= %zu and ldq %% 16 == 0", L->kp);
+    // up to 128 tokens: weights unpacked into tensor memory (KB_GEMM_TMEM_A=0 keeps the shared-memory tiles)
+    static const int use_tmem_a = []() { const char *e = getenv("KB_GEMM_TMEM_A"); return e ? atoi(e) : 1; }();
+    if (a.n <= 128 && use_tmem_a && L->has_tmap128) return launch_gemm_tcs(a, stream);
     if (a.n <= 64) return launch_bn<64>(a, stream);
     if (a.n <= 128) return launch_bn<128>(a, stream);
     // full 256-token tiles go to the CTA-pair kernel (KB_GEMM_PAIR=0 keeps the single-CTA one)
     static const int use_pair = []() { const char *e = getenv("KB_GEMM_PAIR"); return e ? atoi(e) : 1; }();
-    if (use_pair && L->has_tmap64) return launch_gemm_tc2(a, stream);
+    if (use_pair && L->has_tmap128) return launch_gemm_tc2(a, stream);
     return launch_bn<256>(a, stream);
 }
 

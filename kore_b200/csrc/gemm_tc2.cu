@@ -7,8 +7,14 @@
 //     each CTA's 128 x 256 int32 accumulator into that CTA's own TMEM;
 //   * per k-block (128 bytes of K) a CTA therefore moves 16 KB of activations + 4 KB of
 //     packed weights through TMA instead of 32 + 4 KB in the single-CTA kernel, which
-//     shortens the copy pipeline's latency per unit of MMA time; a stage (activations, packed
-//     and unpacked weights) is released by one tcgen05.commit multicast to both CTAs.
+//     shortens the copy pipeline's latency per unit of MMA time; a stage (activations and
+//     unpacked weights) is released by one tcgen05.commit multicast to both CTAs;
+//   * the packed weights do not ride in the stage: they arrive as 128-byte-wide, 128-byte-
+//     swizzled tiles (128 rows x 512 codes, four k-blocks) in a ring of their own: one copy
+//     of 128-byte rows instead of four copies of 32-byte rows for the same bytes measured 7 %
+//     faster end to end, and the unpack warps can turn a tile into codes in registers before
+//     the stage they will store into is free.  They release a packed tile themselves when its
+//     last k-block has been read.
 // Barriers the leader's MMA thread waits on live in the leader; the peer's TMA completes its
 // activation bytes on the leader's barrier (cta_group::2 form) and the peer's unpack /
 // epilogue warps arrive there through shared::cluster addresses.  No multicast loads.
@@ -38,13 +44,18 @@ constexpr int SLABS = 2;  // slabs per pipeline stage: barrier traffic is paid o
 constexpr int RS = 3;     // pipeline stages: raw (activations + packed weights) + unpacked weights
 constexpr int ACT_SLAB = BNH * BK;                 // 16 KB
 constexpr int ACT_BYTES = SLABS * ACT_SLAB;        // 32 KB
-constexpr int PK_BYTES = BM * (SLABS * BK / 4);    // 8 KB, rows of 64 packed bytes
-constexpr int RAW_BYTES = ACT_BYTES + PK_BYTES;    // 40 KB
+constexpr int RAW_BYTES = ACT_BYTES;               // 32 KB
 constexpr int UNP_SLAB = BM * BK;                  // 16 KB
 constexpr int UNP_BYTES = SLABS * UNP_SLAB;        // 32 KB
-constexpr int STAGE_BYTES = RAW_BYTES + UNP_BYTES;  // 72 KB
-constexpr int NUM_BARS = 3 * RS + 5;
-constexpr int SMEM_BYTES = 1024 + RS * STAGE_BYTES + 8 * NUM_BARS + 16;
+constexpr int STAGE_BYTES = RAW_BYTES + UNP_BYTES;  // 64 KB
+// Packed weights travel in their own ring of 128-byte-wide tiles (128 rows x 128 B = 16 KB = four
+// slabs = two stages).
+constexpr int PKS = 2;                              // packed-weight tiles in flight
+constexpr int PKT_STAGES = 2;                       // stages covered by one packed tile
+constexpr int PKT_BYTES = BM * 128;                 // 16 KB, 128-byte swizzle
+constexpr int NUM_BARS = 2 * RS + 2 * PKS + 5;
+constexpr int SMEM_BYTES = 1024 + RS * STAGE_BYTES + PKS * PKT_BYTES + 8 * NUM_BARS + 16;
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 constexpr int NUM_THREADS = 512;  // warps: 0 TMA, 1 MMA, 2 TMEM, 3 idle, 4-11 unpack, 12-15 epilogue
 constexpr int TMEM_COLS = 2 * BN;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
@@ -118,16 +129,17 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
     uint8_t *base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
 
     auto act_addr = [&](int s) { return base + (uint32_t)s * STAGE_BYTES; };
-    auto pk_addr = [&](int s) { return act_addr(s) + ACT_BYTES; };
     auto unp_addr = [&](int s) { return act_addr(s) + RAW_BYTES; };
-    const uint32_t tail = base + RS * STAGE_BYTES;
+    auto pkt_addr = [&](int q) { return base + (uint32_t)(RS * STAGE_BYTES) + (uint32_t)q * PKT_BYTES; };
+    const uint32_t tail = base + RS * STAGE_BYTES + PKS * PKT_BYTES;
     auto ready = [&](int s) { return tail + 8u * s; };                 // leader: activations landed + weights unpacked
-    auto pk_full = [&](int s) { return tail + 8u * (RS + s); };        // local: packed weights landed
-    auto empty = [&](int s) { return tail + 8u * (2 * RS + s); };      // local: the stage's MMAs completed
-    auto tfull = [&](int b) { return tail + 8u * (3 * RS + b); };
-    auto tempty = [&](int b) { return tail + 8u * (3 * RS + 2 + b); };
-    const uint32_t drain_bar = tail + 8u * (3 * RS + 4);
-    uint8_t *tail_ptr = base_ptr + RS * STAGE_BYTES;
+    auto empty = [&](int s) { return tail + 8u * (RS + s); };          // local: the stage's MMAs completed
+    auto pk_full = [&](int q) { return tail + 8u * (2 * RS + q); };    // local: a packed-weight tile landed
+    auto pk_empty = [&](int q) { return tail + 8u * (2 * RS + PKS + q); };  // local: the tile has been unpacked
+    auto tfull = [&](int b) { return tail + 8u * (2 * RS + 2 * PKS + b); };
+    auto tempty = [&](int b) { return tail + 8u * (2 * RS + 2 * PKS + 2 + b); };
+    const uint32_t drain_bar = tail + 8u * (2 * RS + 2 * PKS + 4);
+    uint8_t *tail_ptr = base_ptr + RS * STAGE_BYTES + PKS * PKT_BYTES;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail_ptr + 8 * NUM_BARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -145,8 +157,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
             // leader's producer arrives once carrying the pair's 64 KB of activation tx;
             // the 8 unpack warps of each CTA arrive once each
             mbar_init(ready(s), 17);
-            mbar_init(pk_full(s), 1);
             mbar_init(empty(s), 1);  // tcgen05.commit (multicast)
+        }
+        for (int q = 0; q < PKS; ++q) {
+            mbar_init(pk_full(q), 1);
+            mbar_init(pk_empty(q), 8);  // the CTA's 8 unpack warps, after their last read of the tile
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull(b), 1);      // tcgen05.commit (multicast)
@@ -173,31 +188,36 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t it = 0, pit = 0;  // stage counter, packed-tile counter
             bool ok = true;
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
                 const int m0 = (tile / tiles_n) * (2 * BM) + (int)rank * BM;
                 const int nh0 = (tile % tiles_n) * BN + (int)rank * BNH;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    if ((kb % PKT_STAGES) == 0) {  // the packed weights of this and the next stage: one 128-byte-wide tile
+                        const int q = pit % PKS;
+                        if (!(ok = wait_bar<false>(pk_empty(q), ((pit / PKS) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_TMA_EMPTY))) break;
+                        mbar_expect_tx(pk_full(q), PKT_BYTES);
+                        tma_load_2d(pkt_addr(q), &tmap_w, pk_full(q), kb * (SLABS * BK / 4), m0);
+                        ++pit;
+                    }
                     const int s = it % RS;
                     const uint32_t ph = (it / RS) & 1u;
                     if (!(ok = wait_bar<false>(empty(s), ph ^ 1u, abort_flag, p.status, DEV_TIMEOUT_TMA_EMPTY))) break;
                     TRC(0, it);
                     if (leader) mbar_expect_tx(ready(s), 2 * ACT_BYTES);
-                    mbar_expect_tx(pk_full(s), PK_BYTES);
                     const uint32_t lead_bar = mapa(ready(s), 0);
 #pragma unroll
                     for (int sl = 0; sl < SLABS; ++sl)
                         tma_load_2d_pair(act_addr(s) + sl * ACT_SLAB, &tmap_x, lead_bar, (kb * SLABS + sl) * BK, nh0);
-                    tma_load_2d(pk_addr(s), &tmap_w, pk_full(s), kb * (SLABS * BK / 4), m0);
                 }
             }
-            // drain the packed-weight copies (their barrier is local); the activation copies
+            // drain the packed-weight copies (their barriers are local); the activation copies
             // are accounted on the leader's barrier, which the leader's MMA thread drains
-            const uint32_t issued = it;
-            for (uint32_t j = (issued > (uint32_t)RS ? issued - RS : 0); j < issued; ++j) {
+            const uint32_t issued = pit;
+            for (uint32_t j = (issued > (uint32_t)PKS ? issued - PKS : 0); j < issued; ++j) {
                 bool landed = false;
-                for (uint32_t i = 0; i < WAIT_LIMIT && !landed; ++i) landed = mbar_try_wait(pk_full(j % RS), (j / RS) & 1u);
+                for (uint32_t i = 0; i < WAIT_LIMIT && !landed; ++i) landed = mbar_try_wait(pk_full(j % PKS), (j / PKS) & 1u);
                 if (!landed) atomicCAS(p.status, 0, DEV_TIMEOUT_DRAIN);
             }
         }
@@ -243,34 +263,55 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         // ---------------- unpack: packed 2-bit -> swizzled code bytes (both CTAs) ----------------
         // thread = (row r, slab sl): 32 packed bytes -> one 128-byte swizzled row of that slab
         const int r = (threadIdx.x - 128) & 127, sl = (threadIdx.x - 128) >> 7;
-        uint32_t it = 0;
+        uint32_t it = 0, pit = 0;
         bool ok = true;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
                 const int s = it % RS;
-                // packed weights of round R land only after the producer saw the stage released,
-                // so the unpacked buffer of this stage is free as well
-                if (!(ok = wait_bar<false>(pk_full(s), (it / RS) & 1u, abort_flag, p.status, DEV_TIMEOUT_UNPACK_FULL))) break;
+                const int half = kb % PKT_STAGES;  // which stage of the packed tile
+                if (half == 0) ++pit;
+                const uint32_t pt = pit - 1;
+                const int q = pt % PKS;
+                if (!(ok = wait_bar<false>(pk_full(q), (pt / PKS) & 1u, abort_flag, p.status, DEV_TIMEOUT_UNPACK_FULL))) break;
                 if (threadIdx.x == 128) TRC(1, it);
-                if (DBG2(p, 0)) { __syncwarp(); if (lane == 0) mbar_arrive_cluster(mapa(ready(s), 0)); continue; }
-                const uint8_t *pk = base_ptr + (pk_addr(s) - base) + r * (SLABS * 32) + sl * 32;
-                uint8_t *dst = base_ptr + (unp_addr(s) - base) + sl * UNP_SLAB + r * 128;
-                // the two 16-byte halves are read in an order that spreads a quarter-warp over
-                // all eight 16-byte bank groups (rows are 64 bytes apart)
-                const int first = (r >> 1) & 1;
-                const uint4 h0 = *reinterpret_cast<const uint4 *>(pk + 16 * first);
-                const uint4 h1 = *reinterpret_cast<const uint4 *>(pk + 16 * (first ^ 1));
-                const uint4 lo = first ? h1 : h0, hi = first ? h0 : h1;
+                const bool last_use = half == PKT_STAGES - 1 || kb == num_kb - 1;
+                // packed tile: 128-byte rows, 128-byte swizzle (16-byte chunk c of row r sits at chunk c ^ (r & 7)),
+                // so the eight rows of a quarter-warp read eight different bank groups
+                const uint8_t *prow = base_ptr + (pkt_addr(q) - base) + r * 128;
+                const int c0 = half * 4 + sl * 2;
+                uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+                if (!DBG2(p, 0)) {
+                    lo = *reinterpret_cast<const uint4 *>(prow + (((c0) ^ (r & 7)) << 4));
+                    hi = *reinterpret_cast<const uint4 *>(prow + (((c0 + 1) ^ (r & 7)) << 4));
+                }
+                // the codes are ready in registers before the stage's buffer is asked for: only the
+                // stores sit between the stage being freed and its being ready again
                 const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                uint4 o[8];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    uint4 o;
-                    o.x = w[c] & 0x03030303u;
-                    o.y = (w[c] >> 2) & 0x03030303u;
-                    o.z = (w[c] >> 4) & 0x03030303u;
-                    o.w = (w[c] >> 6) & 0x03030303u;
-                    if (!DBG2(p, 2)) *reinterpret_cast<uint4 *>(dst + ((c ^ (r & 7)) << 4)) = o;
+                    o[c].x = w[c] & 0x03030303u;
+                    o[c].y = (w[c] >> 2) & 0x03030303u;
+                    o[c].z = (w[c] >> 4) & 0x03030303u;
+                    o[c].w = (w[c] >> 6) & 0x03030303u;
                 }
+                if (last_use) {  // this warp has read all it needs from the tile
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(pk_empty(q));
+                }
+                // the code buffer of this stage is free once the MMAs of iteration it - RS have completed
+                if (it >= (uint32_t)RS) {
+                    if (!(ok = wait_bar<false>(empty(s), ((it / RS) - 1u) & 1u, abort_flag, p.status, DEV_TIMEOUT_UNPACK_FULL))) break;
+                }
+                if (DBG2(p, 0)) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa(ready(s), 0));
+                    continue;
+                }
+                uint8_t *dst = base_ptr + (unp_addr(s) - base) + sl * UNP_SLAB + r * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    if (!DBG2(p, 2)) *reinterpret_cast<uint4 *>(dst + ((c ^ (r & 7)) << 4)) = o[c];
                 if (!DBG2(p, 1)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa(ready(s), 0));
@@ -431,7 +472,7 @@ extern "C" int kb_debug_gemm2_trace(unsigned long long *host) {
 int launch_gemm_tc2(const FwdArgs &a, cudaStream_t stream) {
     const Linear *L = a.lin;
     if (a.n == 0) return KB_OK;
-    if (!L->has_tmap) return fail(KB_ERR_UNSUPPORTED, "gemm: weight tensor map missing");
+    if (!L->has_tmap128) return fail(KB_ERR_UNSUPPORTED, "gemm: weight tensor map missing");
     if (!a.xq || !a.sx || !a.sumq) return fail(KB_ERR_INVALID, "gemm: needs pre-quantised activations");
     if ((reinterpret_cast<uintptr_t>(a.xq) & 15) || (a.ldq % 16) || a.ldq < L->kp)
         return fail(KB_ERR_INVALID, "gemm: xq must be 16-byte aligned with ldq >= %zu and ldq %% 16 == 0", L->kp);
@@ -473,7 +514,7 @@ int launch_gemm_tc2(const FwdArgs &a, cudaStream_t stream) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, tmap_x, L->tmap_w64, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, tmap_x, L->tmap_w128, p);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "gemm2 launch");
 }
 
