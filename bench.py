@@ -228,7 +228,7 @@ def main():
     ap.add_argument("--fused-quant", action="store_true",
                     help="N=1: run the activation quantiser inside the GEMV prologue (one launch per layer)")
     ap.add_argument("--no-decoder", action="store_true", help="skip the BitNet-3B-shaped decoder measurement")
-    ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "small_batch", "prefill_up", "prefill_down"],
+    ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "small_batch", "medium_batch", "prefill_up", "prefill_down"],
                     help="run one small case and print its own JSON line (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -418,6 +418,7 @@ def main():
 def single_case(torch, lib, _cabi, nn, kernels, dev, args):
     """One kernel on one small case, a handful of eager launches: the command profiled with ncu."""
     shapes = {"gemv_big": (28672, 8192, 1, 3), "gemv_4096": (4096, 4096, 1, 40), "small_batch": (28672, 8192, 16, 3),
+              "medium_batch": (28672, 8192, 64, 3),
               "prefill_up": (11008, 4096, 2048, 1), "prefill_down": (4096, 11008, 2048, 1)}
     m, k, n, copies = shapes[args.only]
     w = (torch.randn((m, k), generator=torch.Generator().manual_seed(7)) * 0.02).numpy()
@@ -658,8 +659,9 @@ def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, 
     bp, bs = big.packed_weights(), big.scales()
     bigpool = [big] + [nn.BitLinear.from_packed(bp, bs, None, 8192, 28672, device=dev.index) for _ in range(3)]
     del wbig
-    # batch 1: dp4a GEMV; 8 and 16: the kernel KB_PATH_AUTO picks (small-batch MMA kernel)
-    for nb in (1, 8, 16):
+    # batch 1: dp4a GEMV; 8 and 16: the kernel KB_PATH_AUTO picks (small-batch MMA kernel); 64: tcgen05
+    # tile with the weight operand in tensor memory
+    for nb in (1, 8, 16, 64):
         xb = torch.from_numpy(gaussian(5002, (nb, 8192), 1.0)).to(dev)
         yb = torch.empty((nb, 28672), dtype=torch.float32, device=dev)
         xqb, sxb, smb = kernels.quantize_act_i8(xb)
