@@ -40,7 +40,7 @@ def _rank_main(rank, world, port, q):
             for exchange in ("p2p", "collective"):
                 lay = sharded.ShardedLinear(kind, packed, scales, bias, k, m, rank, world, device=rank, ctx=ctx,
                                             dist=dist, exchange=exchange)
-                for n in (1, 3, 5, 16, 200):  # GEMV with fused barrier, small-batch kernel, GEMM
+                for n in (1, 3, 5, 16, 64, 200):  # GEMV with fused barrier, small-batch kernel, both GEMMs
                     for rep in range(3):  # repeated calls exercise the double buffering and epochs
                         x = cases.gaussian(100 * n + rep, (n, k), 1.0)
                         y = lay.forward(torch.from_numpy(x).cuda())
