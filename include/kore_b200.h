@@ -65,6 +65,7 @@ enum {
 enum { KB_PATH_AUTO = 0, KB_PATH_GEMV = 1, KB_PATH_GEMM_TC = 2, KB_PATH_GEMV_SHARED = 3, KB_PATH_GEMV_MMA = 4 };
 
 typedef struct kb_linear kb_linear; /* opaque: device-resident 2-bit weights + scales + bias */
+typedef struct kb_linear_group kb_linear_group; /* opaque: a set of same-shaped layers run in one launch */
 typedef void *kb_stream;            /* a cudaStream_t; NULL = the legacy default stream */
 
 /* ---- library ---- */
@@ -227,6 +228,23 @@ int kb_linear_forward_host(const kb_linear *h, const float *x, size_t n, size_t 
 int kb_linear_forward_static(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *y,
                              kb_stream stream);
 size_t kb_static_scratch_bytes(void);
+
+/* ---- grouped decode: one token through each of several independent layers ----
+ *
+ * `count` BitLinear / QuatLinear layers of the same kind, shape and device, each called once
+ * with its own single-token input (Module::forward, bit_linear.rs:175-237 /
+ * quat_linear.rs:245-319, called once per layer: independent projections such as the experts
+ * or heads of a block, or the same projection of several models).  One launch streams all their
+ * weights: a 4 MiB layer is shorter than any kernel's launch, ramp-up and tail, so launching them
+ * one by one leaves HBM bandwidth unused.  Layer i reads token row i of (xq, sx, sumq) — one
+ * kb_quantize_act_i8 call over the [count, K] matrix of inputs produces all three — and writes
+ * y[i, 0..M) (ldy = 0 means M).  Results are bit-identical to kb_linear_forward_q8 per layer.
+ * The group borrows the handles' device memory: destroy the group before its members. */
+int kb_linear_group_create(const kb_linear *const *handles, size_t count, kb_linear_group **out);
+void kb_linear_group_destroy(kb_linear_group *g);
+size_t kb_linear_group_count(const kb_linear_group *g);
+int kb_linear_group_forward_q8(const kb_linear_group *g, const int8_t *xq, size_t ldq, const float *sx,
+                               const int32_t *sumq, float *y, size_t ldy, kb_stream stream);
 
 /* ---- kernel-shaped one-shots (host pointers), signatures of
  * ternary_matmul (crates/kore-kernels/src/cpu_ternary_matmul.rs:29-36) and

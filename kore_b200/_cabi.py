@@ -47,6 +47,10 @@ SIGNATURES = {
     "kb_attn_decode_scratch_bytes": (_sz, [_sz, C.c_int]),
     "kb_linear_forward_host": (C.c_int, [_vp, _vp, _sz, _sz, _vp]),
     "kb_linear_forward_static": (C.c_int, [_vp, _vp, _sz, _sz, _vp, _vp]),
+    "kb_linear_group_create": (C.c_int, [_vp, _sz, _vp]),
+    "kb_linear_group_destroy": (None, [_vp]),
+    "kb_linear_group_count": (_sz, [_vp]),
+    "kb_linear_group_forward_q8": (C.c_int, [_vp, _vp, _sz, _vp, _vp, _vp, _sz, _vp]),
     "kb_static_scratch_bytes": (_sz, []),
     "kb_ternary_matmul": (C.c_int, [_vp, _sz, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
     "kb_linear_forward_rmsnorm": (C.c_int, [_vp, _vp, _vp, C.c_float, _sz, _vp, _sz, C.c_int, _vp, _vp]),

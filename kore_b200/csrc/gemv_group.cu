@@ -1,0 +1,380 @@
+// Grouped decode GEMV (sm_100a): one token through each of L independent layers of the same
+// shape in ONE launch — y[l, :] = layer_l(x[l, :]).
+//
+// A 4 MiB layer streams in well under a microsecond, less than the launch, ramp-up and tail of
+// any kernel, so launching such layers one by one (even on many streams) leaves a quarter of the
+// HBM bandwidth unused.  Here the L layers form one virtual matrix of L * M rows: every CTA owns a
+// contiguous range of row groups (R rows each), its warps take the groups of the range in turn,
+// and the register pipeline of weight loads (PF chunks x R rows per warp, 512 contiguous bytes
+// per warp instruction) runs across layer boundaries without draining.  The arithmetic per row is
+// that of the single-layer GEMV: (word & (0x03030303 << 2j)) dp4a x, four partial accumulators
+// that are exact multiples of 1, 4, 16, 64, mul * S - off * sum(xq), then (acc * w_scale) * s + bias.
+//
+// Activations: layer l reads token row l of the quantised matrix (int8 codes, scale, code sum),
+// i.e. one quantiser launch over an [L, K] matrix feeds the whole group.  A CTA stages the rows
+// of the layers its range touches (two for ranges shorter than a layer) in shared memory in the
+// GEMV's permuted order; the host grows the grid until they fit.
+#include <cstdlib>
+#include <vector>
+
+#include "common.cuh"
+#include "device_utils.cuh"
+
+namespace kb {
+
+namespace {
+
+constexpr uint32_t GROUP_MAGIC = 0x4b423247u;  // "KB2G"
+constexpr int MAX_STAGED = 32;                 // layers whose activations one CTA may hold
+
+struct LayerRef {
+    const uint8_t *w2;
+    const float *sw;
+    const float *bias;  // nullptr: no bias
+};
+
+struct Group {
+    uint32_t magic;
+    int device;
+    int kind, mul, off;
+    size_t count, m, k, kp, row_bytes;
+    LayerRef *table;  // device, [count]
+};
+
+struct GroupParams {
+    const LayerRef *table;
+    int count, m, kp;
+    size_t row_bytes;
+    const int8_t *xq;
+    size_t ldq;
+    const float *sx;
+    const int32_t *sumq;
+    float *y;
+    size_t ldy;
+    int mul, off;
+    int groups_per_cta;  // row groups per CTA (a multiple of the warps per CTA)
+    int staged;          // activation rows a CTA stages (layers its range can touch)
+};
+
+// same permutation as the single-layer GEMV: inside each 2048-element block, 16-element group g
+// of lane (g % 128) / 4, sub-chunk g % 4 lives at slot (g % 4) * 32 + lane
+__device__ __forceinline__ int group_of_slot(int d) {
+    const int blk = d >> 7, within = d & 127;
+    return (blk << 7) + ((within & 31) << 2) + (within >> 5);
+}
+
+// Sum over the warp of four per-lane values at once: after the call lanes 8r .. 8r+7 hold the
+// total of value r.  Halving the number of live values at each of the first two steps takes
+// 6 shuffles instead of the 20 of four separate butterflies — at K = 4096 a row is only two
+// 512-byte warp loads, so what is spent per row decides whether the kernel is issue-bound.
+__device__ __forceinline__ int warp_reduce4(int v0, int v1, int v2, int v3, int lane) {
+    const bool hi = (lane & 16) != 0, h8 = (lane & 8) != 0;
+    int a = hi ? v2 : v0, b = hi ? v3 : v1;
+    a += __shfl_xor_sync(0xffffffffu, hi ? v0 : v2, 16);
+    b += __shfl_xor_sync(0xffffffffu, hi ? v1 : v3, 16);
+    int c = h8 ? b : a;
+    c += __shfl_xor_sync(0xffffffffu, h8 ? a : b, 8);
+    c += __shfl_xor_sync(0xffffffffu, c, 4);
+    c += __shfl_xor_sync(0xffffffffu, c, 2);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    return c;
+}
+
+// a cursor over the virtual row groups a warp owns: v, v + nwarps, ... ; (layer, g) follow without divisions
+struct Cursor {
+    int v, layer, g;
+    __device__ __forceinline__ void init(int v0, int row_groups) { v = v0; layer = v0 / row_groups; g = v0 - layer * row_groups; }
+    __device__ __forceinline__ void advance(int step, int row_groups) {
+        v += step; g += step;
+        while (g >= row_groups) { g -= row_groups; ++layer; }
+    }
+};
+
+// FULLK: Kp is a multiple of 2048, so every lane of every chunk lies inside the row
+template <int PF, bool FULLK>
+__global__ void __launch_bounds__(256) gemv_group_kernel(const GroupParams p) {
+    constexpr int R = 4;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    uint4 *xs = reinterpret_cast<uint4 *>(smem_raw);  // [staged][slots]
+    __shared__ float s_sx[MAX_STAGED];
+    __shared__ int s_sum[MAX_STAGED];
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int groups16 = p.kp >> 4;
+    const int slots = (groups16 + 127) & ~127;
+    const int nch = (p.kp + 2047) >> 11;
+    const int row_groups = (p.m + R - 1) / R;  // per layer
+    const int total = p.count * row_groups;    // the host checks that this fits
+    const int begin = min(blockIdx.x * p.groups_per_cta, total);
+    const int end = min(begin + p.groups_per_cta, total);
+    const int layer0 = begin / row_groups;
+    const int kc0 = lane * 64;
+
+    // ---- weight pipeline: PF chunks x R rows in registers, cursor over (virtual group, chunk) ----
+    uint4 buf[PF][R];
+#pragma unroll
+    for (int s = 0; s < PF; ++s)
+#pragma unroll
+        for (int r = 0; r < R; ++r) buf[s][r] = make_uint4(0, 0, 0, 0);
+    Cursor lc;
+    lc.init(begin + warp, row_groups);
+    int lci = 0, l_layer = -1;
+    const uint8_t *l_w2 = nullptr;
+    auto issue = [&](uint4(&dst)[R]) {
+        const int kc = kc0 + (lci << 11);
+        if (lc.v < end && (FULLK || kc < p.kp)) {  // registers of a skipped load keep zeros or stale codes nobody consumes
+            if (lc.layer != l_layer) { l_layer = lc.layer; l_w2 = p.table[l_layer].w2; }
+            const uint8_t *src = l_w2 + (size_t)(lc.g * R) * p.row_bytes + (kc >> 2);
+#pragma unroll
+            for (int r = 0; r < R; ++r) dst[r] = ld_stream_v4(src + (size_t)r * p.row_bytes);
+        } else if (!FULLK) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) dst[r] = make_uint4(0, 0, 0, 0);
+        }
+        if (++lci == nch) { lci = 0; lc.advance(nwarps, row_groups); }
+    };
+#pragma unroll
+    for (int s = 0; s < PF; ++s) issue(buf[s]);
+
+    // consume cursor; lane 8r finishes row r of a group and fetches that row's scale and bias one
+    // group ahead, so the epilogue of a group never waits on them
+    Cursor cc, nc;
+    cc.init(begin + warp, row_groups);
+    nc = cc;
+    int cci = 0, ref_layer = -1;
+    const float *ref_sw = nullptr, *ref_bias = nullptr;
+    float my_sw = 0.0f, my_bias = 0.0f, nx_sw = 0.0f, nx_bias = 0.0f;
+    bool my_hb = false, nx_hb = false;
+    const bool finisher = (lane & 7) == 0;
+    const int my_r = lane >> 3;
+    auto fetch_consts = [&](const Cursor &c, float &sw, float &bias, bool &hb) {
+        if (c.v < end && finisher) {
+            if (c.layer != ref_layer) {
+                const LayerRef ref = p.table[c.layer];
+                ref_layer = c.layer; ref_sw = ref.sw; ref_bias = ref.bias;
+            }
+            const int row = c.g * R + my_r;  // rows up to m_alloc - 1 are allocated
+            sw = ref_sw[row];
+            hb = ref_bias != nullptr;
+            bias = hb ? ref_bias[row] : 0.0f;
+        }
+    };
+    fetch_consts(nc, my_sw, my_bias, my_hb);
+    nc.advance(nwarps, row_groups);
+    fetch_consts(nc, nx_sw, nx_bias, nx_hb);
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // ---- activations of the layers this range touches -> shared memory (int8, permuted) ----
+    for (int idx = threadIdx.x; idx < p.staged * slots; idx += blockDim.x) {
+        const int t = idx / slots, d = idx - t * slots;
+        const int layer = layer0 + t;
+        const int g = group_of_slot(d);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (layer < p.count && g < groups16)
+            v = *reinterpret_cast<const uint4 *>(p.xq + (size_t)layer * p.ldq + (size_t)g * 16);
+        xs[idx] = v;
+    }
+    if ((int)threadIdx.x < p.staged) {
+        const int layer = layer0 + threadIdx.x;
+        s_sx[threadIdx.x] = layer < p.count ? p.sx[layer] : 1.0f;
+        s_sum[threadIdx.x] = layer < p.count ? p.sumq[layer] : 0;
+    }
+    __syncthreads();
+
+    int acc[R][4];
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0;
+
+    while (cc.v < end) {
+#pragma unroll
+        for (int s = 0; s < PF; ++s) {
+            if (cc.v < end) {
+                const uint4 *xrow = xs + (size_t)(cc.layer - layer0) * slots + (cci << 7) + lane;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint4 xv = xrow[32 * i];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const uint32_t w = i == 0 ? buf[s][r].x : (i == 1 ? buf[s][r].y : (i == 2 ? buf[s][r].z : buf[s][r].w));
+                        acc[r][0] = dp4a_u8s8(w & 0x03030303u, xv.x, acc[r][0]);
+                        acc[r][1] = dp4a_u8s8(w & 0x0c0c0c0cu, xv.y, acc[r][1]);
+                        acc[r][2] = dp4a_u8s8(w & 0x30303030u, xv.z, acc[r][2]);
+                        acc[r][3] = dp4a_u8s8(w & 0xc0c0c0c0u, xv.w, acc[r][3]);
+                    }
+                }
+                issue(buf[s]);
+                if (++cci == nch) {
+                    int v[R];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {  // the four partials are exact multiples of 1, 4, 16, 64
+                        v[r] = acc[r][0] + (acc[r][1] >> 2) + (acc[r][2] >> 4) + (acc[r][3] >> 6);
+                        acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0;
+                    }
+                    const int mine = warp_reduce4(v[0], v[1], v[2], v[3], lane);
+                    const int row = cc.g * R + my_r;
+                    if (finisher && row < p.m) {
+                        const int t = cc.layer - layer0;
+                        const int a = p.mul * mine - p.off * s_sum[t];
+                        p.y[(size_t)cc.layer * p.ldy + row] = dequant_out(a, my_sw, s_sx[t], my_bias, my_hb);
+                    }
+                    cci = 0;
+                    cc.advance(nwarps, row_groups);
+                    my_sw = nx_sw; my_bias = nx_bias; my_hb = nx_hb;
+                    nc.advance(nwarps, row_groups);
+                    fetch_consts(nc, nx_sw, nx_bias, nx_hb);
+                }
+            }
+        }
+    }
+}
+
+}  // namespace
+
+namespace {
+
+constexpr int GROUP_R = 4, GROUP_THREADS = 256;
+
+struct ScopedDevice {
+    int prev = -1;
+    bool switched = false;
+    explicit ScopedDevice(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) switched = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~ScopedDevice() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+
+const Group *check_group(const kb_linear_group *g) {
+    const Group *G = reinterpret_cast<const Group *>(g);
+    if (!G || G->magic != GROUP_MAGIC) {
+        fail(KB_ERR_BAD_HANDLE, "null or destroyed kb_linear_group handle");
+        return nullptr;
+    }
+    return G;
+}
+
+int env_int(const char *name, int dflt) {
+    const char *e = getenv(name);
+    return e ? atoi(e) : dflt;
+}
+
+}  // namespace
+
+}  // namespace kb
+
+using namespace kb;
+
+extern "C" {
+
+int kb_linear_group_create(const kb_linear *const *handles, size_t count, kb_linear_group **out) {
+    if (!handles || !out) return fail(KB_ERR_INVALID, "null pointer");
+    if (count == 0) return fail(KB_ERR_INVALID, "empty group");
+    std::vector<LayerRef> host(count);
+    const Linear *first = nullptr;
+    for (size_t i = 0; i < count; ++i) {
+        const Linear *L = reinterpret_cast<const Linear *>(handles[i]);
+        if (!L || L->magic != HANDLE_MAGIC) return fail(KB_ERR_BAD_HANDLE, "null or destroyed kb_linear handle (group member %zu)", i);
+        if (!first) first = L;
+        if (L->kind != first->kind || L->m != first->m || L->k != first->k || L->device != first->device)
+            return fail(KB_ERR_SHAPE, "shape mismatch: group member %zu is [%zu, %zu] kind %d on device %d, member 0 is [%zu, %zu] kind %d on device %d",
+                        i, L->m, L->k, L->kind, L->device, first->m, first->k, first->kind, first->device);
+        host[i] = LayerRef{L->w2, L->scales, L->bias};
+    }
+    const size_t row_groups = (first->m + GROUP_R - 1) / GROUP_R;
+    if (count * row_groups > (size_t)1 << 30) return fail(KB_ERR_UNSUPPORTED, "group too large: %zu layers of %zu rows", count, first->m);
+    ScopedDevice dev(first->device);
+    Group *G = new Group{};
+    G->device = first->device;
+    G->kind = first->kind; G->mul = first->mul; G->off = first->off;
+    G->count = count; G->m = first->m; G->k = first->k; G->kp = first->kp; G->row_bytes = first->row_bytes;
+    cudaError_t e = cudaMalloc(&G->table, count * sizeof(LayerRef));
+    if (e == cudaSuccess) e = cudaMemcpy(G->table, host.data(), count * sizeof(LayerRef), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        if (G->table) cudaFree(G->table);
+        delete G;
+        return cuda_fail(e, "group table");
+    }
+    G->magic = GROUP_MAGIC;
+    *out = reinterpret_cast<kb_linear_group *>(G);
+    return KB_OK;
+}
+
+void kb_linear_group_destroy(kb_linear_group *g) {
+    Group *G = reinterpret_cast<Group *>(g);
+    if (!G || G->magic != GROUP_MAGIC) return;
+    ScopedDevice dev(G->device);
+    G->magic = 0;
+    cudaFree(G->table);
+    delete G;
+}
+
+size_t kb_linear_group_count(const kb_linear_group *g) {
+    const Group *G = check_group(g);
+    return G ? G->count : 0;
+}
+
+int kb_linear_group_forward_q8(const kb_linear_group *g, const int8_t *xq, size_t ldq, const float *sx, const int32_t *sumq,
+                               float *y, size_t ldy, kb_stream stream) {
+    const Group *G = check_group(g);
+    if (!G) return KB_ERR_BAD_HANDLE;
+    if (!xq || !sx || !sumq || !y) return fail(KB_ERR_INVALID, "null activation or output pointer");
+    if ((reinterpret_cast<uintptr_t>(xq) & 15) || (ldq % 16) || ldq < G->kp)
+        return fail(KB_ERR_INVALID, "group: xq must be 16-byte aligned with ldq >= %zu and ldq %% 16 == 0", G->kp);
+    if (ldy == 0) ldy = G->m;
+    if (ldy < G->m) return fail(KB_ERR_SHAPE, "shape mismatch: ldy %zu is smaller than out_features %zu", ldy, G->m);
+    ScopedDevice dev(G->device);
+    const int nwarps = GROUP_THREADS / 32;
+    const long long row_groups = (long long)((G->m + GROUP_R - 1) / GROUP_R);
+    const long long total = (long long)G->count * row_groups;
+    const size_t row_smem = (G->kp + 2047) / 2048 * 2048;  // bytes of one staged activation row
+    // persistent-size grid; grown (smaller ranges touch fewer layers) until a CTA's activation rows fit
+    long long grid = (long long)sm_count(G->device) * env_int("KB_GROUP_CTAS_PER_SM", 2);
+    if (grid < 1) grid = 1;
+    long long per_cta = 0, staged = 0;
+    for (;;) {
+        per_cta = (total + grid - 1) / grid;
+        per_cta = (per_cta + nwarps - 1) / nwarps * nwarps;
+        staged = (per_cta + row_groups - 2) / row_groups + 1;
+        if (staged > (long long)G->count) staged = (long long)G->count;
+        if ((staged <= MAX_STAGED && (size_t)staged * row_smem <= 200 * 1024) || per_cta <= nwarps) break;
+        grid *= 2;
+    }
+    if (staged > MAX_STAGED || (size_t)staged * row_smem > 200 * 1024)
+        return fail(KB_ERR_UNSUPPORTED, "group: %lld activation rows of %zu bytes per CTA do not fit in shared memory", staged, row_smem);
+    grid = (total + per_cta - 1) / per_cta;
+    GroupParams p;
+    p.table = G->table;
+    p.count = (int)G->count; p.m = (int)G->m; p.kp = (int)G->kp;
+    p.row_bytes = G->row_bytes;
+    p.xq = xq; p.ldq = ldq; p.sx = sx; p.sumq = sumq;
+    p.y = y; p.ldy = ldy;
+    p.mul = G->mul; p.off = G->off;
+    p.groups_per_cta = (int)per_cta;
+    p.staged = (int)staged;
+    const bool fullk = G->kp % 2048 == 0;
+    static const int pf = env_int("KB_GROUP_PF", 3);
+    auto kern = pf >= 3 ? (fullk ? gemv_group_kernel<3, true> : gemv_group_kernel<3, false>)
+                        : (fullk ? gemv_group_kernel<2, true> : gemv_group_kernel<2, false>);
+    const size_t smem = (size_t)staged * row_smem;
+    if (smem > 40 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(e, "group smem attribute");
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(GROUP_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "group launch");
+}
+
+}  // extern "C"

@@ -361,3 +361,67 @@ class QLoraLinear:
     def __repr__(self):  # Display impl, lora.rs:360-372
         return (f"QLoraLinear(in={self.in_features}, out={self.out_features}, rank={self.rank}, alpha={self.alpha:g}, "
                 f"base_compression={self.base_compression_ratio():.1f}x, trainable={self.trainable_params()})")
+
+
+class LinearGroup:
+    """Several BitLinear / QuatLinear layers of one shape, each applied to its own single token,
+    in one launch (``kb_linear_group_forward_q8``): ``forward(x)[i] == layers[i].forward(x[i])``
+    bit for bit.  The counterpart in the reference is a loop of ``forward`` calls over
+    independent modules (``crates/kore-nn/src/bit_linear.rs:175-237``)."""
+
+    def __init__(self, layers):
+        layers = list(layers)
+        if not layers:
+            raise KoreError(_cabi.ERR_INVALID, "empty group")
+        self.layers = layers  # keeps the members (and their device memory) alive
+        self.in_features = layers[0].in_features
+        self.out_features = layers[0].out_features
+        arr = (C.c_void_p * len(layers))(*[lay.handle for lay in layers])
+        h = C.c_void_p()
+        _cabi.check(_cabi.lib().kb_linear_group_create(arr, len(layers), C.byref(h)))
+        self._h = h
+
+    def __len__(self):
+        return len(self.layers)
+
+    @property
+    def handle(self):
+        if not self._h:
+            raise KoreError(_cabi.ERR_BAD_HANDLE, "group was closed")
+        return self._h
+
+    def close(self):
+        if getattr(self, "_h", None):
+            _cabi.lib().kb_linear_group_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def forward_q8(self, xq, sx, sumq, out=None):
+        """xq/sx/sumq as returned by ``kernels.quantize_act_i8`` for an input of [len(self), K]."""
+        import torch
+
+        if xq.shape[0] != len(self.layers):
+            raise KoreError(_cabi.ERR_SHAPE, f"shape mismatch: expected [{len(self.layers)}] rows, got {list(xq.shape)}")
+        y = out if out is not None else torch.empty((len(self.layers), self.out_features), dtype=torch.float32, device=xq.device)
+        _cabi.check(_cabi.lib().kb_linear_group_forward_q8(self.handle, xq.data_ptr(), xq.stride(0), sx.data_ptr(), sumq.data_ptr(),
+                                                           y.data_ptr(), y.stride(0), _current_stream_ptr(xq.device.index)))
+        return y
+
+    def forward(self, x):
+        """x: CUDA float32 [len(self), K]; row i goes through layer i."""
+        import torch
+
+        from . import kernels
+
+        if not _is_torch(x) or not x.is_cuda or x.dtype != torch.float32:
+            raise KoreError(_cabi.ERR_DTYPE, "expected a CUDA float32 tensor")
+        if x.dim() != 2 or x.shape[0] != len(self.layers) or x.shape[1] != self.in_features:
+            raise KoreError(_cabi.ERR_SHAPE, f"shape mismatch: expected [{len(self.layers)}, {self.in_features}], got {list(x.shape)}")
+        return self.forward_q8(*kernels.quantize_act_i8(x))
+
+    __call__ = forward
