@@ -239,12 +239,17 @@ size_t kb_static_scratch_bytes(void);
  * one by one leaves HBM bandwidth unused.  Layer i reads token row i of (xq, sx, sumq) — one
  * kb_quantize_act_i8 call over the [count, K] matrix of inputs produces all three — and writes
  * y[i, 0..M) (ldy = 0 means M).  Results are bit-identical to kb_linear_forward_q8 per layer.
+ * kb_linear_group_forward takes the f32 inputs x [count, ldx] (ldx = 0 means K) instead and
+ * quantises them in the kernel's prologue (bit-identical to kb_quantize_act_i8 + the q8 entry):
+ * the whole group is then a single launch.
  * The group borrows the handles' device memory: destroy the group before its members. */
 int kb_linear_group_create(const kb_linear *const *handles, size_t count, kb_linear_group **out);
 void kb_linear_group_destroy(kb_linear_group *g);
 size_t kb_linear_group_count(const kb_linear_group *g);
 int kb_linear_group_forward_q8(const kb_linear_group *g, const int8_t *xq, size_t ldq, const float *sx,
                                const int32_t *sumq, float *y, size_t ldy, kb_stream stream);
+int kb_linear_group_forward(const kb_linear_group *g, const float *x, size_t ldx, float *y, size_t ldy,
+                            kb_stream stream);
 
 /* ---- kernel-shaped one-shots (host pointers), signatures of
  * ternary_matmul (crates/kore-kernels/src/cpu_ternary_matmul.rs:29-36) and

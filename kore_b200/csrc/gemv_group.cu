@@ -45,6 +45,9 @@ struct GroupParams {
     const LayerRef *table;
     int count, m, kp;
     size_t row_bytes;
+    const float *x;  // f32 [count, ldx]: the per-token quantiser runs in the prologue (then xq, sx, sumq are unused)
+    size_t ldx;
+    int k, x_vec4;
     const int8_t *xq;
     size_t ldq;
     const float *sx;
@@ -90,8 +93,11 @@ struct Cursor {
     }
 };
 
-// FULLK: Kp is a multiple of 2048, so every lane of every chunk lies inside the row
-template <int PF, bool FULLK>
+// FULLK: Kp is a multiple of 2048, so every lane of every chunk lies inside the row.
+// FUSED: the activations arrive as f32 and each CTA quantises the rows of the layers it touches
+// itself (per-token absmax -> int8, the quantiser kernel's arithmetic), which costs a CTA that
+// streams for a hundred microseconds a few microseconds once and removes the quantiser launch.
+template <int PF, bool FULLK, bool FUSED>
 __global__ void __launch_bounds__(256) gemv_group_kernel(const GroupParams p) {
     constexpr int R = 4;
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -167,19 +173,76 @@ __global__ void __launch_bounds__(256) gemv_group_kernel(const GroupParams p) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- activations of the layers this range touches -> shared memory (int8, permuted) ----
-    for (int idx = threadIdx.x; idx < p.staged * slots; idx += blockDim.x) {
-        const int t = idx / slots, d = idx - t * slots;
-        const int layer = layer0 + t;
-        const int g = group_of_slot(d);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (layer < p.count && g < groups16)
-            v = *reinterpret_cast<const uint4 *>(p.xq + (size_t)layer * p.ldq + (size_t)g * 16);
-        xs[idx] = v;
-    }
-    if ((int)threadIdx.x < p.staged) {
-        const int layer = layer0 + threadIdx.x;
-        s_sx[threadIdx.x] = layer < p.count ? p.sx[layer] : 1.0f;
-        s_sum[threadIdx.x] = layer < p.count ? p.sumq[layer] : 0;
+    if (FUSED) {
+        __shared__ float red_f[32];
+        __shared__ int red_i[32];
+#pragma unroll 1
+        for (int t = 0; t < p.staged; ++t) {
+            const int layer = layer0 + t;
+            uint4 *dst = xs + (size_t)t * slots;
+            if (layer >= p.count) {
+                for (int d = threadIdx.x; d < slots; d += blockDim.x) dst[d] = make_uint4(0, 0, 0, 0);
+                if (threadIdx.x == 0) { s_sx[t] = 1.0f; s_sum[t] = 0; }
+                continue;
+            }
+            const float *row = p.x + (size_t)layer * p.ldx;
+            float amax = 0.0f;
+            if (p.x_vec4) {
+                const float4 *row4 = reinterpret_cast<const float4 *>(row);
+                for (int i = threadIdx.x; i < (p.k >> 2); i += blockDim.x) {
+                    const float4 v = row4[i];
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                }
+            } else {
+                for (int i = threadIdx.x; i < p.k; i += blockDim.x) amax = fmaxf(amax, fabsf(row[i]));
+            }
+            amax = block_reduce_max(amax, red_f);
+            const float sc = amax < 1e-8f ? 1.0f : __fdiv_rn(amax, 127.0f);
+            const float rs = __frcp_rn(sc);
+            int local_sum = 0;
+            for (int d = threadIdx.x; d < slots; d += blockDim.x) {
+                const int g = group_of_slot(d);
+                uint32_t out[4] = {0u, 0u, 0u, 0u};
+                if (g < groups16) {
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        const int base = g * 16 + w * 4;
+                        float v[4];
+                        if (p.x_vec4 && base + 3 < p.k) {
+                            const float4 f = *reinterpret_cast<const float4 *>(row + base);
+                            v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) v[e] = (base + e < p.k) ? row[base + e] : 0.0f;
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int q = quantise_one_fast(v[e], sc, rs);
+                            local_sum += q;
+                            out[w] |= (uint32_t)(q & 0xff) << (8 * e);
+                        }
+                    }
+                }
+                dst[d] = make_uint4(out[0], out[1], out[2], out[3]);
+            }
+            local_sum = block_reduce_sum(local_sum, red_i);
+            if (threadIdx.x == 0) { s_sx[t] = sc; s_sum[t] = local_sum; }
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < p.staged * slots; idx += blockDim.x) {
+            const int t = idx / slots, d = idx - t * slots;
+            const int layer = layer0 + t;
+            const int g = group_of_slot(d);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (layer < p.count && g < groups16)
+                v = *reinterpret_cast<const uint4 *>(p.xq + (size_t)layer * p.ldq + (size_t)g * 16);
+            xs[idx] = v;
+        }
+        if ((int)threadIdx.x < p.staged) {
+            const int layer = layer0 + threadIdx.x;
+            s_sx[threadIdx.x] = layer < p.count ? p.sx[layer] : 1.0f;
+            s_sum[threadIdx.x] = layer < p.count ? p.sumq[layer] : 0;
+        }
     }
     __syncthreads();
 
@@ -261,6 +324,67 @@ int env_int(const char *name, int dflt) {
     return e ? atoi(e) : dflt;
 }
 
+int group_forward(const Group *G, const float *x, size_t ldx, const int8_t *xq, size_t ldq, const float *sx,
+                  const int32_t *sumq, float *y, size_t ldy, cudaStream_t stream) {
+    if (ldy == 0) ldy = G->m;
+    if (ldy < G->m) return fail(KB_ERR_SHAPE, "shape mismatch: ldy %zu is smaller than out_features %zu", ldy, G->m);
+    ScopedDevice dev(G->device);
+    const int nwarps = GROUP_THREADS / 32;
+    const long long row_groups = (long long)((G->m + GROUP_R - 1) / GROUP_R);
+    const long long total = (long long)G->count * row_groups;
+    const size_t row_smem = (G->kp + 2047) / 2048 * 2048;  // bytes of one staged activation row
+    // persistent-size grid; grown (smaller ranges touch fewer layers) until a CTA's activation rows fit
+    long long grid = (long long)sm_count(G->device) * env_int("KB_GROUP_CTAS_PER_SM", 2);
+    if (grid < 1) grid = 1;
+    long long per_cta = 0, staged = 0;
+    for (;;) {
+        per_cta = (total + grid - 1) / grid;
+        per_cta = (per_cta + nwarps - 1) / nwarps * nwarps;
+        staged = (per_cta + row_groups - 2) / row_groups + 1;
+        if (staged > (long long)G->count) staged = (long long)G->count;
+        if ((staged <= MAX_STAGED && (size_t)staged * row_smem <= 200 * 1024) || per_cta <= nwarps) break;
+        grid *= 2;
+    }
+    if (staged > MAX_STAGED || (size_t)staged * row_smem > 200 * 1024)
+        return fail(KB_ERR_UNSUPPORTED, "group: %lld activation rows of %zu bytes per CTA do not fit in shared memory", staged, row_smem);
+    grid = (total + per_cta - 1) / per_cta;
+    GroupParams p;
+    p.table = G->table;
+    p.count = (int)G->count; p.m = (int)G->m; p.kp = (int)G->kp;
+    p.row_bytes = G->row_bytes;
+    p.x = x; p.ldx = ldx; p.k = (int)G->k;
+    p.x_vec4 = x && (G->k % 4 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    p.xq = xq; p.ldq = ldq; p.sx = sx; p.sumq = sumq;
+    p.y = y; p.ldy = ldy;
+    p.mul = G->mul; p.off = G->off;
+    p.groups_per_cta = (int)per_cta;
+    p.staged = (int)staged;
+    const bool fullk = G->kp % 2048 == 0;
+    static const int pf = env_int("KB_GROUP_PF", 3);
+    void (*kern)(const GroupParams);
+    if (x) kern = pf >= 3 ? (fullk ? gemv_group_kernel<3, true, true> : gemv_group_kernel<3, false, true>)
+                          : (fullk ? gemv_group_kernel<2, true, true> : gemv_group_kernel<2, false, true>);
+    else kern = pf >= 3 ? (fullk ? gemv_group_kernel<3, true, false> : gemv_group_kernel<3, false, false>)
+                        : (fullk ? gemv_group_kernel<2, true, false> : gemv_group_kernel<2, false, false>);
+    const size_t smem = (size_t)staged * row_smem;
+    if (smem > 40 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return cuda_fail(e, "group smem attribute");
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(GROUP_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "group launch");
+}
+
 }  // namespace
 
 }  // namespace kb
@@ -323,58 +447,16 @@ int kb_linear_group_forward_q8(const kb_linear_group *g, const int8_t *xq, size_
     if (!xq || !sx || !sumq || !y) return fail(KB_ERR_INVALID, "null activation or output pointer");
     if ((reinterpret_cast<uintptr_t>(xq) & 15) || (ldq % 16) || ldq < G->kp)
         return fail(KB_ERR_INVALID, "group: xq must be 16-byte aligned with ldq >= %zu and ldq %% 16 == 0", G->kp);
-    if (ldy == 0) ldy = G->m;
-    if (ldy < G->m) return fail(KB_ERR_SHAPE, "shape mismatch: ldy %zu is smaller than out_features %zu", ldy, G->m);
-    ScopedDevice dev(G->device);
-    const int nwarps = GROUP_THREADS / 32;
-    const long long row_groups = (long long)((G->m + GROUP_R - 1) / GROUP_R);
-    const long long total = (long long)G->count * row_groups;
-    const size_t row_smem = (G->kp + 2047) / 2048 * 2048;  // bytes of one staged activation row
-    // persistent-size grid; grown (smaller ranges touch fewer layers) until a CTA's activation rows fit
-    long long grid = (long long)sm_count(G->device) * env_int("KB_GROUP_CTAS_PER_SM", 2);
-    if (grid < 1) grid = 1;
-    long long per_cta = 0, staged = 0;
-    for (;;) {
-        per_cta = (total + grid - 1) / grid;
-        per_cta = (per_cta + nwarps - 1) / nwarps * nwarps;
-        staged = (per_cta + row_groups - 2) / row_groups + 1;
-        if (staged > (long long)G->count) staged = (long long)G->count;
-        if ((staged <= MAX_STAGED && (size_t)staged * row_smem <= 200 * 1024) || per_cta <= nwarps) break;
-        grid *= 2;
-    }
-    if (staged > MAX_STAGED || (size_t)staged * row_smem > 200 * 1024)
-        return fail(KB_ERR_UNSUPPORTED, "group: %lld activation rows of %zu bytes per CTA do not fit in shared memory", staged, row_smem);
-    grid = (total + per_cta - 1) / per_cta;
-    GroupParams p;
-    p.table = G->table;
-    p.count = (int)G->count; p.m = (int)G->m; p.kp = (int)G->kp;
-    p.row_bytes = G->row_bytes;
-    p.xq = xq; p.ldq = ldq; p.sx = sx; p.sumq = sumq;
-    p.y = y; p.ldy = ldy;
-    p.mul = G->mul; p.off = G->off;
-    p.groups_per_cta = (int)per_cta;
-    p.staged = (int)staged;
-    const bool fullk = G->kp % 2048 == 0;
-    static const int pf = env_int("KB_GROUP_PF", 3);
-    auto kern = pf >= 3 ? (fullk ? gemv_group_kernel<3, true> : gemv_group_kernel<3, false>)
-                        : (fullk ? gemv_group_kernel<2, true> : gemv_group_kernel<2, false>);
-    const size_t smem = (size_t)staged * row_smem;
-    if (smem > 40 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return cuda_fail(e, "group smem attribute");
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(GROUP_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
-    return e == cudaSuccess ? KB_OK : cuda_fail(e, "group launch");
+    return group_forward(G, nullptr, 0, xq, ldq, sx, sumq, y, ldy, static_cast<cudaStream_t>(stream));
+}
+
+int kb_linear_group_forward(const kb_linear_group *g, const float *x, size_t ldx, float *y, size_t ldy, kb_stream stream) {
+    const Group *G = check_group(g);
+    if (!G) return KB_ERR_BAD_HANDLE;
+    if (!x || !y) return fail(KB_ERR_INVALID, "null activation or output pointer");
+    if (ldx == 0) ldx = G->k;
+    if (ldx < G->k) return fail(KB_ERR_SHAPE, "shape mismatch: expected [%zu], got row stride %zu", G->k, ldx);
+    return group_forward(G, x, ldx, nullptr, 0, nullptr, nullptr, y, ldy, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

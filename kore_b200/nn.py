@@ -412,16 +412,20 @@ class LinearGroup:
                                                            y.data_ptr(), y.stride(0), _current_stream_ptr(xq.device.index)))
         return y
 
-    def forward(self, x):
-        """x: CUDA float32 [len(self), K]; row i goes through layer i."""
+    def forward(self, x, out=None):
+        """x: CUDA float32 [len(self), K]; row i goes through layer i (one launch, the per-token
+        quantiser runs in the kernel's prologue)."""
         import torch
-
-        from . import kernels
 
         if not _is_torch(x) or not x.is_cuda or x.dtype != torch.float32:
             raise KoreError(_cabi.ERR_DTYPE, "expected a CUDA float32 tensor")
         if x.dim() != 2 or x.shape[0] != len(self.layers) or x.shape[1] != self.in_features:
             raise KoreError(_cabi.ERR_SHAPE, f"shape mismatch: expected [{len(self.layers)}, {self.in_features}], got {list(x.shape)}")
-        return self.forward_q8(*kernels.quantize_act_i8(x))
+        if x.stride(1) != 1:
+            x = x.contiguous()
+        y = out if out is not None else torch.empty((len(self.layers), self.out_features), dtype=torch.float32, device=x.device)
+        _cabi.check(_cabi.lib().kb_linear_group_forward(self.handle, x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0),
+                                                        _current_stream_ptr(x.device.index)))
+        return y
 
     __call__ = forward

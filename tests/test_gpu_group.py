@@ -49,8 +49,13 @@ def test_group_matches_oracle_per_layer(torch, kind, quantiser, count, m, k):
     layers, raw = _make(kind, quantiser, count, m, k, True, 1000 + count + m)
     grp = nn.LinearGroup(layers)
     assert len(grp) == count
+    from kore_b200 import kernels
+
     x = cases.gaussian(7 + count, (count, k), 1.0)
-    y = grp(torch.from_numpy(x).cuda()).cpu().numpy()
+    xd = torch.from_numpy(x).cuda()
+    y = grp(xd).cpu().numpy()  # f32 in: quantiser in the kernel's prologue
+    y_q8 = grp.forward_q8(*kernels.quantize_act_i8(xd)).cpu().numpy()  # quantised beforehand
+    assert (y == y_q8).all()
     for i, (packed, scales, bias) in enumerate(raw):
         y_ref, _ = kbref.q_forward(kind, packed, scales, bias, m, k, x[i : i + 1], threads=2)
         assert (y[i] == y_ref[0]).all(), f"layer {i}"
@@ -122,5 +127,32 @@ def test_group_errors(torch):
     assert lib.kb_linear_group_forward_q8(None, None, 0, None, None, None, 0, None) == _cabi.ERR_BAD_HANDLE
     assert lib.kb_linear_group_forward_q8(grp.handle, None, 0, None, None, None, 0, None) == _cabi.ERR_INVALID
     assert lib.kb_linear_group_count(grp.handle) == 2
+    assert lib.kb_linear_group_forward(grp.handle, None, 0, None, 0, None) == _cabi.ERR_INVALID
+    xs = torch.zeros((2, 128), device="cuda")
+    ys = torch.zeros((2, 64), device="cuda")
+    assert lib.kb_linear_group_forward(grp.handle, xs.data_ptr(), 100, ys.data_ptr(), 0, None) == _cabi.ERR_SHAPE
+    assert lib.kb_linear_group_forward(grp.handle, xs.data_ptr(), 0, ys.data_ptr(), 10, None) == _cabi.ERR_SHAPE
     grp.close()
     lib.kb_linear_group_destroy(None)  # harmless
+
+
+def test_group_f32_input_strided_and_unaligned(torch):
+    """Rows of x that are neither contiguous nor 16-byte aligned take the scalar path of the prologue."""
+    from kore_b200 import nn
+
+    count, m, k = 6, 96, 333
+    layers, raw = _make(Q, "reference", count, m, k, True, 400)
+    grp = nn.LinearGroup(layers)
+    x = cases.gaussian(9, (count, k), 1.0)
+    wide = torch.zeros((count, k + 3), dtype=torch.float32, device="cuda")
+    wide[:, 1 : k + 1] = torch.from_numpy(x).cuda()
+    y = grp(wide[:, 1 : k + 1]).cpu().numpy()
+    for i, (packed, scales, bias) in enumerate(raw):
+        y_ref, _ = kbref.q_forward(Q, packed, scales, bias, m, k, x[i : i + 1], threads=2)
+        assert (y[i] == y_ref[0]).all(), f"layer {i}"
+    # an all-zero row quantises with scale 1 (the reference's 1e-8 rule)
+    x[2] = 0.0
+    y = grp(torch.from_numpy(x).cuda()).cpu().numpy()
+    y_ref, _ = kbref.q_forward(Q, raw[2][0], raw[2][1], raw[2][2], m, k, x[2:3], threads=2)
+    assert (y[2] == y_ref[0]).all()
+    grp.close()
