@@ -413,7 +413,11 @@ def main():
     tpath = os.path.join(ROOT, "profiles", "gemv_traffic.json")
     if os.path.exists(tpath):
         with open(tpath) as f:
-            roofline["traffic"] = json.load(f).get("dram_bytes_per_launch_4096x4096_b1")
+            tj = json.load(f)
+            roofline["traffic"] = tj.get("dram_bytes_per_launch_4096x4096_b1")
+            if grouped and tj.get("dram_bytes_per_layer_group_kernel_4096x4096"):
+                # captured on a 40-layer pool; the kernel's traffic grows with the number of layers
+                roofline["traffic"] = tj["dram_bytes_per_layer_group_kernel_4096x4096"] * pool_n
 
     cpu = cpu_reference_arm(budget_s=12.0) if world == 1 else None
 
