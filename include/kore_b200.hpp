@@ -196,6 +196,29 @@ public:
 };
 
 // ---- kore-kernels shaped free functions: a_packed wire format, b [K,N], result [M,N] ----
+// Several layers of one kind, shape and device, each applied to its own single token in ONE launch
+// (device pointers: x [count, K] f32 -> y [count, M] f32 on `stream`).  Equivalent, bit for bit, to
+// calling forward on every member with its row; the group borrows the members' device memory, so
+// it must be destroyed before them.
+class LinearGroup {
+  public:
+    explicit LinearGroup(const std::vector<const QuantLinear *> &members) {
+        std::vector<const kb_linear *> hs;
+        for (const QuantLinear *m : members) hs.push_back(m ? m->handle() : nullptr);
+        check(kb_linear_group_create(hs.data(), hs.size(), &g_));
+    }
+    LinearGroup(const LinearGroup &) = delete;
+    LinearGroup &operator=(const LinearGroup &) = delete;
+    ~LinearGroup() { kb_linear_group_destroy(g_); }
+    size_t size() const { return kb_linear_group_count(g_); }
+    void forward_device(const float *x, size_t ldx, float *y, size_t ldy, kb_stream stream) const {
+        check(kb_linear_group_forward(g_, x, ldx, y, ldy, stream));
+    }
+
+  private:
+    kb_linear_group *g_ = nullptr;
+};
+
 inline std::vector<float> ternary_matmul(const std::vector<uint8_t> &a_packed, const std::vector<float> &a_scales,
                                          const std::vector<float> &b, size_t m, size_t n, size_t k) {
     if (b.size() < k * n) throw KoreError(KoreError::StorageError, "b too small");

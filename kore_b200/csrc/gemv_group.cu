@@ -83,6 +83,44 @@ __device__ __forceinline__ int warp_reduce4(int v0, int v1, int v2, int v3, int 
     return c;
 }
 
+// block-wide reductions of two values at once (one barrier pair for both rows of a prologue pass)
+__device__ __forceinline__ void block_max2(float &a, float &b, float *scratch /* [64] */) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, o));
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) { scratch[warp] = a; scratch[32 + warp] = b; }
+    __syncthreads();
+    a = lane < nwarps ? scratch[lane] : 0.0f;
+    b = lane < nwarps ? scratch[32 + lane] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, o));
+    }
+}
+__device__ __forceinline__ void block_sum2(int &a, int &b, int *scratch /* [64] */) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        b += __shfl_xor_sync(0xffffffffu, b, o);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) { scratch[warp] = a; scratch[32 + warp] = b; }
+    __syncthreads();
+    a = lane < nwarps ? scratch[lane] : 0;
+    b = lane < nwarps ? scratch[32 + lane] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        b += __shfl_xor_sync(0xffffffffu, b, o);
+    }
+}
+
 // a cursor over the virtual row groups a warp owns: v, v + nwarps, ... ; (layer, g) follow without divisions
 struct Cursor {
     int v, layer, g;
@@ -174,59 +212,88 @@ __global__ void __launch_bounds__(256) gemv_group_kernel(const GroupParams p) {
 
     // ---- activations of the layers this range touches -> shared memory (int8, permuted) ----
     if (FUSED) {
-        __shared__ float red_f[32];
-        __shared__ int red_i[32];
+        // two rows per pass: their loads are in flight together and share the block reductions
+        __shared__ float red_f[64];
+        __shared__ int red_i[64];
 #pragma unroll 1
-        for (int t = 0; t < p.staged; ++t) {
-            const int layer = layer0 + t;
-            uint4 *dst = xs + (size_t)t * slots;
-            if (layer >= p.count) {
-                for (int d = threadIdx.x; d < slots; d += blockDim.x) dst[d] = make_uint4(0, 0, 0, 0);
-                if (threadIdx.x == 0) { s_sx[t] = 1.0f; s_sum[t] = 0; }
-                continue;
+        for (int t0 = 0; t0 < p.staged; t0 += 2) {
+            const float *row[2];
+            bool live[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int layer = layer0 + t0 + u;
+                live[u] = t0 + u < p.staged && layer < p.count;
+                row[u] = p.x + (size_t)(live[u] ? layer : 0) * p.ldx;
             }
-            const float *row = p.x + (size_t)layer * p.ldx;
-            float amax = 0.0f;
+            float amax[2] = {0.0f, 0.0f};
             if (p.x_vec4) {
-                const float4 *row4 = reinterpret_cast<const float4 *>(row);
-                for (int i = threadIdx.x; i < (p.k >> 2); i += blockDim.x) {
-                    const float4 v = row4[i];
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                // eight independent 16-byte loads per thread in flight: one L2 round trip for K = 4096
+                const int nv4 = p.k >> 2;
+                for (int i0 = threadIdx.x; i0 < nv4; i0 += 4 * blockDim.x) {
+                    float4 v[2][4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int i = i0 + j * blockDim.x;
+#pragma unroll
+                        for (int u = 0; u < 2; ++u)
+                            v[u][j] = (live[u] && i < nv4) ? reinterpret_cast<const float4 *>(row[u])[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int u = 0; u < 2; ++u)
+                            amax[u] = fmaxf(amax[u], fmaxf(fmaxf(fabsf(v[u][j].x), fabsf(v[u][j].y)), fmaxf(fabsf(v[u][j].z), fabsf(v[u][j].w))));
                 }
             } else {
-                for (int i = threadIdx.x; i < p.k; i += blockDim.x) amax = fmaxf(amax, fabsf(row[i]));
+                for (int i = threadIdx.x; i < p.k; i += blockDim.x) {
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+                        if (live[u]) amax[u] = fmaxf(amax[u], fabsf(row[u][i]));
+                }
             }
-            amax = block_reduce_max(amax, red_f);
-            const float sc = amax < 1e-8f ? 1.0f : __fdiv_rn(amax, 127.0f);
-            const float rs = __frcp_rn(sc);
-            int local_sum = 0;
+            block_max2(amax[0], amax[1], red_f);
+            float sc[2], rs[2];
+            int local_sum[2] = {0, 0};
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                sc[u] = amax[u] < 1e-8f ? 1.0f : __fdiv_rn(amax[u], 127.0f);
+                rs[u] = __frcp_rn(sc[u]);
+            }
             for (int d = threadIdx.x; d < slots; d += blockDim.x) {
                 const int g = group_of_slot(d);
-                uint32_t out[4] = {0u, 0u, 0u, 0u};
-                if (g < groups16) {
 #pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        const int base = g * 16 + w * 4;
-                        float v[4];
-                        if (p.x_vec4 && base + 3 < p.k) {
-                            const float4 f = *reinterpret_cast<const float4 *>(row + base);
-                            v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
-                        } else {
+                for (int u = 0; u < 2; ++u) {
+                    if (t0 + u >= p.staged) continue;
+                    uint32_t out[4] = {0u, 0u, 0u, 0u};
+                    if (live[u] && g < groups16) {
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) v[e] = (base + e < p.k) ? row[base + e] : 0.0f;
-                        }
+                        for (int w = 0; w < 4; ++w) {
+                            const int base = g * 16 + w * 4;
+                            float v[4];
+                            if (p.x_vec4 && base + 3 < p.k) {
+                                const float4 f = *reinterpret_cast<const float4 *>(row[u] + base);
+                                v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+                            } else {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int q = quantise_one_fast(v[e], sc, rs);
-                            local_sum += q;
-                            out[w] |= (uint32_t)(q & 0xff) << (8 * e);
+                                for (int e = 0; e < 4; ++e) v[e] = (base + e < p.k) ? row[u][base + e] : 0.0f;
+                            }
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int q = quantise_one_fast(v[e], sc[u], rs[u]);
+                                local_sum[u] += q;
+                                out[w] |= (uint32_t)(q & 0xff) << (8 * e);
+                            }
                         }
                     }
+                    xs[(size_t)(t0 + u) * slots + d] = make_uint4(out[0], out[1], out[2], out[3]);
                 }
-                dst[d] = make_uint4(out[0], out[1], out[2], out[3]);
             }
-            local_sum = block_reduce_sum(local_sum, red_i);
-            if (threadIdx.x == 0) { s_sx[t] = sc; s_sum[t] = local_sum; }
+            block_sum2(local_sum[0], local_sum[1], red_i);
+            if (threadIdx.x == 0) {
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+                    if (t0 + u < p.staged) { s_sx[t0 + u] = live[u] ? sc[u] : 1.0f; s_sum[t0 + u] = live[u] ? local_sum[u] : 0; }
+            }
         }
     } else {
         for (int idx = threadIdx.x; idx < p.staged * slots; idx += blockDim.x) {

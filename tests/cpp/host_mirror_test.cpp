@@ -122,6 +122,17 @@ int main() {
         auto c = ternary_ternary_matmul(pa, sa, pb, sb, 2, 2, 2);
         EXPECT(c == (std::vector<float>{1, -2, 0, 1}));
     }
+    // a group of same-shaped layers; members of another shape are a ShapeMismatch
+    {
+        const float w[8] = {1, -1, 0, 1, -1, 1, 1, 0};
+        BitLinear a = BitLinear::create(w, nullptr, 2, 4, 0.3f), b = BitLinear::create(w, nullptr, 2, 4, 0.3f);
+        BitLinear c = BitLinear::create(w, nullptr, 4, 2, 0.3f);
+        LinearGroup g({&a, &b});
+        EXPECT(g.size() == 2);
+        bool threw = false;
+        try { LinearGroup bad({&a, &c}); } catch (const KoreError &e) { threw = e.kind() == KoreError::ShapeMismatch; }
+        EXPECT(threw);
+    }
     std::printf("OK %d\n", checks);
     return 0;
 }
