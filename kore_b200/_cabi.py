@@ -52,6 +52,7 @@ SIGNATURES = {
     "kb_linear_group_count": (_sz, [_vp]),
     "kb_linear_group_forward_q8": (C.c_int, [_vp, _vp, _sz, _vp, _vp, _vp, _sz, _vp]),
     "kb_linear_group_forward": (C.c_int, [_vp, _vp, _sz, _vp, _sz, _vp]),
+    "kb_linear_group_forward_host": (C.c_int, [_vp, _vp, _vp]),
     "kb_static_scratch_bytes": (_sz, []),
     "kb_ternary_matmul": (C.c_int, [_vp, _sz, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
     "kb_linear_forward_rmsnorm": (C.c_int, [_vp, _vp, _vp, C.c_float, _sz, _vp, _sz, C.c_int, _vp, _vp]),

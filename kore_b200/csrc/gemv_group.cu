@@ -15,6 +15,7 @@
 // of the layers its range touches (two for ranges shorter than a layer) in shared memory in the
 // GEMV's permuted order; the host grows the grid until they fit.
 #include <cstdlib>
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -39,6 +40,9 @@ struct Group {
     int kind, mul, off;
     size_t count, m, k, kp, row_bytes;
     LayerRef *table;  // device, [count]
+    // host entry point: device copies of x [count, k] and y [count, m]; one call at a time
+    float *dx, *dy;
+    std::mutex host_mutex;
 };
 
 struct GroupParams {
@@ -483,8 +487,12 @@ int kb_linear_group_create(const kb_linear *const *handles, size_t count, kb_lin
     G->count = count; G->m = first->m; G->k = first->k; G->kp = first->kp; G->row_bytes = first->row_bytes;
     cudaError_t e = cudaMalloc(&G->table, count * sizeof(LayerRef));
     if (e == cudaSuccess) e = cudaMemcpy(G->table, host.data(), count * sizeof(LayerRef), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMalloc(&G->dx, count * first->k * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&G->dy, count * first->m * sizeof(float));
     if (e != cudaSuccess) {
         if (G->table) cudaFree(G->table);
+        if (G->dx) cudaFree(G->dx);
+        if (G->dy) cudaFree(G->dy);
         delete G;
         return cuda_fail(e, "group table");
     }
@@ -499,6 +507,8 @@ void kb_linear_group_destroy(kb_linear_group *g) {
     ScopedDevice dev(G->device);
     G->magic = 0;
     cudaFree(G->table);
+    cudaFree(G->dx);
+    cudaFree(G->dy);
     delete G;
 }
 
@@ -524,6 +534,26 @@ int kb_linear_group_forward(const kb_linear_group *g, const float *x, size_t ldx
     if (ldx == 0) ldx = G->k;
     if (ldx < G->k) return fail(KB_ERR_SHAPE, "shape mismatch: expected [%zu], got row stride %zu", G->k, ldx);
     return group_forward(G, x, ldx, nullptr, 0, nullptr, nullptr, y, ldy, static_cast<cudaStream_t>(stream));
+}
+
+int kb_linear_group_forward_host(const kb_linear_group *g, const float *x, float *y) {
+    const Group *Gc = check_group(g);
+    if (!Gc) return KB_ERR_BAD_HANDLE;
+    if (!x || !y) return fail(KB_ERR_INVALID, "null activation or output pointer");
+    Group *G = const_cast<Group *>(Gc);  // the staging buffers are the only state a call touches
+    std::lock_guard<std::mutex> lock(G->host_mutex);
+    ScopedDevice dev(G->device);
+    cudaStream_t st = cudaStreamPerThread;
+    int rc = KB_OK;
+    cudaError_t e;
+    if ((e = cudaMemcpyAsync(G->dx, x, G->count * G->k * sizeof(float), cudaMemcpyHostToDevice, st)) != cudaSuccess)
+        rc = cuda_fail(e, "activation upload");
+    if (rc == KB_OK) rc = group_forward(G, G->dx, G->k, nullptr, 0, nullptr, nullptr, G->dy, G->m, st);
+    if (rc == KB_OK && (e = cudaMemcpyAsync(y, G->dy, G->count * G->m * sizeof(float), cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+        rc = cuda_fail(e, "output download");
+    e = cudaStreamSynchronize(st);
+    if (rc == KB_OK && e != cudaSuccess) rc = cuda_fail(e, "stream synchronize");
+    return rc;
 }
 
 }  // extern "C"

@@ -413,11 +413,18 @@ class LinearGroup:
         return y
 
     def forward(self, x, out=None):
-        """x: CUDA float32 [len(self), K]; row i goes through layer i (one launch, the per-token
-        quantiser runs in the kernel's prologue)."""
+        """x: float32 [len(self), K], a CUDA tensor or a numpy array; row i goes through layer i (one
+        launch, the per-token quantiser runs in the kernel's prologue)."""
         import torch
 
-        if not _is_torch(x) or not x.is_cuda or x.dtype != torch.float32:
+        if not _is_torch(x):  # numpy in, numpy out: copies and synchronisation inside one C call
+            x = np.ascontiguousarray(x, dtype=np.float32)
+            if x.ndim != 2 or x.shape[0] != len(self.layers) or x.shape[1] != self.in_features:
+                raise KoreError(_cabi.ERR_SHAPE, f"shape mismatch: expected [{len(self.layers)}, {self.in_features}], got {list(x.shape)}")
+            y = np.empty((len(self.layers), self.out_features), np.float32)
+            _cabi.check(_cabi.lib().kb_linear_group_forward_host(self.handle, x.ctypes.data, y.ctypes.data))
+            return y
+        if not x.is_cuda or x.dtype != torch.float32:
             raise KoreError(_cabi.ERR_DTYPE, "expected a CUDA float32 tensor")
         if x.dim() != 2 or x.shape[0] != len(self.layers) or x.shape[1] != self.in_features:
             raise KoreError(_cabi.ERR_SHAPE, f"shape mismatch: expected [{len(self.layers)}, {self.in_features}], got {list(x.shape)}")

@@ -56,6 +56,7 @@ def test_group_matches_oracle_per_layer(torch, kind, quantiser, count, m, k):
     y = grp(xd).cpu().numpy()  # f32 in: quantiser in the kernel's prologue
     y_q8 = grp.forward_q8(*kernels.quantize_act_i8(xd)).cpu().numpy()  # quantised beforehand
     assert (y == y_q8).all()
+    assert (grp(x) == y).all()  # numpy in: host entry point
     for i, (packed, scales, bias) in enumerate(raw):
         y_ref, _ = kbref.q_forward(kind, packed, scales, bias, m, k, x[i : i + 1], threads=2)
         assert (y[i] == y_ref[0]).all(), f"layer {i}"
@@ -128,6 +129,8 @@ def test_group_errors(torch):
     assert lib.kb_linear_group_forward_q8(grp.handle, None, 0, None, None, None, 0, None) == _cabi.ERR_INVALID
     assert lib.kb_linear_group_count(grp.handle) == 2
     assert lib.kb_linear_group_forward(grp.handle, None, 0, None, 0, None) == _cabi.ERR_INVALID
+    assert lib.kb_linear_group_forward_host(grp.handle, None, None) == _cabi.ERR_INVALID
+    assert lib.kb_linear_group_forward_host(None, None, None) == _cabi.ERR_BAD_HANDLE
     xs = torch.zeros((2, 128), device="cuda")
     ys = torch.zeros((2, 64), device="cuda")
     assert lib.kb_linear_group_forward(grp.handle, xs.data_ptr(), 100, ys.data_ptr(), 0, None) == _cabi.ERR_SHAPE
