@@ -139,8 +139,10 @@ struct Cursor {
 // FUSED: the activations arrive as f32 and each CTA quantises the rows of the layers it touches
 // itself (per-token absmax -> int8, the quantiser kernel's arithmetic), which costs a CTA that
 // streams for a hundred microseconds a few microseconds once and removes the quantiser launch.
-template <int PF, bool FULLK, bool FUSED>
-__global__ void __launch_bounds__(256) gemv_group_kernel(const GroupParams p) {
+// TPB threads per CTA, MINB CTAs per SM (bounds the registers: more resident warps hide more of
+// the load latency than a third chunk in flight per warp)
+template <int PF, bool FULLK, bool FUSED, int TPB, int MINB>
+__global__ void __launch_bounds__(TPB, MINB) gemv_group_kernel(const GroupParams p) {
     constexpr int R = 4;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     uint4 *xs = reinterpret_cast<uint4 *>(smem_raw);  // [staged][slots]
@@ -400,12 +402,17 @@ int group_forward(const Group *G, const float *x, size_t ldx, const int8_t *xq, 
     if (ldy == 0) ldy = G->m;
     if (ldy < G->m) return fail(KB_ERR_SHAPE, "shape mismatch: ldy %zu is smaller than out_features %zu", ldy, G->m);
     ScopedDevice dev(G->device);
-    const int nwarps = GROUP_THREADS / 32;
+    // launch shapes: {chunks in flight per warp, threads per CTA, CTAs per SM}
+    static const int cfg_id = env_int("KB_GROUP_CFG", 1);
+    const int shape = (cfg_id >= 0 && cfg_id <= 4) ? cfg_id : 1;
+    static const int cfg_threads[5] = {256, 128, 128, 256, 128}, cfg_minb[5] = {2, 5, 6, 3, 4};
+    const int threads = cfg_threads[shape];
+    const int nwarps = threads / 32;
     const long long row_groups = (long long)((G->m + GROUP_R - 1) / GROUP_R);
     const long long total = (long long)G->count * row_groups;
     const size_t row_smem = (G->kp + 2047) / 2048 * 2048;  // bytes of one staged activation row
     // persistent-size grid; grown (smaller ranges touch fewer layers) until a CTA's activation rows fit
-    long long grid = (long long)sm_count(G->device) * env_int("KB_GROUP_CTAS_PER_SM", 2);
+    long long grid = (long long)sm_count(G->device) * cfg_minb[shape];
     if (grid < 1) grid = 1;
     long long per_cta = 0, staged = 0;
     for (;;) {
@@ -431,12 +438,18 @@ int group_forward(const Group *G, const float *x, size_t ldx, const int8_t *xq, 
     p.groups_per_cta = (int)per_cta;
     p.staged = (int)staged;
     const bool fullk = G->kp % 2048 == 0;
-    static const int pf = env_int("KB_GROUP_PF", 3);
-    void (*kern)(const GroupParams);
-    if (x) kern = pf >= 3 ? (fullk ? gemv_group_kernel<3, true, true> : gemv_group_kernel<3, false, true>)
-                          : (fullk ? gemv_group_kernel<2, true, true> : gemv_group_kernel<2, false, true>);
-    else kern = pf >= 3 ? (fullk ? gemv_group_kernel<3, true, false> : gemv_group_kernel<3, false, false>)
-                        : (fullk ? gemv_group_kernel<2, true, false> : gemv_group_kernel<2, false, false>);
+    void (*kern)(const GroupParams) = nullptr;
+#define KB_GROUP_PICK(PF_, TPB_, MINB_)                                                                              \
+    kern = x ? (fullk ? gemv_group_kernel<PF_, true, true, TPB_, MINB_> : gemv_group_kernel<PF_, false, true, TPB_, MINB_>) \
+             : (fullk ? gemv_group_kernel<PF_, true, false, TPB_, MINB_> : gemv_group_kernel<PF_, false, false, TPB_, MINB_>)
+    switch (shape) {
+        case 0: KB_GROUP_PICK(3, 256, 2); break;
+        case 2: KB_GROUP_PICK(2, 128, 6); break;
+        case 3: KB_GROUP_PICK(2, 256, 3); break;
+        case 4: KB_GROUP_PICK(3, 128, 4); break;
+        default: KB_GROUP_PICK(2, 128, 5); break;
+    }
+#undef KB_GROUP_PICK
     const size_t smem = (size_t)staged * row_smem;
     if (smem > 40 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -444,7 +457,7 @@ int group_forward(const Group *G, const float *x, size_t ldx, const int8_t *xq, 
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(GROUP_THREADS);
+    cfg.blockDim = dim3((unsigned)threads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
