@@ -437,7 +437,7 @@ def main():
         # the step IS one launch of the dominant kernel: its launch duration is the step time
         achieved = pool_n * gemv_bytes(M_DEC, K_DEC, 1) / sec_per_step / 1e9
         pre_q = pool_n * gemv_bytes(M_DEC, K_DEC, 1) / group_sec / 1e9
-        roofline.update({"achieved": achieved, "frac": achieved / peaks["hbm_gbs"], "kernel": "gemv_group_kernel<3,true,true>",
+        roofline.update({"achieved": achieved, "frac": achieved / peaks["hbm_gbs"], "kernel": "gemv_group_kernel<2,true,true,128,5>",
                          "us_per_launch": sec_per_step * 1e6, "us_per_layer": sec_per_step / pool_n * 1e6,
                          "frac_of_nominal_8000": achieved / 8000.0,
                          "note": "one launch per step: algorithmic bytes of the launch / its duration in the timed region "
