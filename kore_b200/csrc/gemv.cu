@@ -446,7 +446,7 @@ static int launch_one(const GemvParams &p, int tok_groups, bool shared_grid, cud
     const int nwarps = threads / 32;
     const size_t smem = gemv_smem_bytes((size_t)p.kp, NT);
     auto kern = gemv_kernel<NT, R, PF, FUSED, EPI>;
-    if (smem > 48 * 1024) {
+    if (smem > 40 * 1024) {  // the static arrays count toward the 48 KB default limit too
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return cuda_fail(e, "gemv smem attribute");
     }

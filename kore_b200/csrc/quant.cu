@@ -12,6 +12,12 @@
 
 namespace kb {
 
+// status of the launch just issued: the error is read once (reading it clears it)
+static int launch_status(const char *what) {
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, what);
+}
+
 // ------------------------------------------------------------------ activations
 
 // One CTA per token row.  Pass 1 reduces max|x|, pass 2 (re-reading the row from L1/L2)
@@ -83,7 +89,7 @@ int launch_act_quant(const float *x, size_t n, size_t k, int8_t *xq, size_t ldq,
         act_quant_kernel<true><<<(unsigned)n, 256, 0, stream>>>(x, (int)k, xq, (int)ldq, sx, sumq);
     else
         act_quant_kernel<false><<<(unsigned)n, 256, 0, stream>>>(x, (int)k, xq, (int)ldq, sx, sumq);
-    return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "act_quant launch");
+    return launch_status("act_quant launch");
 }
 
 // ------------------------------------------------------------------ weights
@@ -140,7 +146,7 @@ int launch_repack_wire(int kind, const uint8_t *wire, size_t m, size_t k, uint8_
     else
         repack_wire_kernel<KB_QUATERNARY><<<blocks, 256, 0, stream>>>(
             wire, (int)m, (int)k, (int)((k + 3) / 4), reinterpret_cast<uint32_t *>(w2), row_words, total);
-    return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "repack launch");
+    return launch_status("repack launch");
 }
 
 // base-243 rows -> int8 trits [n][ldq] (tail zero) and their per-row sums: a ternary operand in
@@ -270,7 +276,7 @@ int launch_quantise_f32(int kind, int quantiser, const float *w, size_t m, size_
             quantise_f32_kernel<2><<<blocks, 256, 0, stream>>>(w, (int)m, (int)k, threshold, scales, dst,
                                                                row_words, total);
     }
-    return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "quantise launch");
+    return launch_status("quantise launch");
 }
 
 // device layout -> wire format, one thread per wire byte.  Pad slots follow the
@@ -312,7 +318,7 @@ int launch_export_wire(int kind, const uint8_t *w2, size_t row_bytes, size_t m, 
         export_wire_kernel<KB_TERNARY><<<blocks, 256, 0, stream>>>(src, (int)(row_bytes / 4), (int)m, (int)k, kpw, wire);
     else
         export_wire_kernel<KB_QUATERNARY><<<blocks, 256, 0, stream>>>(src, (int)(row_bytes / 4), (int)m, (int)k, kpw, wire);
-    return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "export launch");
+    return launch_status("export launch");
 }
 
 __global__ void dequantize_kernel(const uint32_t *__restrict__ w2, int row_words, int kind,
@@ -331,7 +337,7 @@ int launch_dequantize(int kind, const uint8_t *w2, size_t row_bytes, const float
     const size_t total = m * k;
     dequantize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
         reinterpret_cast<const uint32_t *>(w2), (int)(row_bytes / 4), kind, scales, (int)m, (int)k, w);
-    return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "dequantize launch");
+    return launch_status("dequantize launch");
 }
 
 // [rows, cols] -> [cols, rows] through a padded shared-memory tile (coalesced both ways)
@@ -354,7 +360,7 @@ int launch_transpose_f32(const float *src, size_t rows, size_t cols, float *dst,
     if (rows == 0 || cols == 0) return KB_OK;
     dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
     transpose_f32_kernel<<<grid, dim3(32, 8), 0, stream>>>(src, (int)rows, (int)cols, dst);
-    return cudaGetLastError() == cudaSuccess ? KB_OK : cuda_fail(cudaGetLastError(), "transpose launch");
+    return launch_status("transpose launch");
 }
 
 }  // namespace kb

@@ -20,7 +20,7 @@ full tensor before splitting so that results do not depend on the number of rank
 from __future__ import annotations
 
 import ctypes as C
-from typing import Callable, List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 
@@ -156,41 +156,43 @@ class ShardContext:
 
 
 class ShardedLinear:
-    """One rank's share of a column-sharded layer.
+    """One rank's share of a column-sharded layer (CUDA only: the local slice is a
+    ``BitLinear`` / ``QuatLinear`` on this rank's GPU).
 
-    ``compute`` replaces the CUDA layer by a callable ``(packed, scales, bias, m, k, x) ->
-    y[N, m]`` — used by the CPU tests of the host logic (gloo), never by the product path.
-    """
+    Every rank must own at least one output feature: a layer with fewer than ``32 * world``
+    features would leave some ranks without a slice, and those ranks would have no launch to
+    join the exchange from, so construction fails on every rank alike (the partition is a pure
+    function of ``out_features`` and ``world``)."""
 
     def __init__(self, kind: int, packed, scales, bias, in_features: int, out_features: int, rank: int, world: int,
-                 *, device: int = 0, ctx: Optional[ShardContext] = None, dist=None, exchange: str = "p2p",
-                 compute: Optional[Callable] = None):
+                 *, device: int = 0, ctx: Optional[ShardContext] = None, dist=None, exchange: str = "p2p"):
         self.kind, self.k, self.m_total = kind, in_features, out_features
         self.rank, self.world = rank, world
         self.parts = row_partition(out_features, world)
+        empty = [r for r, (_, size) in enumerate(self.parts) if size == 0]
+        if empty:
+            raise ValueError(f"{out_features} output features over {world} ranks leave rank(s) {empty} without a slice "
+                             f"(slices are multiples of 32 features): use at most {max(1, (out_features + 31) // 32)} ranks")
         self.start, self.size = self.parts[rank]
         self.exchange, self.ctx, self.dist = exchange, ctx, (dist if dist is not None else (ctx.dist if ctx else None))
         p, s, b = slice_wire_rows(kind, packed, scales, bias, out_features, in_features, self.start, self.size)
-        self._compute = compute
-        self._wire = (p.copy(), s.copy(), None if b is None else b.copy())
-        self.layer = None
-        if compute is None:
-            from . import nn
-
-            cls = nn.BitLinear if kind == TERNARY else nn.QuatLinear
-            self.layer = cls.from_packed(p, s, b, in_features, self.size, device=device)
-        if exchange == "p2p" and compute is None and ctx is None:
+        self.layer = self._build_local(kind, p, s, b, in_features, self.size, device)
+        if exchange == "p2p" and ctx is None:
             raise ValueError("the p2p exchange needs a ShardContext")
+
+    def _build_local(self, kind, packed, scales, bias, k, m_local, device):
+        from . import nn
+
+        cls = nn.BitLinear if kind == TERNARY else nn.QuatLinear
+        return cls.from_packed(packed, scales, bias, k, m_local, device=device)
 
     # -- product path -------------------------------------------------------------------------
     def forward(self, x, path: int = _cabi.PATH_AUTO, stream_ptr: Optional[int] = None):
         """x: CUDA f32 [N, K] (replicated on every rank) -> y [N, M] on this rank."""
-        if self._compute is not None:
-            return self._forward_collective_generic(x)
         import torch
 
         n = x.shape[0]
-        if stream_ptr is None:
+        if stream_ptr is None and x.is_cuda:
             stream_ptr = torch.cuda.current_stream(x.device.index).cuda_stream
         if self.exchange == "p2p":
             ctx = self.ctx
@@ -202,16 +204,30 @@ class ShardedLinear:
                 self.m_total, self.start, path, None, 0, ctx.flag_table.data_ptr(), ctx.sync_words.data_ptr(),
                 stream_ptr))
             return ctx.local_y[par][:n]
-        # collective: equal-sized staging blocks, NCCL all-gather, then [g, N, s] -> [N, M]
+        # collective: equal-sized staging blocks, all-gather, then [g, N, s] -> [N, M]
         smax = max(s for _, s in self.parts)
-        stage = torch.zeros((n, smax), dtype=torch.float32, device=x.device)
-        _cabi.check(_cabi.lib().kb_linear_forward_ex(self.layer.handle, x.data_ptr(), n, x.shape[1], stage.data_ptr(),
-                                                     smax, None, path, None, 0, stream_ptr))
-        out = torch.empty((self.world, n, smax), dtype=torch.float32, device=x.device)
-        self.dist.all_gather_into_tensor(out, stage)
+        stage = self._local_forward(x, n, smax, path, stream_ptr)
+        out = self._all_gather(stage)
         if n == 1 and all(s == smax for _, s in self.parts):
             return out.reshape(1, self.world * smax)
         return assemble_gathered([out[q] for q in range(self.world)], [s for _, s in self.parts])
+
+    def _local_forward(self, x, n, smax, path, stream_ptr):
+        """This rank's slice of the output in a [N, smax] staging block (columns beyond the slice stay zero)."""
+        import torch
+
+        stage = torch.zeros((n, smax), dtype=torch.float32, device=x.device)
+        _cabi.check(_cabi.lib().kb_linear_forward_ex(self.layer.handle, x.data_ptr(), n, x.shape[1], stage.data_ptr(),
+                                                     smax, None, path, None, 0, stream_ptr))
+        return stage
+
+    def _all_gather(self, stage):
+        """[N, smax] per rank -> [world, N, smax] on every rank (NCCL)."""
+        import torch
+
+        out = torch.empty((self.world,) + tuple(stage.shape), dtype=stage.dtype, device=stage.device)
+        self.dist.all_gather_into_tensor(out, stage)
+        return out
 
     __call__ = forward
 
@@ -233,17 +249,3 @@ class ShardedLinear:
             self.world, self.rank, self.m_total, self.start, path, ctx.flag_table.data_ptr(), ctx.sync_words.data_ptr(),
             stream_ptr))
         return ctx.local_y[par][:n]
-
-    # -- CPU test path: same partition / gather logic, compute injected -------------------------
-    def _forward_collective_generic(self, x):
-        import torch
-
-        p, s, b = self._wire
-        y_local = np.asarray(self._compute(p, s, b, self.size, self.k, np.asarray(x, dtype=np.float32)), dtype=np.float32)
-        n = y_local.shape[0]
-        smax = max(sz for _, sz in self.parts)
-        stage = torch.zeros((n, smax), dtype=torch.float32)
-        stage[:, :self.size] = torch.from_numpy(y_local)
-        chunks = [torch.empty_like(stage) for _ in range(self.world)]
-        self.dist.all_gather(chunks, stage)
-        return assemble_gathered(chunks, [sz for _, sz in self.parts]).numpy()

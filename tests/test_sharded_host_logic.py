@@ -40,8 +40,35 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def _oracle_shard_class():
+    """ShardedLinear with this rank's CUDA layer replaced by the oracle (the test's own stand-in:
+    the package has no CPU compute), so that partition, slicing and gather layout run under gloo."""
+    import torch
+
+    class OracleShard(sharded.ShardedLinear):
+        def _build_local(self, kind, packed, scales, bias, k, m_local, device):
+            return (packed.copy(), scales.copy(), None if bias is None else bias.copy())
+
+        def _local_forward(self, x, n, smax, path, stream_ptr):
+            p, s, b = self.layer
+            y = kbref.q_forward(self.kind, p, s, b, self.size, self.k, x.numpy())[0]
+            stage = torch.zeros((n, smax), dtype=torch.float32)
+            stage[:, :self.size] = torch.from_numpy(y)
+            return stage
+
+        def _all_gather(self, stage):
+            chunks = [torch.empty_like(stage) for _ in range(self.world)]
+            self.dist.all_gather(chunks, stage)
+            return torch.stack(chunks)
+
+    return OracleShard
+
+
 def _rank_main(rank, world, port, kind, m, k, n, q):
+    import torch
     import torch.distributed as dist
+
+    _OracleShard = _oracle_shard_class()
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -53,14 +80,12 @@ def _rank_main(rank, world, port, kind, m, k, n, q):
         bias = cases.gaussian(12, (m,), 0.1)
         x = cases.gaussian(13, (n, k), 1.0)
 
-        def compute(p, s, b, m_local, k_, x_):
-            return kbref.q_forward(kind, p, s, b, m_local, k_, x_)[0]
-
-        lay = sharded.ShardedLinear(kind, packed, scales, bias, k, m, rank, world, dist=dist, exchange="collective",
-                                    compute=compute)
-        y = lay.forward(x)
+        lay = _OracleShard(kind, packed, scales, bias, k, m, rank, world, dist=dist, exchange="collective")
+        y = lay.forward(torch.from_numpy(x)).numpy()
         y_ref = kbref.q_forward(kind, packed, scales, bias, m, k, x)[0]
         q.put((rank, bool((y == y_ref).all()), y.shape))
+    except Exception as exc:  # report instead of leaving the parent waiting on the queue
+        q.put((rank, False, repr(exc)))
     finally:
         dist.destroy_process_group()
 
@@ -79,5 +104,18 @@ def test_two_gloo_ranks_reproduce_the_unsharded_result(kind, m, k, n):
     [p.join(timeout=60) for p in procs]
     assert all(p.exitcode == 0 for p in procs)
     for rank, same, shape in results:
-        assert same, f"rank {rank} disagrees with the unsharded oracle"
+        assert same, f"rank {rank} disagrees with the unsharded oracle: {shape}"
         assert tuple(shape) == (n, m)
+
+
+def test_layer_too_small_for_the_ranks_is_rejected_on_every_rank():
+    """64 features over 4 ranks would leave two ranks without a slice: every rank must fail at
+    construction (before any exchange), not only the empty ones."""
+    cls = _oracle_shard_class()
+    w = cases.gaussian(5, (64, 32), 0.02)
+    packed, scales = cases.make_weights(kbref.TERNARY, "absmean", w)
+    for rank in range(4):
+        with pytest.raises(ValueError, match="without a slice"):
+            cls(kbref.TERNARY, packed, scales, None, 32, 64, rank, 4, exchange="collective")
+    # 64 features over 2 ranks is fine
+    cls(kbref.TERNARY, packed, scales, None, 32, 64, 1, 2, exchange="collective")
