@@ -64,6 +64,9 @@ enum {
  * shared memory): weights stream global -> registers -> warp-level int8 MMA. */
 enum { KB_PATH_AUTO = 0, KB_PATH_GEMV = 1, KB_PATH_GEMM_TC = 2, KB_PATH_GEMV_SHARED = 3, KB_PATH_GEMV_MMA = 4 };
 
+/* epilogue activation of kb_linear_forward_act */
+enum { KB_ACT_NONE = 0, KB_ACT_RELU = 1 };
+
 typedef struct kb_linear kb_linear; /* opaque: device-resident 2-bit weights + scales + bias */
 typedef struct kb_linear_group kb_linear_group; /* opaque: a set of same-shaped layers run in one launch */
 typedef void *kb_stream;            /* a cudaStream_t; NULL = the legacy default stream */
@@ -134,6 +137,15 @@ int kb_linear_forward_ex(const kb_linear *h, const float *x, size_t n, size_t in
                          size_t ldy, int32_t *acc, int path, void *workspace,
                          size_t workspace_bytes, kb_stream stream);
 size_t kb_linear_workspace_bytes(const kb_linear *h, size_t n);
+
+/* Forward with an activation in the epilogue: y = act(dequant(acc) + bias), act = KB_ACT_RELU
+ * gives max(., 0).  The layer-shaped form of the reference's fused bias + ReLU variant of its
+ * dequantising matmul (crates/kore-kernels/src/cuda/ops.rs:828-878, kernel
+ * cuda/kernels/dequant_matmul.cu:210-264).  bias is the handle's own, one value per output
+ * feature.  Other arguments as kb_linear_forward_ex. */
+int kb_linear_forward_act(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *y,
+                          size_t ldy, int act, int path, void *workspace, size_t workspace_bytes,
+                          kb_stream stream);
 
 /* Forward from activations the caller already quantised (kb_quantize_act_i8 layout,
  * ldq = kb_act_ld(K)).  y and acc are each nullable (not both). */
@@ -221,7 +233,11 @@ int kb_linear_forward_host(const kb_linear *h, const float *x, size_t n, size_t 
  *     Kp = kb_act_ld(K); larger requests fail with KB_ERR_UNSUPPORTED and a message
  *     stating both sizes;
  *   - the first call on each device resolves the array's device address
- *     (cudaGetSymbolAddress); make that call during set-up, before any stream capture;
+ *     (cudaGetSymbolAddress), and the first launch of each kernel it can pick (token
+ *     counts 1, 2, 3..4, 5..8, 9..128, 129..256 and above 256 each take a different one)
+ *     loads that kernel and sets its shared-memory limit, which the driver may back with
+ *     memory of its own.  Make one warm-up call per token-count class you will use during
+ *     set-up, before any stream capture and before the process's memory budget is frozen;
  *   - all calls on a device share the array and it keeps the previous call's bytes.
  *     Each call overwrites everything it reads, so nothing has to be cleared, but calls
  *     that overlap on the GPU (two streams, two threads) race: serialise them. */
@@ -263,6 +279,15 @@ int kb_ternary_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scal
                       size_t scales_len, const float *b, float *c, size_t m, size_t n, size_t k);
 int kb_quat_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scales, size_t scales_len,
                    const float *b, float *c, size_t m, size_t n, size_t k);
+
+/* cuda_dequant_quat_matmul_bias_relu_f32 (crates/kore-kernels/src/cuda/ops.rs:828-878), host
+ * pointers: c[m,n] = max(0, dequant(a)[m,:] . b[:,n] * a_scales[m] + bias[m]), c [M,N] f32.
+ * bias has one value per weight row (output feature): the reference kernel reads bias[col]
+ * with col running over N (dequant_matmul.cu:259), which indexes tokens in the layer's
+ * orientation; the per-feature form is the one a linear layer needs and the one built here. */
+int kb_quat_matmul_bias_relu(const uint8_t *a_packed, size_t a_len, const float *a_scales,
+                             size_t scales_len, const float *b, const float *bias, size_t bias_len,
+                             float *c, size_t m, size_t n, size_t k);
 
 /* ternary_ternary_matmul (cpu_ternary_matmul.rs:131-193): both operands base-243 rows,
  * a [M, ceil(K/5)] with a_scales [M], b [N, ceil(K/5)] with b_scales [N], integer dot product,

@@ -119,6 +119,10 @@ public:
     // raw host pointers: x [n, in_dim] -> y [n, out]
     void forward(const float *x, size_t n, size_t in_dim, float *y) const { check(kb_linear_forward_host(h_, x, n, in_dim, y)); }
     // device pointers on a stream (a cudaStream_t passed as void*); returns after enqueueing
+    // max(forward(x), 0), the ReLU applied in the kernel epilogue (cuda/ops.rs:828-878 in layer form)
+    void forward_relu_device(const float *x_dev, size_t n, float *y_dev, void *stream = nullptr) const {
+        check(kb_linear_forward_act(h_, x_dev, n, in_features(), y_dev, 0, KB_ACT_RELU, KB_PATH_AUTO, nullptr, 0, stream));
+    }
     void forward_device(const float *x_dev, size_t n, float *y_dev, void *stream = nullptr) const {
         check(kb_linear_forward(h_, x_dev, n, y_dev, stream));
     }

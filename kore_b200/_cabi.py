@@ -14,6 +14,7 @@ OK, ERR_SHAPE, ERR_STORAGE, ERR_DTYPE, ERR_CUDA = 0, 1, 2, 3, 4
 ERR_TIMEOUT, ERR_BAD_HANDLE, ERR_INVALID, ERR_UNSUPPORTED = 6, 7, 8, 9
 TERNARY, QUATERNARY = 0, 1
 QUANT_REFERENCE, QUANT_ABSMEAN = 0, 1
+ACT_NONE, ACT_RELU = 0, 1
 PATH_AUTO, PATH_GEMV, PATH_GEMM_TC, PATH_GEMV_SHARED, PATH_GEMV_MMA = 0, 1, 2, 3, 4
 
 _u8p, _i8p = C.POINTER(C.c_uint8), C.POINTER(C.c_int8)
@@ -36,6 +37,7 @@ SIGNATURES = {
     "kb_act_ld": (_sz, [_sz]),
     "kb_linear_forward": (C.c_int, [_vp, _vp, _sz, _vp, _vp]),
     "kb_linear_forward_ex": (C.c_int, [_vp, _vp, _sz, _sz, _vp, _sz, _vp, C.c_int, _vp, _sz, _vp]),
+    "kb_linear_forward_act": (C.c_int, [_vp, _vp, _sz, _sz, _vp, _sz, C.c_int, C.c_int, _vp, _sz, _vp]),
     "kb_linear_workspace_bytes": (_sz, [_vp, _sz]),
     "kb_linear_forward_q8": (C.c_int, [_vp, _vp, _sz, _vp, _vp, _sz, _vp, _sz, _vp, C.c_int, _vp]),
     "kb_linear_forward_fused": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, _sz, _vp, _vp, _sz, C.c_int, _vp, _sz, _vp]),
@@ -58,6 +60,7 @@ SIGNATURES = {
     "kb_linear_forward_rmsnorm": (C.c_int, [_vp, _vp, _vp, C.c_float, _sz, _vp, _sz, C.c_int, _vp, _vp]),
     "kb_linear_forward_scaled": (C.c_int, [_vp, _vp, _vp, _sz, _vp, _vp, _sz, _vp, _vp]),
     "kb_quat_matmul": (C.c_int, [_vp, _sz, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
+    "kb_quat_matmul_bias_relu": (C.c_int, [_vp, _sz, _vp, _sz, _vp, _vp, _sz, _vp, _sz, _sz, _sz]),
     "kb_ternary_ternary_matmul": (C.c_int, [_vp, _sz, _vp, _vp, _sz, _vp, _vp, _sz, _sz, _sz]),
     "kb_pack_weights_ternary": (C.c_int, [_vp, _sz, _sz, C.c_float, _vp, _sz, _vp, _sz, C.c_int]),
     "kb_pack_weights_quaternary": (C.c_int, [_vp, _sz, _sz, _vp, _sz, _vp, _sz, C.c_int]),

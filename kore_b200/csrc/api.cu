@@ -4,7 +4,10 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
+#include <set>
+#include <utility>
 
 #include "common.cuh"
 
@@ -39,6 +42,20 @@ struct DeviceGuard {
         if (switched) cudaSetDevice(prev);
     }
 };
+
+int set_dyn_smem_once(const void *kernel, int device, int bytes, const char *what) {
+    static std::mutex mu;
+    static std::set<std::pair<const void *, int>> done;
+    std::lock_guard<std::mutex> lock(mu);
+    const auto key = std::make_pair(kernel, device);
+    if (done.count(key)) return KB_OK;
+    DeviceGuard g(device);
+    if (g.err != cudaSuccess) return cuda_fail(g.err, "cudaSetDevice");
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return cuda_fail(e, what);
+    done.insert(key);
+    return KB_OK;
+}
 
 static size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static size_t wire_row_bytes(int kind, size_t k) { return kind == KB_TERNARY ? (k + 4) / 5 : (k + 3) / 4; }
@@ -106,15 +123,18 @@ static size_t workspace_bytes(const Linear *L, size_t n) {
 }
 
 static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim, float *y, size_t ldy,
-                        int32_t *acc, int path, void *workspace, size_t ws_bytes, cudaStream_t stream) {
+                        int32_t *acc, int path, void *workspace, size_t ws_bytes, cudaStream_t stream,
+                        int act = KB_ACT_NONE) {
     if (in_dim != L->k)
         return fail(KB_ERR_SHAPE, "shape mismatch: expected [%zu], got last dimension %zu", L->k, in_dim);
     if (!x || (!y && !acc)) return fail(KB_ERR_INVALID, "null activation or output pointer");
     if (ldy != 0 && ldy < L->m) return fail(KB_ERR_INVALID, "ldy %zu smaller than out_features %zu", ldy, L->m);
+    if (act != KB_ACT_NONE && act != KB_ACT_RELU) return fail(KB_ERR_INVALID, "unknown activation %d", act);
     if (n == 0) return KB_OK;
     if (path == KB_PATH_AUTO) path = auto_path(L, n, false);
     FwdArgs a = {};
     a.lin = L; a.n = n; a.y = y; a.acc = acc; a.ldy = ldy;
+    a.relu = act == KB_ACT_RELU;
     if (path == KB_PATH_GEMV_SHARED) { a.shared_grid = true; path = KB_PATH_GEMV; }
     if (path == KB_PATH_GEMV) {
         a.x = x;
@@ -271,13 +291,14 @@ static int create_from_f32(int kind, int quantiser, const float *w, const float 
 
 // reference-shaped one-shot: b [K,N] host -> c [M,N] host
 static int one_shot(int kind, const uint8_t *a_packed, size_t a_len, const float *a_scales, size_t scales_len,
-                    const float *b, float *c, size_t m, size_t n, size_t k) {
+                    const float *b, float *c, size_t m, size_t n, size_t k, const float *bias = nullptr,
+                    int act = KB_ACT_NONE) {
     if (!b || !c) return fail(KB_ERR_INVALID, "null pointer");
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     Linear *L = nullptr;
-    int rc = create_from_wire(kind, a_packed, a_len, a_scales, scales_len, nullptr, m, k, device, &L);
+    int rc = create_from_wire(kind, a_packed, a_len, a_scales, scales_len, bias, m, k, device, &L);
     if (rc) return rc;
     if (n == 0) { free_linear(L); return KB_OK; }
     cudaStream_t st = cudaStreamPerThread;
@@ -289,7 +310,7 @@ static int one_shot(int kind, const uint8_t *a_packed, size_t a_len, const float
     }
     if (rc == KB_OK && (e = cudaMemcpyAsync(db, b, xb, cudaMemcpyHostToDevice, st)) != cudaSuccess) rc = cuda_fail(e, "b upload");
     if (rc == KB_OK) rc = launch_transpose_f32(db, k, n, dx, st);  // [K,N] -> [N,K]
-    if (rc == KB_OK) rc = forward_impl(L, dx, n, k, dy, 0, nullptr, KB_PATH_AUTO, nullptr, 0, st);
+    if (rc == KB_OK) rc = forward_impl(L, dx, n, k, dy, 0, nullptr, KB_PATH_AUTO, nullptr, 0, st, act);
     if (rc == KB_OK) rc = launch_transpose_f32(dy, n, m, dc, st);  // [N,M] -> [M,N]
     if (rc == KB_OK && (e = cudaMemcpyAsync(c, dc, yb, cudaMemcpyDeviceToHost, st)) != cudaSuccess) rc = cuda_fail(e, "c download");
     e = cudaStreamSynchronize(st);
@@ -477,6 +498,15 @@ int kb_linear_forward_ex(const kb_linear *h, const float *x, size_t n, size_t in
                         static_cast<cudaStream_t>(stream));
 }
 
+int kb_linear_forward_act(const kb_linear *h, const float *x, size_t n, size_t in_dim, float *y, size_t ldy, int act,
+                          int path, void *workspace, size_t workspace_bytes_, kb_stream stream) {
+    const Linear *L = check(h);
+    if (!L) return KB_ERR_BAD_HANDLE;
+    DeviceGuard g(L->device);
+    return forward_impl(L, x, n, in_dim, y, ldy, nullptr, path, workspace, workspace_bytes_,
+                        static_cast<cudaStream_t>(stream), act);
+}
+
 size_t kb_linear_workspace_bytes(const kb_linear *h, size_t n) {
     const Linear *L = check(h);
     return L ? workspace_bytes(L, n) : 0;
@@ -592,6 +622,13 @@ int kb_ternary_ternary_matmul(const uint8_t *a_packed, size_t a_len, const float
 int kb_quat_matmul(const uint8_t *a_packed, size_t a_len, const float *a_scales, size_t scales_len, const float *b,
                    float *c, size_t m, size_t n, size_t k) {
     return one_shot(KB_QUATERNARY, a_packed, a_len, a_scales, scales_len, b, c, m, n, k);
+}
+
+int kb_quat_matmul_bias_relu(const uint8_t *a_packed, size_t a_len, const float *a_scales, size_t scales_len,
+                             const float *b, const float *bias, size_t bias_len, float *c, size_t m, size_t n, size_t k) {
+    if (!bias) return fail(KB_ERR_INVALID, "null pointer");
+    if (bias_len < m) return fail(KB_ERR_STORAGE, "bias too small: need %zu, got %zu", m, bias_len);
+    return one_shot(KB_QUATERNARY, a_packed, a_len, a_scales, scales_len, b, c, m, n, k, bias, KB_ACT_RELU);
 }
 
 int kb_pack_weights_ternary(const float *w, size_t m, size_t k, float threshold, uint8_t *packed, size_t packed_len,

@@ -65,6 +65,11 @@ int cuda_fail(cudaError_t e, const char *what);
         if (_e != cudaSuccess) return kb::cuda_fail(_e, #expr); \
     } while (0)
 
+// Raises a kernel's dynamic shared-memory limit once per (kernel, device).  The device is made
+// current for the call, and concurrent callers are serialised, so the forward entry points may
+// be used from many host threads and on several devices.
+int set_dyn_smem_once(const void *kernel, int device, int bytes, const char *what);
+
 // ---- launchers (each returns a KB_* status; all work is enqueued on `stream`) ----
 int launch_act_quant(const float *x, size_t n, size_t k, int8_t *xq, size_t ldq, float *sx,
                      int32_t *sumq, cudaStream_t stream);
@@ -112,6 +117,8 @@ struct FwdArgs {
     const struct PeerSync *sync;
     // optional residual, same [N][ldy] layout as y (may be y itself): y = dequant(...) + resid
     const float *resid;
+    // ReLU on the dequantised output (after the bias): y = max(dequant(...) + bias, 0); not combined with resid
+    bool relu;
     // GEMV only: size the grid for launches that overlap with other streams' GEMVs
     bool shared_grid;
     // GEMV with f32 input only (decoder fusions): RMSNorm in the prologue (gamma, eps), a known

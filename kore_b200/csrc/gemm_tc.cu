@@ -60,27 +60,8 @@ struct GemmParams {
     float *y_more[MAX_PEERS - 1];  // further copies of y (peer GPUs), same offsets
     int n_more;
     const float *resid;
-#ifdef KB_GEMM_DEBUG
-    int dbg;  // developer build: bit0 skip unpack work, bit1 skip packed TMA, bit2 skip act TMA, bit3 skip MMA
-#endif
+    int relu;  // max(y, 0) after the bias
 };
-#ifdef KB_GEMM_DEBUG
-#define DBG(p, bit) (((p).dbg >> (bit)) & 1)
-// developer build: per (CTA, local tile) timestamps: 0 mma start, 1 mma done issuing,
-// 2 epilogue got the accumulator, 3 epilogue done
-__device__ unsigned long long g_gemm_tl[4][148 * 8];
-__device__ __forceinline__ void gtl(int i, uint32_t ti) {
-    if (blockIdx.x < 148 && ti < 8) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_gemm_tl[i][blockIdx.x * 8 + ti] = t;
-    }
-}
-#define GTL(i, ti) gtl(i, ti)
-#else
-#define GTL(i, ti)
-#define DBG(p, bit) 0
-#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -236,9 +217,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, DEV_TIMEOUT_TMA_EMPTY))) break;
-                    mbar_expect_tx(full_bar(s), (DBG(p, 2) ? 0 : C::ACT_BYTES) + (DBG(p, 1) ? 0 : C::PK_BYTES));
-                    if (!DBG(p, 2)) tma_load_2d(act_addr(s), &tmap_x, full_bar(s), kb * BK, n0);
-                    if (!DBG(p, 1)) tma_load_2d(pk_addr(s), &tmap_w, full_bar(s), kb * (BK / 4), m0);
+                    mbar_expect_tx(full_bar(s), C::ACT_BYTES + C::PK_BYTES);
+                    tma_load_2d(act_addr(s), &tmap_x, full_bar(s), kb * BK, n0);
+                    tma_load_2d(pk_addr(s), &tmap_w, full_bar(s), kb * (BK / 4), m0);
                 }
             }
             // drain: every copy this thread issued must have landed before the CTA exits
@@ -262,7 +243,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 const int b = ti & 1;
                 if (!(ok = mbar_wait(tempty_bar(b), ((ti >> 1) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM_EMPTY))) break;
                 tc_fence_after();
-                GTL(0, ti);
                 const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -274,12 +254,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     const uint64_t bdesc = umma_desc_sw128(act_addr(s));
 #pragma unroll
                     for (int k4 = 0; k4 < BK / 32; ++k4)
-                        if (!DBG(p, 3)) umma_i8(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc,
+                        umma_i8(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc,
                                 (kb | k4) != 0 ? 1u : 0u);
                     umma_commit(empty_bar(s));
                 }
                 if (ok) umma_commit(tfull_bar(b));
-                GTL(1, ti);
             }
             // all MMAs issued by this thread must retire before smem/TMEM are released
             umma_commit(drain_bar);
@@ -297,7 +276,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1u;
                 if (!(ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, DEV_TIMEOUT_UNPACK_FULL))) break;
-                if (DBG(p, 0)) { __syncwarp(); if (lane == 0) mbar_arrive(unp_bar(s)); continue; }
                 const uint8_t *pk = base_ptr + (pk_addr(s) - base) + r * 32;
                 uint8_t *dst = base_ptr + (unp_addr(s) - base) + r * 128;
                 const uint4 lo = *reinterpret_cast<const uint4 *>(pk);
@@ -354,7 +332,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             ok = mbar_wait(tfull_bar(b), (ti >> 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_EPI_TMEM_FULL);
             if (!ok) break;
             tc_fence_after();
-            if (et == 0) GTL(2, ti);
 #pragma unroll 1
             for (int c = 0; c < NCH; ++c) {
                 sx_cur = sx_next;
@@ -389,6 +366,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     const int a = p.mul * (int)v[i] - p.off * sm_i;
                     outv[i] = dequant_out(a, sw, sx_i, bias, has_bias);
                     if (add_resid) outv[i] = __fadd_rn(outv[i], r_i);
+                    if (p.relu) outv[i] = fmaxf(outv[i], 0.0f);
                     v[i] = (uint32_t)a;
                 }
                 if (row_ok) {
@@ -412,7 +390,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 }
             }
             if (p.n_more) __threadfence_system();  // peer copies of this tile are ordered before the exit
-            if (et == 0) GTL(3, ti);
         }
     }
 
@@ -425,13 +402,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     }
 }
 
-#ifdef KB_GEMM_DEBUG
-}  // namespace
-extern "C" int kb_debug_gemm_timeline(unsigned long long *host) {
-    return (int)cudaMemcpyFromSymbol(host, g_gemm_tl, sizeof(g_gemm_tl));
-}
-namespace {
-#endif
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -494,18 +464,11 @@ int launch_bn(const FwdArgs &a, cudaStream_t stream) {
     p.n_more = a.y ? a.n_more : 0;
     for (int q = 0; q < MAX_PEERS - 1; ++q) p.y_more[q] = q < p.n_more ? a.y_more[q] : nullptr;
     p.resid = a.y ? a.resid : nullptr;
+    p.relu = a.relu ? 1 : 0;
     p.mul = L->mul; p.off = L->off; p.status = L->dev_status;
-#ifdef KB_GEMM_DEBUG
-    { const char *e = getenv("KB_GEMM_DBG"); p.dbg = e ? atoi(e) : 0; }
-#endif
     auto kern = gemm_tc_kernel<BN>;
-    static bool attr_set[64] = {false};
-    const int dev = (L->device >= 0 && L->device < 64) ? L->device : 0;
-    if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-        if (e != cudaSuccess) return cuda_fail(e, "gemm smem attribute");
-        attr_set[dev] = true;
-    }
+    const int dev = L->device;
+    if (int rc_attr = set_dyn_smem_once(reinterpret_cast<const void *>(kern), dev, C::SMEM_BYTES, "gemm smem attribute")) return rc_attr;
     const int tiles = (int)(((L->m + BM - 1) / BM) * ((a.n + BN - 1) / BN));
     const int sms = sm_count(L->device);
     const int grid = tiles < sms ? tiles : sms;

@@ -73,36 +73,8 @@ struct Gemm2Params {
     float *y_more[MAX_PEERS - 1];
     int n_more;
     const float *resid;
-#ifdef KB_GEMM_DEBUG
-    int dbg;  // developer build: bit0 skip unpack work, bit3 skip MMA
-#endif
+    int relu;  // max(y, 0) after the bias
 };
-#ifdef KB_GEMM_DEBUG
-#define DBG2(p, bit) (((p).dbg >> (bit)) & 1)
-__device__ unsigned long long g_gemm2_tl[4][148 * 8];
-__device__ __forceinline__ void gtl2(int i, uint32_t ti) {
-    if (blockIdx.x < 148 && ti < 8) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_gemm2_tl[i][blockIdx.x * 8 + ti] = t;
-    }
-}
-#define GTL2(i, ti) gtl2(i, ti)
-// per-k-block event trace of the first tile of CTAs 0 and 1: [cta][event][kb < 40]
-__device__ unsigned long long g_gemm2_trace[2][8][40];
-__device__ __forceinline__ void trc(int ev, uint32_t it) {
-    if (blockIdx.x < 2 && it < 40) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_gemm2_trace[blockIdx.x][ev][it] = t;
-    }
-}
-#define TRC(ev, it) trc(ev, it)
-#else
-#define TRC(ev, it)
-#define DBG2(p, bit) 0
-#define GTL2(i, ti)
-#endif
 
 template <bool CLUSTER_ACQUIRE>
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
@@ -204,7 +176,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                     const int s = it % RS;
                     const uint32_t ph = (it / RS) & 1u;
                     if (!(ok = wait_bar<false>(empty(s), ph ^ 1u, abort_flag, p.status, DEV_TIMEOUT_TMA_EMPTY))) break;
-                    TRC(0, it);
                     if (leader) mbar_expect_tx(ready(s), 2 * ACT_BYTES);
                     const uint32_t lead_bar = mapa(ready(s), 0);
 #pragma unroll
@@ -232,12 +203,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 const int b = ti & 1;
                 if (!(ok = wait_bar<false>(tempty(b), ((ti >> 1) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM_EMPTY))) break;
                 tc_fence_after();
-                GTL2(0, ti);
                 const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % RS;
                     if (!(ok = wait_bar<false>(ready(s), (it / RS) & 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL))) break;
-                    TRC(5, it);
                     tc_fence_after();
 #pragma unroll
                     for (int sl = 0; sl < SLABS; ++sl) {
@@ -245,14 +214,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                         const uint64_t bdesc = umma_desc_sw128(act_addr(s) + sl * ACT_SLAB);
 #pragma unroll
                         for (int k4 = 0; k4 < BK / 32; ++k4)
-                            if (!DBG2(p, 3)) umma_i8_pair(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc,
+                            umma_i8_pair(tmem_d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc,
                                          (kb | sl | k4) != 0 ? 1u : 0u);
                     }
                     umma_commit_pair_multicast(empty(s), 3);
-                    TRC(6, it);
                 }
                 if (ok) umma_commit_pair_multicast(tfull(b), 3);
-                GTL2(1, ti);
             }
             umma_commit_pair_multicast(drain_bar, 1);
             bool done = false;
@@ -273,14 +240,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 const uint32_t pt = pit - 1;
                 const int q = pt % PKS;
                 if (!(ok = wait_bar<false>(pk_full(q), (pt / PKS) & 1u, abort_flag, p.status, DEV_TIMEOUT_UNPACK_FULL))) break;
-                if (threadIdx.x == 128) TRC(1, it);
                 const bool last_use = half == PKT_STAGES - 1 || kb == num_kb - 1;
                 // packed tile: 128-byte rows, 128-byte swizzle (16-byte chunk c of row r sits at chunk c ^ (r & 7)),
                 // so the eight rows of a quarter-warp read eight different bank groups
                 const uint8_t *prow = base_ptr + (pkt_addr(q) - base) + r * 128;
                 const int c0 = half * 4 + sl * 2;
                 uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-                if (!DBG2(p, 0)) {
+                {
                     lo = *reinterpret_cast<const uint4 *>(prow + (((c0) ^ (r & 7)) << 4));
                     hi = *reinterpret_cast<const uint4 *>(prow + (((c0 + 1) ^ (r & 7)) << 4));
                 }
@@ -303,19 +269,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 if (it >= (uint32_t)RS) {
                     if (!(ok = wait_bar<false>(empty(s), ((it / RS) - 1u) & 1u, abort_flag, p.status, DEV_TIMEOUT_UNPACK_FULL))) break;
                 }
-                if (DBG2(p, 0)) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(mapa(ready(s), 0));
-                    continue;
-                }
                 uint8_t *dst = base_ptr + (unp_addr(s) - base) + sl * UNP_SLAB + r * 128;
 #pragma unroll
                 for (int c = 0; c < 8; ++c)
-                    if (!DBG2(p, 2)) *reinterpret_cast<uint4 *>(dst + ((c ^ (r & 7)) << 4)) = o[c];
-                if (!DBG2(p, 1)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    *reinterpret_cast<uint4 *>(dst + ((c ^ (r & 7)) << 4)) = o[c];
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa(ready(s), 0));
-                if (threadIdx.x == 128) TRC(3, it);
             }
         }
     } else if (warp >= 12) {
@@ -347,7 +307,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
             ok = wait_bar<false>(tfull(b), (ti >> 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_EPI_TMEM_FULL);
             if (!ok) break;
             tc_fence_after();
-            if (threadIdx.x == 384) GTL2(2, ti);
             // 16 half-chunks of 16 token columns; the TMEM load of the next half-chunk is in
             // flight while the current one is converted and stored
             constexpr int N16 = BN / 16;
@@ -374,6 +333,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                     const int a = p.mul * (int)v[i] - p.off * sm_i;
                     outv[i] = dequant_out(a, sw, sx_i, bias, has_bias);
                     if (add_resid) outv[i] = __fadd_rn(outv[i], r_i);
+                    if (p.relu) outv[i] = fmaxf(outv[i], 0.0f);
                     v[i] = (uint32_t)a;
                 }
                 if (row_ok) {
@@ -418,7 +378,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
             }
             (void)N16;
             if (p.n_more) __threadfence_system();
-            if (threadIdx.x == 384) GTL2(3, ti);
         }
     }
 
@@ -459,14 +418,6 @@ int encode_act_map(CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t r
 
 }  // namespace
 
-#ifdef KB_GEMM_DEBUG
-extern "C" int kb_debug_gemm2_timeline(unsigned long long *host) {
-    return (int)cudaMemcpyFromSymbol(host, g_gemm2_tl, sizeof(g_gemm2_tl));
-}
-extern "C" int kb_debug_gemm2_trace(unsigned long long *host) {
-    return (int)cudaMemcpyFromSymbol(host, g_gemm2_trace, sizeof(g_gemm2_trace));
-}
-#endif
 
 // CTA-pair GEMM: used for token counts above 128 (a full 256-token MMA N)
 int launch_gemm_tc2(const FwdArgs &a, cudaStream_t stream) {
@@ -487,16 +438,9 @@ int launch_gemm_tc2(const FwdArgs &a, cudaStream_t stream) {
     p.n_more = a.y ? a.n_more : 0;
     for (int q = 0; q < MAX_PEERS - 1; ++q) p.y_more[q] = q < p.n_more ? a.y_more[q] : nullptr;
     p.resid = a.y ? a.resid : nullptr;
-#ifdef KB_GEMM_DEBUG
-    { const char *e = getenv("KB_GEMM_DBG"); p.dbg = e ? atoi(e) : 0; }
-#endif
-    static bool attr_set[64] = {false};
-    const int dev = (L->device >= 0 && L->device < 64) ? L->device : 0;
-    if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return cuda_fail(e, "gemm2 smem attribute");
-        attr_set[dev] = true;
-    }
+    p.relu = a.relu ? 1 : 0;
+    const int dev = L->device;
+    if (int rc_attr = set_dyn_smem_once(reinterpret_cast<const void *>(gemm_tc2_kernel), dev, SMEM_BYTES, "gemm2 smem attribute")) return rc_attr;
     int sms = 148;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) sms = 148;
     const int tiles = (int)(((L->m + 2 * BM - 1) / (2 * BM)) * ((a.n + BN - 1) / BN));

@@ -76,15 +76,8 @@ struct TcsParams {
     float *y_more[MAX_PEERS - 1];
     int n_more;
     const float *resid;
-#ifdef KB_GEMM_DEBUG
-    int dbg;  // developer build: bit0 skip unpack work, bit1 skip activation copies, bit2 skip weight copies, bit3 skip MMA, bit4 plain arrive instead of commit
-#endif
+    int relu;  // max(y, 0) after the bias
 };
-#ifdef KB_GEMM_DEBUG
-#define DBGS(p, bit) (((p).dbg >> (bit)) & 1)
-#else
-#define DBGS(p, bit) 0
-#endif
 
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
     long long t0 = 0;
@@ -175,7 +168,6 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 for (int st = 0; st < num_st; ++st, ++it) {
                     const int s = it % NS;
                     if (!(ok = wait_bar(empty(s), ((it / NS) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_TMA_EMPTY))) break;
-                    if (DBGS(p, 1)) { mbar_arrive(full(s)); continue; }
                     const int nsl = min(ST_SLABS, num_kb - st * ST_SLABS);
                     mbar_expect_tx(full(s), (uint32_t)(nsl * C::ACT_SLAB));
                     for (int j = 0; j < nsl; ++j) tma_load_2d(act_addr(s, j), &tmap_x, full(s), (st * ST_SLABS + j) * BK, n0);
@@ -196,7 +188,6 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 for (int k = 0; k < num_pkt; ++k, ++pt) {
                     const int q = pt % PKS;
                     if (!(ok = wait_bar(pk_empty(q), ((pt / PKS) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_TMA_EMPTY))) break;
-                    if (DBGS(p, 2)) { mbar_arrive(pk_full(q)); continue; }
                     mbar_expect_tx(pk_full(q), PKT_BYTES);  // columns past the row's end arrive as zeros and count
                     tma_load_2d(pkt_addr(q), &tmap_w, pk_full(q), k * 128, m0);
                 }
@@ -230,10 +221,9 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                         const uint64_t bdesc = umma_desc_sw128(act_addr(s, j));
 #pragma unroll
                         for (int k4 = 0; k4 < BK / 32; ++k4)  // 32 bytes of K = 8 columns of A, 32 bytes of a B row
-                            if (!DBGS(p, 3)) umma_i8_ta(tmem_d, a_tmem + (uint32_t)(k4 * 8), bdesc + (uint64_t)(k4 * 2), idesc, (st | j | k4) != 0 ? 1u : 0u);
+                            umma_i8_ta(tmem_d, a_tmem + (uint32_t)(k4 * 8), bdesc + (uint64_t)(k4 * 2), idesc, (st | j | k4) != 0 ? 1u : 0u);
                     }
-                    if (DBGS(p, 4)) mbar_arrive(empty(s));
-                    else umma_commit(empty(s));  // frees the stage's activations and its weight slots
+                    umma_commit(empty(s));  // frees the stage's activations and its weight slots
                 }
                 if (ok) umma_commit(tfull(b));
             }
@@ -259,7 +249,7 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 // a packed tile covers two stages; every unpack warp waits for it, also one that owns
                 // none of its slabs: its arrival below must belong to this use of the barrier
                 if ((st & 1) == 0 && !(ok = wait_bar(pk_full(q), (pt / PKS) & 1u, abort_flag, p.status, DEV_TIMEOUT_UNPACK_FULL))) break;
-                const bool work = st * ST_SLABS + grp < num_kb && !DBGS(p, 0);
+                const bool work = st * ST_SLABS + grp < num_kb;
                 const int j = (st & 1) * ST_SLABS + grp;  // the slab's place in the packed tile
                 uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
                 if (work) {
@@ -346,6 +336,7 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                     const int a = p.mul * (int)v[i] - p.off * sm_i;
                     outv[i] = dequant_out(a, sw, sx_i, bias, has_bias);
                     if (add_resid) outv[i] = __fadd_rn(outv[i], r_i);
+                    if (p.relu) outv[i] = fmaxf(outv[i], 0.0f);
                     v[i] = (uint32_t)a;
                 }
                 if (row_ok) {
@@ -394,18 +385,11 @@ int launch_bn(const FwdArgs &a, cudaStream_t stream) {
     p.n_more = a.y ? a.n_more : 0;
     for (int q = 0; q < MAX_PEERS - 1; ++q) p.y_more[q] = q < p.n_more ? a.y_more[q] : nullptr;
     p.resid = a.y ? a.resid : nullptr;
+    p.relu = a.relu ? 1 : 0;
     p.mul = L->mul; p.off = L->off; p.status = L->dev_status;
-#ifdef KB_GEMM_DEBUG
-    { const char *e = getenv("KB_GEMM_DBG"); p.dbg = e ? atoi(e) : 0; }
-#endif
     auto kern = gemm_tcs_kernel<BN>;
-    static bool attr_set[64] = {false};
-    const int dev = (L->device >= 0 && L->device < 64) ? L->device : 0;
-    if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-        if (e != cudaSuccess) return cuda_fail(e, "gemm smem attribute");
-        attr_set[dev] = true;
-    }
+    const int dev = L->device;
+    if (int rc_attr = set_dyn_smem_once(reinterpret_cast<const void *>(kern), dev, C::SMEM_BYTES, "gemm smem attribute")) return rc_attr;
     const int tiles = (int)(((L->m + BM - 1) / BM) * ((a.n + BN - 1) / BN));
     const int sms = sm_count(L->device);
     const int grid = tiles < sms ? tiles : sms;

@@ -58,6 +58,7 @@ struct GemvParams {
     const float *x_absmax;  // per-token max|x| already known: the prologue skips its reduction
     float *absmax_out;      // SwiGLU epilogue: per-token max|h| (atomic max on the float bits)
     float *clear_word;      // n floats the launch sets to zero (the other parity's absmax slots)
+    int relu;               // max(y, 0) after the bias
 };
 
 // 16-element group g (k = 16*g .. 16*g+15) <-> shared-memory slot: inside each
@@ -67,21 +68,6 @@ __device__ __forceinline__ int xs_group_of_slot(int d) {
     return (blk << 7) + ((within & 31) << 2) + (within >> 5);
 }
 
-#ifdef KB_TIMELINE
-// Developer build only: CTA 0..2047 of the most recent launch record %globaltimer at five
-// points (entry, weights issued, dependency wait over, prologue done, rows done).
-__device__ unsigned long long g_timeline[5][2048];
-__device__ __forceinline__ void tl_mark(int i) {
-    if (threadIdx.x == 0 && blockIdx.x < 2048 && blockIdx.y == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_timeline[i][blockIdx.x] = t;
-    }
-}
-#define TL_MARK(i) tl_mark(i)
-#else
-#define TL_MARK(i)
-#endif
 
 constexpr int XR = 8;  // float4 registers per thread for the single-pass fused quantiser
 
@@ -118,8 +104,6 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     const int first_group = blockIdx.x * nwarps + warp;
     const int stride_groups = gridDim.x * nwarps;
     const int kc0 = lane * 64;
-
-    TL_MARK(0);
     // ---- weight pipeline: PF chunks x R rows in registers ----
     uint4 buf[PF][R];
     int lg = first_group, lci = 0;  // load cursor (row group, chunk)
@@ -145,11 +129,8 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
         }
     };
     load_row_consts(first_group);
-
-    TL_MARK(1);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    TL_MARK(2);
     if (FUSED && p.clear_word && blockIdx.x == 0 && blockIdx.y == 0 && (int)threadIdx.x < p.n) p.clear_word[threadIdx.x] = 0.0f;
 
     // ---- prologue: activations -> shared memory (int8, permuted) ----
@@ -286,7 +267,6 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
         }
     }
     __syncthreads();
-    TL_MARK(3);
 
     // ---- main loop: consume chunk, refill its registers, finish a row group when its
     //      last chunk has been consumed (control flow is uniform across the warp) ----
@@ -363,6 +343,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
                             if (p.y) {
                                 float v = dequant_out(a, my_sw, s_sx[t], my_bias, p.bias != nullptr);
                                 if (p.resid) v = __fadd_rn(v, p.resid[o]);
+                                if (p.relu) v = fmaxf(v, 0.0f);
                                 p.y[o] = v;
                                 for (int q = 0; q < p.n_more; ++q) p.y_more[q][o] = v;  // peer copies over NVLink
                             }
@@ -375,7 +356,6 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
             }
         }
     }
-    TL_MARK(4);
 
     // ---- sharded layers: publish this rank's slice and wait for the peers' ----
     // Every CTA orders its peer stores at system scope; the last CTA of the launch to get
@@ -413,11 +393,6 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvParams p) {
     }
 }
 
-#ifdef KB_TIMELINE
-extern "C" int kb_debug_timeline(unsigned long long *host) {
-    return (int)cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline));
-}
-#endif
 
 static size_t gemv_smem_bytes(size_t kp, size_t nt) { return nt * ((kp + 2047) / 2048 * 2048); }
 
@@ -520,6 +495,7 @@ int launch_gemv(const FwdArgs &a, cudaStream_t stream) {
     p.n = (int)a.n; p.y = a.y; p.acc = a.acc; p.ldy = a.ldy ? a.ldy : L->m;
     p.mul = L->mul; p.off = L->off;
     p.resid = a.y ? a.resid : nullptr;
+    p.relu = a.relu ? 1 : 0;
     p.sync = PeerSync{};
     if (a.sync && a.y) p.sync = *a.sync;
     p.n_more = a.y ? a.n_more : 0;

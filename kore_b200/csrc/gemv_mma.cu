@@ -48,6 +48,7 @@ struct MmaGemvParams {
     float *y_more[MAX_PEERS - 1];
     int n_more;
     const float *resid;
+    int relu;  // max(y, 0) after the bias
 };
 
 constexpr int WARPS = 16;
@@ -188,6 +189,7 @@ __global__ void __launch_bounds__(G * WARPS * 32, 1) gemv_mma_kernel(const MmaGe
             if (p.y) {
                 float v = dequant_out(a, e_sw, my_sx, e_bias, p.bias != nullptr);
                 if (p.resid) v = __fadd_rn(v, e_res);
+                if (p.relu) v = fmaxf(v, 0.0f);
                 p.y[off] = v;
                 for (int r = 0; r < p.n_more; ++r) p.y_more[r][off] = v;  // peer copies over NVLink
             }
@@ -312,6 +314,7 @@ int launch_gemv_mma(const FwdArgs &a, cudaStream_t stream) {
     p.n_more = a.y ? a.n_more : 0;
     for (int r = 0; r < MAX_PEERS - 1; ++r) p.y_more[r] = r < p.n_more ? a.y_more[r] : nullptr;
     p.resid = a.y ? a.resid : nullptr;
+    p.relu = a.relu ? 1 : 0;
     if (a.n <= 8) return launch_nb<1>(p, stream);
     if (a.n <= 16) return launch_nb<2>(p, stream);
     return launch_nb<4>(p, stream);

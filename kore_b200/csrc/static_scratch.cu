@@ -19,8 +19,10 @@
 // The array's name is only a host-side stand-in for the device object, not an address a
 // kernel can use.  The first call on each device therefore looks the address up with
 // cudaGetSymbolAddress (device made current first, return code checked) and caches it;
-// later calls reuse the cached pointer.  Make that first call during set-up, before any
-// stream capture begins.
+// later calls reuse the cached pointer.  The first launch of each kernel the call can pick
+// (by token count: 1, 2, 3..4, 5..8, 9..128, 129..256, above 256) additionally loads that kernel and
+// sets its shared-memory limit.  Make one warm-up call per token-count class in use during
+// set-up, before any stream capture begins and before the memory budget is frozen.
 #include <mutex>
 
 #include "common.cuh"

@@ -37,6 +37,22 @@ def quat_matmul(a_packed, a_scales, b, m: int, n: int, k: int) -> np.ndarray:
     return _one_shot(_cabi.lib().kb_quat_matmul, a_packed, a_scales, b, m, n, k)
 
 
+def quat_matmul_bias_relu(a_packed, a_scales, b, bias, m: int, n: int, k: int) -> np.ndarray:
+    """C[M,N] = max(0, quat(A)[M,K] @ B[K,N] * scales[M] + bias[M])  (cuda/ops.rs:828-878); bias is
+    per output feature (weight row)."""
+    a = np.ascontiguousarray(a_packed, dtype=np.uint8).ravel()
+    s = np.ascontiguousarray(a_scales, dtype=np.float32).ravel()
+    bi = np.ascontiguousarray(bias, dtype=np.float32).ravel()
+    b = np.asarray(b)
+    if b.dtype != np.float32:
+        raise KoreError(_cabi.ERR_DTYPE, f"unsupported dtype {b.dtype}")
+    b = np.ascontiguousarray(b).reshape(k, n)
+    c = np.zeros((m, n), np.float32)
+    _cabi.check(_cabi.lib().kb_quat_matmul_bias_relu(a.ctypes.data, a.size, s.ctypes.data, s.size, b.ctypes.data,
+                                                     bi.ctypes.data, bi.size, c.ctypes.data, m, n, k))
+    return c
+
+
 def ternary_ternary_matmul(a_packed, a_scales, b_packed, b_scales, m: int, n: int, k: int) -> np.ndarray:
     """C[M,N] = (ternary(A)[M,K] . ternary(B)[N,K]) * a_scales[M] * b_scales[N], integer dot products
     (both operands base-243 rows; cpu_ternary_matmul.rs:131-193)."""

@@ -138,6 +138,26 @@ class _QuantLinear:
             return out[0].cpu().numpy().reshape(*lead, -1), out[1].cpu().numpy().reshape(*lead, -1)
         return out.cpu().numpy().reshape(*lead, self.out_features) if x.ndim > 1 else out.cpu().numpy().reshape(-1)
 
+    def forward_relu(self, x, path: int = PATH_AUTO):
+        """max(forward(x), 0) with the ReLU in the kernel epilogue (CUDA float32 tensor in and out):
+        the layer-shaped form of the reference's fused bias + ReLU dequantising matmul
+        (crates/kore-kernels/src/cuda/ops.rs:828-878)."""
+        import torch
+
+        if not _is_torch(x) or not x.is_cuda or x.dtype != torch.float32:
+            raise KoreError(_cabi.ERR_DTYPE, "forward_relu expects a CUDA float32 tensor")
+        if x.dim() == 0:
+            raise KoreError(_cabi.ERR_SHAPE, f"shape mismatch: expected [{self.in_features}], got []")
+        in_dim = x.shape[-1]
+        lead = tuple(x.shape[:-1])
+        n = int(np.prod(lead)) if x.dim() > 1 else 1
+        x2 = x.reshape(n, in_dim).contiguous()
+        y = torch.empty((n, self.out_features), dtype=torch.float32, device=x.device)
+        _cabi.check(_cabi.lib().kb_linear_forward_act(
+            self._h, x2.data_ptr(), n, in_dim, y.data_ptr(), 0, _cabi.ACT_RELU, path, None, 0,
+            _current_stream_ptr(x.device.index)))
+        return y.reshape(*lead, self.out_features) if x.dim() > 1 else y.reshape(self.out_features)
+
     def _forward_torch(self, x, path, return_acc):
         import torch
 

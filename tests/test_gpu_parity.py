@@ -189,7 +189,18 @@ FULL_SIZES = [
     ("prefill_up_2048tok", 11008, 4096, 2048, T),
     ("prefill_down_2048tok", 4096, 11008, 2048, T),
     ("ffn70b_8192x28672_b1", 28672, 8192, 1, T),
+    ("ffn70b_8192x28672_b8", 28672, 8192, 8, T),
+    ("ffn70b_8192x28672_b16", 28672, 8192, 16, T),
     ("ffn70b_8192x28672_b64", 28672, 8192, 64, T),
+    ("ffn70b_8192x28672_b512", 28672, 8192, 512, T),
+    # the decoder configuration's projections: q|k|v concatenated, gate/up interleaved, down (K = 8640
+    # is a multiple of 64 but not of 128: the last K tile is masked)
+    ("decoder_qkv_9600x3200_b1", 9600, 3200, 1, T),
+    ("decoder_qkv_9600x3200_b16", 9600, 3200, 16, T),
+    ("decoder_gate_up_17280x3200_b1", 17280, 3200, 1, T),
+    ("decoder_gate_up_17280x3200_b16", 17280, 3200, 16, T),
+    ("decoder_down_3200x8640_b1", 3200, 8640, 1, T),
+    ("decoder_down_3200x8640_b16", 3200, 8640, 16, T),
 ]
 
 
@@ -215,13 +226,61 @@ def test_full_size_checksum_and_sampled_rows(torch, kb, name, m, k, n, kind):
     acc_h, y_h = acc.cpu().numpy(), y.cpu().numpy()
     xq, sx, _ = kbref.quantize_act_i8(x)
     w_i8 = kbref.decode_weights_i8(kind, packed, m, k)
-    colsum = w_i8.astype(np.int64).sum(axis=0)
+    colsum = w_i8.sum(axis=0, dtype=np.int64)
     assert (acc_h.astype(np.int64).sum(axis=1) == xq.astype(np.int64) @ colsum).all()
     rows = np.random.default_rng(1).choice(m, size=48, replace=False)
     acc_ref = kbref.acc_i32(np.ascontiguousarray(w_i8[rows]), xq, threads=8)
     assert (acc_h[:, rows] == acc_ref).all()
     assert (y_h[:, rows] == kbref.dequant_epilogue(acc_ref, scales[rows], sx)).all()
     assert np.isfinite(y_h).all()
+
+
+# token counts x K at which the decode GEMV's activation stage is exactly 48 KiB (the default
+# shared-memory limit once the kernel's static arrays are added) or just beside it
+@pytest.mark.parametrize("n,k", [(3, 11008), (4, 12288), (8, 6144), (5, 5120), (2, 24576), (8, 5000)])
+@pytest.mark.parametrize("kind", [T, Q])
+def test_gemv_at_the_shared_memory_opt_in_boundary(torch, kb, kind, n, k):
+    m = 200
+    w = cases.gaussian(31 * n + k, (m, k), 0.02)
+    packed, scales = cases.make_weights(kind, "absmean" if kind == T else "reference", w)
+    bias = cases.gaussian(4, (m,), 0.1)
+    x = cases.gaussian(77 + n, (n, k), 1.0)
+    y_ref, acc_ref = kbref.q_forward(kind, packed, scales, bias, m, k, x, threads=4)
+    lay = _layer(kb, kind, packed, scales, bias, m, k)
+    xd = torch.from_numpy(x).cuda()
+    for p in (kb.cabi.PATH_GEMV, kb.cabi.PATH_AUTO):
+        y, acc = lay.forward(xd, path=p, return_acc=True)
+        assert (acc.cpu().numpy() == acc_ref).all() and (y.cpu().numpy() == y_ref).all()
+    xq, sx, sumq = kb.kernels.quantize_act_i8(xd)
+    assert (kb.kernels.forward_q8(lay, xq, sx, sumq, path=kb.cabi.PATH_GEMV).cpu().numpy() == y_ref).all()
+    # the allocation-free entry point takes the same kernel for up to 8 tokens
+    ys = torch.empty((n, m), dtype=torch.float32, device="cuda")
+    kb.cabi.check(kb.cabi.lib().kb_linear_forward_static(lay.handle, xd.data_ptr(), n, k, ys.data_ptr(), None))
+    assert (ys.cpu().numpy() == y_ref).all()
+
+
+# ---- ReLU in the epilogue (cuda/ops.rs:828-878 in layer form) -----------------------------
+@pytest.mark.parametrize("kind", [T, Q])
+@pytest.mark.parametrize("m,k,n", [(128, 256, 1), (130, 1000, 5), (257, 2304, 12), (200, 640, 70), (384, 640, 300)])
+def test_relu_epilogue(torch, kb, kind, m, k, n):
+    w = cases.gaussian(500 + m + k, (m, k), 0.02)
+    packed, scales = cases.make_weights(kind, "reference", w)
+    bias = cases.gaussian(6, (m,), 0.1)
+    x = cases.gaussian(600 + n, (n, k), 1.0)
+    y_ref = np.maximum(kbref.q_forward(kind, packed, scales, bias, m, k, x, threads=4)[0], np.float32(0.0))
+    assert (y_ref == 0).any() and (y_ref > 0).any()
+    lay = _layer(kb, kind, packed, scales, bias, m, k)
+    paths = [kb.cabi.PATH_AUTO, kb.cabi.PATH_GEMM_TC] + ([kb.cabi.PATH_GEMV] if n <= 8 else []) + ([kb.cabi.PATH_GEMV_MMA] if n <= 32 else [])
+    for p in paths:
+        y = lay.forward_relu(torch.from_numpy(x).cuda(), path=p)
+        assert (y.cpu().numpy() == y_ref).all(), p
+    if kind == Q:
+        # kernel-shaped one-shot: b [K,N] in, c [M,N] out, bias per weight row
+        c = kb.kernels.quat_matmul_bias_relu(packed, scales, np.ascontiguousarray(x.T), bias, m, n, k)
+        assert (c == y_ref.T).all()
+        with pytest.raises(kb.nn.KoreError) as e:
+            kb.kernels.quat_matmul_bias_relu(packed, scales, np.ascontiguousarray(x.T), bias[:-1], m, n, k)
+        assert e.value.code == kb.cabi.ERR_STORAGE
 
 
 def test_auto_path_matches_and_host_entry(torch, kb):

@@ -2,8 +2,9 @@
 (fixed-footprint real-time loops, plugins living under someone else's allocator, engines
 whose pools are frozen).  Its quantised activations live in a fixed 1 MiB array inside the
 library instead of freshly allocated scratch, so this file checks, through the C ABI, that
-it returns exactly what the regular entry point returns, twice in a row on the shared
-array, and that it refuses work that does not fit.
+it returns exactly what the regular entry point returns — and what the CPU oracle computes
+from the same packed weights — twice in a row on the shared array, and that it refuses
+work that does not fit.
 
 Collected last on purpose (file name): a run that stops at the first failure has then
 already exercised every other test.
@@ -24,6 +25,7 @@ def test_static_scratch_forward_matches_regular_forward_twice():
     import torch
 
     from kore_b200 import _cabi, nn
+    from oracle import kbref
 
     assert torch.cuda.is_available()
     lib = _cabi.lib()
@@ -31,7 +33,8 @@ def test_static_scratch_forward_matches_regular_forward_twice():
     assert limit == 1 << 20
     stream = torch.cuda.current_stream().cuda_stream
 
-    lay_a = nn.BitLinear.new(_gauss(1, (384, 1000), 0.02), _gauss(2, (384,), 0.1), 0.3, quantiser="absmean")
+    lay_a_bias = _gauss(2, (384,), 0.1)
+    lay_a = nn.BitLinear.new(_gauss(1, (384, 1000), 0.02), lay_a_bias, 0.3, quantiser="absmean")
     lay_b = nn.QuatLinear.new(_gauss(3, (200, 4096), 0.02))
     # two calls in a row on the shared array: the second is smaller in both dimensions, so
     # it runs over bytes the first call left behind; then a decode-sized call (GEMV branch)
@@ -48,6 +51,11 @@ def test_static_scratch_forward_matches_regular_forward_twice():
         # same kernels, same arithmetic: the comparison is exact, like every other parity test here
         assert torch.equal(y_static, y_regular)
         assert torch.isfinite(y_static).all()
+        # and the checker that shares no code with either entry point
+        kind = kbref.TERNARY if lay is lay_a else kbref.QUATERNARY
+        bias = lay_a_bias if lay is lay_a else None
+        y_ref = kbref.q_forward(kind, lay.packed_weights(), lay.scales(), bias, m, k, x.cpu().numpy(), threads=4)[0]
+        assert (y_static.cpu().numpy() == y_ref).all()
 
 
 def test_static_scratch_rejects_oversized_and_bad_arguments():
