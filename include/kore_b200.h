@@ -61,8 +61,10 @@ enum {
  * SMs better and their aggregate bandwidth is higher.  Use it when several GEMVs are in
  * flight at once; use KB_PATH_GEMV (or AUTO) for a chain of dependent layers.
  * KB_PATH_GEMV_MMA is the small-batch kernel (up to 32 tokens whose int8 activations fit in
- * shared memory): weights stream global -> registers -> warp-level int8 MMA. */
-enum { KB_PATH_AUTO = 0, KB_PATH_GEMV = 1, KB_PATH_GEMM_TC = 2, KB_PATH_GEMV_SHARED = 3, KB_PATH_GEMV_MMA = 4 };
+ * shared memory): weights stream global -> registers -> warp-level int8 MMA.
+ * KB_PATH_GEMV_STREAM is the streaming decode kernel (1..32 tokens): every warp runs its own ring
+ * of bulk-copied 16-row stages in shared memory and contracts them with the warp-level int8 MMA. */
+enum { KB_PATH_AUTO = 0, KB_PATH_GEMV = 1, KB_PATH_GEMM_TC = 2, KB_PATH_GEMV_SHARED = 3, KB_PATH_GEMV_MMA = 4, KB_PATH_GEMV_STREAM = 5 };
 
 /* epilogue activation of kb_linear_forward_act */
 enum { KB_ACT_NONE = 0, KB_ACT_RELU = 1 };

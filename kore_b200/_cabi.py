@@ -15,7 +15,7 @@ ERR_TIMEOUT, ERR_BAD_HANDLE, ERR_INVALID, ERR_UNSUPPORTED = 6, 7, 8, 9
 TERNARY, QUATERNARY = 0, 1
 QUANT_REFERENCE, QUANT_ABSMEAN = 0, 1
 ACT_NONE, ACT_RELU = 0, 1
-PATH_AUTO, PATH_GEMV, PATH_GEMM_TC, PATH_GEMV_SHARED, PATH_GEMV_MMA = 0, 1, 2, 3, 4
+PATH_AUTO, PATH_GEMV, PATH_GEMM_TC, PATH_GEMV_SHARED, PATH_GEMV_MMA, PATH_GEMV_STREAM = 0, 1, 2, 3, 4, 5
 
 _u8p, _i8p = C.POINTER(C.c_uint8), C.POINTER(C.c_int8)
 _f32p, _i32p = C.POINTER(C.c_float), C.POINTER(C.c_int32)

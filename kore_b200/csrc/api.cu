@@ -140,7 +140,12 @@ static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim
         a.x = x;
         return launch_gemv(a, stream);
     }
-    if (path != KB_PATH_GEMM_TC && path != KB_PATH_GEMV_MMA) return fail(KB_ERR_INVALID, "unknown path %d", path);
+    if (path == KB_PATH_GEMV_STREAM && n <= 8) {  // the quantiser runs in the kernel's prologue
+        a.x = x;
+        return launch_gemv_stream(a, stream);
+    }
+    if (path != KB_PATH_GEMM_TC && path != KB_PATH_GEMV_MMA && path != KB_PATH_GEMV_STREAM)
+        return fail(KB_ERR_INVALID, "unknown path %d", path);
     const size_t need = workspace_bytes(L, n);
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     bool own = false;
@@ -156,7 +161,8 @@ static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim
     int rc = launch_act_quant(x, n, L->k, xq, L->kp, sx, sumq, stream);
     if (rc == KB_OK) {
         a.xq = xq; a.ldq = L->kp; a.sx = sx; a.sumq = sumq;
-        rc = path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, stream) : launch_gemm_tc(a, stream);
+        rc = path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, stream)
+             : (path == KB_PATH_GEMV_STREAM ? launch_gemv_stream(a, stream) : launch_gemm_tc(a, stream));
     }
     if (own) {
         cudaError_t e = cudaFreeAsync(ws, stream);
@@ -526,6 +532,7 @@ int kb_linear_forward_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const
     if (path == KB_PATH_GEMV_SHARED) { a.shared_grid = true; path = KB_PATH_GEMV; }
     if (path == KB_PATH_GEMV) return launch_gemv(a, static_cast<cudaStream_t>(stream));
     if (path == KB_PATH_GEMV_MMA) return launch_gemv_mma(a, static_cast<cudaStream_t>(stream));
+    if (path == KB_PATH_GEMV_STREAM) return launch_gemv_stream(a, static_cast<cudaStream_t>(stream));
     if (path == KB_PATH_GEMM_TC) return launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
     return fail(KB_ERR_INVALID, "unknown path %d", path);
 }
@@ -548,6 +555,7 @@ int kb_linear_forward_fused(const kb_linear *h, const float *x, const int8_t *xq
         a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq;
         if (path == KB_PATH_GEMV) return launch_gemv(a, st);
         if (path == KB_PATH_GEMV_MMA) return launch_gemv_mma(a, st);
+        if (path == KB_PATH_GEMV_STREAM) return launch_gemv_stream(a, st);
         if (path == KB_PATH_GEMM_TC) return launch_gemm_tc(a, st);
         return fail(KB_ERR_INVALID, "unknown path %d", path);
     }
@@ -555,7 +563,12 @@ int kb_linear_forward_fused(const kb_linear *h, const float *x, const int8_t *xq
         a.x = x;
         return launch_gemv(a, st);
     }
-    if (path != KB_PATH_GEMM_TC && path != KB_PATH_GEMV_MMA) return fail(KB_ERR_INVALID, "unknown path %d", path);
+    if (path == KB_PATH_GEMV_STREAM && n <= 8) {
+        a.x = x;
+        return launch_gemv_stream(a, st);
+    }
+    if (path != KB_PATH_GEMM_TC && path != KB_PATH_GEMV_MMA && path != KB_PATH_GEMV_STREAM)
+        return fail(KB_ERR_INVALID, "unknown path %d", path);
     const size_t need = workspace_bytes(L, n);
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     if (!ws || workspace_bytes_ < need || (reinterpret_cast<uintptr_t>(ws) & 255))
@@ -567,7 +580,8 @@ int kb_linear_forward_fused(const kb_linear *h, const float *x, const int8_t *xq
     int rc = launch_act_quant(x, n, L->k, wq, L->kp, wsx, wsum, st);
     if (rc) return rc;
     a.xq = wq; a.ldq = L->kp; a.sx = wsx; a.sumq = wsum;
-    return path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, st) : launch_gemm_tc(a, st);
+    return path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, st)
+           : (path == KB_PATH_GEMV_STREAM ? launch_gemv_stream(a, st) : launch_gemm_tc(a, st));
 }
 
 int kb_linear_forward_rmsnorm(const kb_linear *h, const float *x, const float *gamma, float eps, size_t n, float *y,

@@ -56,6 +56,13 @@ struct Linear {
     int *dev_status;  // one int in device memory
 };
 
+// one member of a grouped launch (device pointers of its handle)
+struct LayerRef {
+    const uint8_t *w2;
+    const float *sw;
+    const float *bias;  // nullptr: no bias
+};
+
 // ---- error plumbing (api.cu) -----------------------------------------------------
 int fail(int code, const char *fmt, ...);
 int cuda_fail(cudaError_t e, const char *what);
@@ -142,6 +149,21 @@ bool gemv_mma_supports(const Linear *lin, size_t n);
 int launch_gemv_mma(const FwdArgs &a, cudaStream_t stream);
 // decode GEMV; when args.x is set the activation quantiser is fused into its prologue
 int launch_gemv(const FwdArgs &a, cudaStream_t stream);
+// streaming decode kernel (bulk-copy row pipeline + warp-level int8 MMA), up to 32 tokens;
+// activations f32 (quantised in the prologue, up to 8 tokens) or pre-quantised
+bool gemv_stream_supports(const Linear *lin, size_t n);
+int launch_gemv_stream(const FwdArgs &a, cudaStream_t stream);
+// the same kernel over `count` same-shaped layers, one token each (layer i reads row i of the inputs)
+struct GroupArgs {
+    const LayerRef *table;  // device, [count]
+    int device, kind, mul, off;
+    size_t count, m, k, kp, row_bytes;
+    const float *x; size_t ldx;                                               // f32 inputs, or
+    const int8_t *xq; size_t ldq; const float *sx; const int32_t *sumq;        // pre-quantised inputs
+    float *y; size_t ldy;
+    int *status;  // device word for a bounded wait that gave up (nullable)
+};
+int launch_group_stream(const GroupArgs &a, cudaStream_t stream);
 // tcgen05 int8 GEMM; needs pre-quantised activations
 int launch_gemm_tc(const FwdArgs &a, cudaStream_t stream);
 // same contract, CTA-pair kernel (tcgen05 cta_group::2); chosen by launch_gemm_tc for large token counts

@@ -28,12 +28,6 @@ namespace {
 constexpr uint32_t GROUP_MAGIC = 0x4b423247u;  // "KB2G"
 constexpr int MAX_STAGED = 32;                 // layers whose activations one CTA may hold
 
-struct LayerRef {
-    const uint8_t *w2;
-    const float *sw;
-    const float *bias;  // nullptr: no bias
-};
-
 struct Group {
     uint32_t magic;
     int device;
@@ -402,6 +396,15 @@ int group_forward(const Group *G, const float *x, size_t ldx, const int8_t *xq, 
     if (ldy == 0) ldy = G->m;
     if (ldy < G->m) return fail(KB_ERR_SHAPE, "shape mismatch: ldy %zu is smaller than out_features %zu", ldy, G->m);
     ScopedDevice dev(G->device);
+    static const int impl = env_int("KB_GROUP_IMPL", 1);  // 1: streaming MMA kernel, 0: dp4a kernel
+    if (impl == 1) {
+        GroupArgs ga = {};
+        ga.table = G->table; ga.device = G->device; ga.kind = G->kind; ga.mul = G->mul; ga.off = G->off;
+        ga.count = G->count; ga.m = G->m; ga.k = G->k; ga.kp = G->kp; ga.row_bytes = G->row_bytes;
+        ga.x = x; ga.ldx = ldx; ga.xq = xq; ga.ldq = ldq; ga.sx = sx; ga.sumq = sumq;
+        ga.y = y; ga.ldy = ldy; ga.status = nullptr;
+        return launch_group_stream(ga, stream);
+    }
     // launch shapes: {chunks in flight per warp, threads per CTA, CTAs per SM}
     static const int cfg_id = env_int("KB_GROUP_CFG", 1);
     const int shape = (cfg_id >= 0 && cfg_id <= 4) ? cfg_id : 1;

@@ -1,12 +1,16 @@
 """CPU restatement (numpy) of the decoder step around the quantized-linear path.
 
-TEST INFRASTRUCTURE ONLY (see kbref.h).  Parity status: the reference's decoder
-(``crates/kore-edge/src/runtime.rs:106-294``) has no recorded outputs and cannot be run
-here, so this restatement is pinned only through its parts: RMSNorm against the formula of
-``crates/kore-kernels/src/cpu_fused.rs:160-190``, RoPE against the identity-at-position-0
-and rotation properties asserted in ``crates/kore-edge/src/ops/rope.rs:38-80``, attention
-against a direct softmax(QK^T)V, and every projection through ``kbref.q_forward``.
-Projections use the W2A8 arithmetic (per-token int8 activations), as the GPU path does.
+TEST INFRASTRUCTURE ONLY (see kbref.h).  Parity status: the reference's decoder loop
+(``crates/kore-edge/src/runtime.rs:106-294``) has no recorded end-to-end outputs and cannot
+be run here, so this restatement is pinned operator by operator against every known answer
+the reference's own unit tests hold for them (``tests/golden/decoder_kats.json``, checked in
+``tests/test_decoder_ref_cpu.py``): RMSNorm (``crates/kore-edge/src/ops/norm.rs:43-49``,
+``crates/kore-kernels/src/cpu_fused.rs:264-276``), the fused RMSNorm + projection and
+RMSNorm x SiLU-gate references (``cpu_fused.rs:309-370,451-489``), RoPE
+(``crates/kore-edge/src/ops/rope.rs:43-75``), attention (``ops/attention.rs:142-207``), SiLU
+and softmax (``ops/activation.rs:87-119``); every projection goes through the pinned
+``kbref.q_forward``.  Projections use the W2A8 arithmetic (per-token int8 activations), as
+the GPU path does.
 """
 from __future__ import annotations
 
@@ -30,6 +34,27 @@ def silu_mul(g, u):
     """(g / (1 + exp(-g))) * u — ops/activation.rs:21-26, runtime.rs:249-252"""
     g = np.asarray(g, f32)
     return ((g / (f32(1.0) + np.exp(-g).astype(f32))).astype(f32) * np.asarray(u, f32)).astype(f32)
+
+
+def silu(x):
+    """x / (1 + exp(-x)) — ops/activation.rs:21-26"""
+    x = np.asarray(x, f32)
+    return (x / (f32(1.0) + np.exp(-x).astype(f32))).astype(f32)
+
+
+def softmax(x):
+    """over the last axis, max subtracted first — ops/activation.rs:37-56"""
+    x = np.asarray(x, f32)
+    e = np.exp((x - x.max(axis=-1, keepdims=True)).astype(f32)).astype(f32)
+    return (e * (f32(1.0) / e.sum(axis=-1, keepdims=True, dtype=f32))).astype(f32)
+
+
+def rope_tables(head_dim, max_len, base):
+    """cos/sin [max_len, head_dim/2]: freq_i = 1 / base^(2i/head_dim), angle = pos * freq_i (ops/rope.rs:24-27)"""
+    i = np.arange(head_dim // 2, dtype=f32)
+    freq = (f32(1.0) / np.power(f32(base), (f32(2.0) * i / f32(head_dim)).astype(f32))).astype(f32)
+    ang = (np.arange(max_len, dtype=f32)[:, None] * freq[None, :]).astype(f32)
+    return np.cos(ang).astype(f32), np.sin(ang).astype(f32)
 
 
 def rope(x, positions, cos, sin):

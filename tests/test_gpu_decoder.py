@@ -294,3 +294,109 @@ def test_fused_projection_argument_checks(env):
     t.cuda.synchronize()
     lay.close()
     odd.close()
+
+
+# ---- the reference's own known answers for these operators, on the GPU kernels ----------------
+def _decoder_kats():
+    import json
+    import os
+
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "decoder_kats.json")) as fh:
+        return json.load(fh)
+
+
+def _gpu_rmsnorm(env, x, gamma, eps):
+    t = env.torch
+    n, d = x.shape
+    xd, gd = t.from_numpy(np.ascontiguousarray(x, np.float32)).cuda(), t.from_numpy(np.asarray(gamma, np.float32)).cuda()
+    xn = t.empty((n, d), device="cuda")
+    env.cabi.check(env.lib.kb_rmsnorm_quant(xd.data_ptr(), gd.data_ptr(), n, d, C.c_float(eps), xn.data_ptr(), None, 0, None, None,
+                                            env.sp))
+    t.cuda.synchronize()
+    return xn.cpu().numpy()
+
+
+def _gpu_swiglu(env, gate, up):
+    t = env.torch
+    n, f = gate.shape
+    gu = t.from_numpy(np.concatenate([gate, up], axis=1).astype(np.float32)).cuda()
+    h = t.empty((n, f), device="cuda")
+    env.cabi.check(env.lib.kb_swiglu_quant(gu.data_ptr(), n, f, 2 * f, h.data_ptr(), None, 0, None, None, env.sp))
+    t.cuda.synchronize()
+    return h.cpu().numpy()
+
+
+def test_reference_known_answers_norm_and_gate_kernels(env):
+    k = _decoder_kats()
+    for c in k["rmsnorm"]:
+        out = _gpu_rmsnorm(env, np.array([c["x"]], np.float32), c["gamma"], c["eps"]).ravel()
+        for idx, (lo, hi) in c.get("between", {}).items():
+            assert lo < out[int(idx)] < hi
+        for idx, v in c.get("greater", {}).items():
+            assert out[int(idx)] > v
+    c = k["rmsnorm_proj"][0]
+    x = np.array(c["x"], np.float32).reshape(c["batch"], c["hidden"])
+    assert np.abs(_gpu_rmsnorm(env, x, c["gamma"], c["eps"]).ravel() - np.array(c["normed"], np.float32)).max() < c["tol"]
+    c = k["silu"][0]
+    out = _gpu_swiglu(env, np.array([c["x"]], np.float32), np.ones((1, len(c["x"])), np.float32)).ravel()
+    assert abs(out[0]) < c["abs_less"]["0"] and out[1] > c["greater"]["1"]
+    c = k["rmsnorm_silu_gate"][0]
+    x = np.array(c["x"], np.float32).reshape(c["rows"], c["cols"])
+    z = np.array(c["z"], np.float32).reshape(c["rows"], c["cols"])
+    out = _gpu_swiglu(env, z, _gpu_rmsnorm(env, x, c["gamma"], c["eps"])).ravel()
+    assert np.isfinite(out).all() and abs(out[c["zero_index"]]) < c["tol"]
+    assert np.abs(out - np.array(c["expect"], np.float32)).max() < c["tol"]
+
+
+def test_reference_known_answers_rope_and_attention_kernels(env):
+    t = env.torch
+    k = _decoder_kats()
+    for c in k["rope"]:
+        H, hd = c["n_heads"], c["head_dim"]
+        d = H * hd
+        cos, sin = dr.rope_tables(hd, 16, c["base"])
+        data = np.array(c["data"], np.float32)
+        qkv = t.from_numpy(np.concatenate([data, data, data])[None, :]).cuda()  # q = k = v = the case's row
+        q_out = t.empty((1, d), device="cuda")
+        kc, vc = t.zeros((1, d), device="cuda"), t.zeros((1, d), device="cuda")
+        pos = t.tensor([c["pos"]], dtype=t.int32, device="cuda")
+        row = t.tensor([0], dtype=t.int64, device="cuda")
+        cosd, sind = t.from_numpy(cos).cuda(), t.from_numpy(sin).cuda()
+        env.cabi.check(env.lib.kb_rope_kv(qkv.data_ptr(), pos.data_ptr(), row.data_ptr(), cosd.data_ptr(), sind.data_ptr(), 1, H, hd,
+                                          q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), env.sp))
+        t.cuda.synchronize()
+        for y in (q_out.cpu().numpy().ravel(), kc.cpu().numpy().ravel()):  # q and the cached k are both rotated
+            if "expect" in c:
+                assert np.abs(y - np.array(c["expect"], np.float32)).max() < c["tol"]
+            if "changes_by_more_than" in c:
+                assert np.abs(y - data).max() > c["changes_by_more_than"]
+            if "pair" in c:
+                a, b = c["pair"]
+                assert abs(float(np.sqrt(y[a] * y[a] + y[b] * y[b])) - c["pair_norm"]) < c["tol"]
+        assert (vc.cpu().numpy().ravel() == data).all()  # v goes to the cache untouched
+    for c in k["attention"]:
+        seq, H, hd = c["seq"], c["n_heads"], c["head_dim"]
+        d = H * hd
+        q = np.array(c["q"], np.float32).reshape(seq, d)
+        kk = np.array(c["k"], np.float32).reshape(seq, d)
+        v = np.array(c["v"], np.float32).reshape(seq, d)
+        # the decode kernel serves one query per sequence: query i becomes sequence i over the same
+        # cache, seeing i + 1 positions (causal) or all of them
+        kc = t.from_numpy(np.broadcast_to(kk, (seq, seq, d)).copy()).cuda()
+        vc = t.from_numpy(np.broadcast_to(v, (seq, seq, d)).copy()).cuda()
+        lens = t.tensor([i + 1 if c["causal"] else seq for i in range(seq)], dtype=t.int32, device="cuda")
+        out = t.empty((seq, d), device="cuda")
+        nbytes = int(env.lib.kb_attn_decode_scratch_bytes(seq, H))
+        scratch = t.zeros(max(nbytes, 4), dtype=t.uint8, device="cuda")
+        qd = t.from_numpy(q).cuda()
+        env.cabi.check(env.lib.kb_attn_decode(qd.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens.data_ptr(), seq, H, hd, seq,
+                                              out.data_ptr(), scratch.data_ptr(), nbytes, env.sp))
+        t.cuda.synchronize()
+        o = out.cpu().numpy()
+        if "expect_all" in c:
+            assert np.abs(o - c["expect_all"]).max() < c["tol"]
+        if "expect_row0" in c:
+            assert np.abs(o[0] - np.array(c["expect_row0"], np.float32)).max() < c["tol"]
+        ref = dr.attention(q.reshape(seq, H, hd), kk.reshape(seq, H, hd), v.reshape(seq, H, hd), 0).reshape(seq, d) if c["causal"] else None
+        if ref is not None:
+            assert np.abs(o - ref).max() < 1e-5

@@ -151,14 +151,14 @@ SHAPES = [
 ]
 
 
-@pytest.mark.parametrize("path", ["gemv", "gemv_shared", "gemv_mma", "gemm_tc"])
+@pytest.mark.parametrize("path", ["gemv", "gemv_shared", "gemv_mma", "gemv_stream", "gemm_tc"])
 @pytest.mark.parametrize("kind,quantiser", [(T, "reference"), (T, "absmean"), (Q, "reference")])
 @pytest.mark.parametrize("m,k,n", SHAPES)
 def test_forward_bit_exact(torch, kb, path, kind, quantiser, m, k, n):
     if path.startswith("gemv") and n > 40:
         pytest.skip("decode kernel is exercised up to a few token groups")
-    if path == "gemv_mma" and n > 32:
-        pytest.skip("small-batch kernel takes up to 32 tokens")
+    if path in ("gemv_mma", "gemv_stream") and n > 32:
+        pytest.skip("small-batch kernels take up to 32 tokens")
     w = cases.gaussian(1000 + m + k, (m, k), 0.02)
     packed, scales = cases.make_weights(kind, quantiser, w)
     bias = cases.gaussian(3, (m,), 0.1) if (m + n) % 2 else None
@@ -166,7 +166,7 @@ def test_forward_bit_exact(torch, kb, path, kind, quantiser, m, k, n):
     y_ref, acc_ref = kbref.q_forward(kind, packed, scales, bias, m, k, x, threads=4)
     lay = _layer(kb, kind, packed, scales, bias, m, k)
     p = {"gemv": kb.cabi.PATH_GEMV, "gemv_shared": kb.cabi.PATH_GEMV_SHARED, "gemv_mma": kb.cabi.PATH_GEMV_MMA,
-         "gemm_tc": kb.cabi.PATH_GEMM_TC}[path]
+         "gemv_stream": kb.cabi.PATH_GEMV_STREAM, "gemm_tc": kb.cabi.PATH_GEMM_TC}[path]
     y, acc = lay.forward(torch.from_numpy(x).cuda(), path=p, return_acc=True)
     torch.cuda.synchronize()
     st = C.c_int(0)
