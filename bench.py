@@ -4,23 +4,30 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 Headline workload (N = 1): the batch-1 decode GEMV of the benchmark specification's second configuration —
-ternary 4096x4096 weights (absmean-ternarised N(0, 0.02^2), seed 2001), one f32
-activation row N(0,1) (seed 2002), per-token int8 absmax fused into the kernel.
-A "step" is one pass over a pool of POOL distinct copies of that layer (each copy has
-its own allocation, POOL * 4 MiB > the 126 MB L2, so every weight byte comes from HBM).
-Each layer forward is two launches — the per-token int8 quantiser of its f32 input and
-the decode GEMV — and the layers of the pool, which are independent of one another, are
-spread round-robin over STREAMS CUDA streams; the whole step is captured once and
-replayed as one CUDA graph.  value = algorithmic bytes of the step / device time.
-The same pool as a single stream-ordered chain (what a decoder's dependent layers look
-like) is reported under "extra".
+ternary 4096x4096 weights (absmean-ternarised N(0, 0.02^2), seed 2001), one f32 activation row N(0,1)
+(seed 2002) per layer.  A "step" is one pass over a pool of POOL separately allocated copies of that layer
+(POOL * 4 MiB > the 126 MB L2, so every weight byte comes from HBM), every layer with its own input row:
+ONE kb_linear_group_forward launch — the per-token int8 quantiser runs in the kernel's prologue, then the
+streaming GEMV over all layers — captured in a CUDA graph.  value = algorithmic bytes of the step / device
+time.  Beside it, at the same level of the JSON line:
 
-With N > 1 the layers of the pool are independent units, so every rank runs the N = 1 step on
-its own pool (weak scaling, no exchange; value = all ranks' bytes / max time over ranks).  What
-does need an exchange is measured beside it under "extra": the same pool as column-sharded
-layers (every rank owns a 4096-row shard of a K=4096 x M=4096*N projection and all ranks end
-each layer with the full y[1, 4096*N]) and the sharded 8192 -> 28672 projection at batch
-1 / 8 / 64 / 512.
+  e2e            the same step through kb_linear_group_forward_host (host buffers, copies timed)
+  e2e_drop_in    the same pool as POOL synchronous kb_linear_forward_host calls: what a caller of the
+                 reference's forward gets without restructuring into a group
+  drop_in_chain  the pool as one stream-ordered chain of per-layer launches (dependent layers of a decoder)
+  prefill        2048-token GEMMs (4096 -> 11008, 11008 -> 4096) with their own tensor roofline object
+  decoder        BitNet-3B-shaped decoder, 512-token prompt + 128 greedy steps, batch 1 and 16
+  cpu_baseline   the CPU port of the reference's ternary_matmul on the same packed weights, all host cores
+
+With N > 1 the layers of the pool are independent units, so every rank runs the N = 1 step on its own pool
+(weak scaling, no exchange; value = all ranks' bytes / max time over ranks).  What does need an exchange is
+reported at the top level as `sharded_projection`: the 8192 -> 28672 projection split by output features
+over the ranks at batch 1 / 8 / 64 / 512, every rank ending with the full output, checked against the
+unsharded layer and timed next to it in the same run.
+
+`--impl reference` times the CPU port (oracle/kbref.c, a restatement of the reference's CPU code: the
+reference is Rust and no Rust toolchain exists here) on the same workload and config; a step there is a
+bounded sample of the pool (SAMPLE_LAYERS layers), all host cores.
 
 All inputs are synthetic (no dataset or checkpoint exists for this path).
 """
@@ -44,7 +51,17 @@ if ROOT not in sys.path:
 M_DEC, K_DEC = 4096, 4096
 POOL = 160  # 160 x 4 MiB = 640 MiB of packed weights, five times the L2
 STREAMS = 16
+SAMPLE_LAYERS = 8  # layers of the pool one CPU-arm step runs
 METRIC, UNIT = "bitlinear_gemv_hbm_gbs", "GB/s"
+WORKLOAD = "decode_gemv_ternary_4096x4096_batch1"
+
+
+def headline_config(pool_n):
+    """What is measured, in the same words for both arms (the driver compares the two dicts)."""
+    return {"workload": WORKLOAD, "pool": pool_n, "pool_bytes": pool_n * M_DEC * K_DEC // 4,
+            "weights": "ternary 4096x4096, absmean per-tensor scale, N(0, 0.02^2), seed 2001",
+            "activations": "f32 [1, 4096] N(0, 1) per layer, seed 2002",
+            "l2": "inputs larger than L2 (pool of separately allocated weight copies)"}
 
 
 def gemv_bytes(m, k, n):
@@ -119,40 +136,53 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU arm
-def cpu_reference_arm(budget_s: float = 12.0):
-    """Times the CPU restatement of what the reference runs today for the headline
-    workload: BitLinear::new(W, threshold 0.3) then forward(x[1,4096]) — per-call row
-    decode, both transposes, rows in parallel over all host cores (rayon rule)."""
+def cpu_prepare():
+    """The headline layer in the reference wire format (base-243, per-row scales): the same absmean-ternarised
+    weights the GPU arm uploads, so both arms run one workload."""
     from oracle import kbref
 
-    threads = kbref.max_threads()
     w = gaussian(2001, (M_DEC, K_DEC), 0.02)
     x = gaussian(2002, (1, K_DEC), 1.0)
-    packed, scales = kbref.pack_weights_ternary(w, M_DEC, K_DEC, 0.3)
-    kbref.linear_forward(kbref.TERNARY, packed, scales, None, M_DEC, K_DEC, x, threads=threads)  # warm-up
-    times = []
-    t_end = time.perf_counter() + budget_s
-    while time.perf_counter() < t_end and len(times) < 2000:
-        t0 = time.perf_counter()
+    packed, scales = kbref.pack_weights_ternary_absmean(w, M_DEC, K_DEC)
+    return kbref, packed, scales, x
+
+
+def cpu_step(kbref, packed, scales, x, layers, threads):
+    """`layers` forwards of the 4096x4096 layer as the reference runs them today: BitLinear::forward ->
+    ternary_matmul with per-call row decode, both transposes, rows in parallel over `threads` cores."""
+    t0 = time.perf_counter()
+    for _ in range(layers):
         kbref.linear_forward(kbref.TERNARY, packed, scales, None, M_DEC, K_DEC, x, threads=threads)
-        times.append(time.perf_counter() - t0)
-    best = float(np.median(times))
-    return {"value": gemv_bytes(M_DEC, K_DEC, 1) / best / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"{len(times)} forwards of the 4096x4096 batch-1 layer (median {best * 1e3:.3f} ms each), "
-                      "reference quantiser (per-row absmax, threshold 0.3), f32 activations",
-            "ms_per_forward": best * 1e3}
+    return time.perf_counter() - t0
+
+
+def cpu_reference_arm(steps: int, warmup: int, layers: int = SAMPLE_LAYERS):
+    kbref, packed, scales, x = cpu_prepare()
+    threads = kbref.host_cores()  # not OMP_NUM_THREADS: torch.distributed.run pins that to 1 for its workers
+    for _ in range(max(1, warmup)):
+        cpu_step(kbref, packed, scales, x, layers, threads)
+    times = [cpu_step(kbref, packed, scales, x, layers, threads) for _ in range(max(1, steps))]
+    sec = float(np.mean(times))
+    return {"value": layers * gemv_bytes(M_DEC, K_DEC, 1) / sec / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{len(times)} steps of {layers} forwards of the 4096x4096 batch-1 layer (of the pool's {POOL}), "
+                      f"{sec / layers * 1e3:.3f} ms per forward; the GPU arm's absmean-ternarised weights in the reference "
+                      "wire format, f32 activations, the reference's ternary_matmul restated in C",
+            "ms_per_step": sec * 1e3, "ms_per_forward": sec / layers * 1e3}
 
 
 def run_reference_impl(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    base = cpu_reference_arm(budget_s=max(5.0, min(60.0, 4.0 * (args.steps + args.warmup))))
+    pool_n = args.pool + (args.pool & 1)
+    base = cpu_reference_arm(args.steps, args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_forward"] * POOL,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "decode_gemv_ternary_4096x4096_batch1", "pool": POOL, "l2": "inputs larger than L2 on the GPU arm; CPU arm re-uses one layer"},
+        "config": headline_config(pool_n),
+        "step": f"{SAMPLE_LAYERS} layers of the pool per step (bounded sample); a whole pool would take "
+                f"{base['ms_per_forward'] * pool_n:.1f} ms (extrapolated)",
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -403,9 +433,11 @@ def main():
         e2e = {"value": step_bytes / ge_sec / 1e9, "unit": UNIT, "h2d_bytes_per_step": pool_n * 4 * K_DEC,
                "d2h_bytes_per_step": pool_n * 4 * M_DEC, "ms_per_step": ge_sec * 1e3,
                "note": "kb_linear_group_forward_host: pinned x [pool, K] -> device, one grouped launch, y [pool, M] -> "
-                       "pinned host, synchronise; wall clock around the calls",
-               "per_layer_synchronous_calls": {"value": per_layer["value"], "ms_per_step": per_layer["ms_per_step"],
-                                               "note": per_layer["note"]}}
+                       "pinned host, synchronise; wall clock around the calls"}
+        e2e_drop_in = per_layer
+    else:
+        e2e_drop_in = dict(e2e)
+    e2e_drop_in["us_per_call"] = e2e_drop_in["ms_per_step"] * 1e3 / pool_n
     assert (y_host[0] == y_chk).all(), "host entry point and graph replay disagree"
 
     sharded_extra = sharded_step_extra = None
@@ -426,77 +458,85 @@ def main():
             dist.destroy_process_group()
         return
 
-    per_launch_s = sec_per_step / pool_n
-    achieved = gemv_bytes(M_DEC, K_DEC, 1) / per_launch_s / 1e9
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["src"],
-                "kernel": "gemv_kernel<1,4,2,q8>", "us_per_layer": per_launch_s * 1e6,
-                "note": "step time / layers: launches of independent layers overlap across streams",
-                "frac_of_nominal_8000": achieved / 8000.0}
+    kernel_name = "gemv_stream_kernel<1,grouped>" if os.environ.get("KB_GROUP_IMPL", "1") == "1" else "gemv_group_kernel"
     if grouped:
         # the step IS one launch of the dominant kernel: its launch duration is the step time
         achieved = pool_n * gemv_bytes(M_DEC, K_DEC, 1) / sec_per_step / 1e9
         pre_q = pool_n * gemv_bytes(M_DEC, K_DEC, 1) / group_sec / 1e9
-        roofline.update({"achieved": achieved, "frac": achieved / peaks["hbm_gbs"], "kernel": "gemv_group_kernel<2,true,true,128,5>",
-                         "us_per_launch": sec_per_step * 1e6, "us_per_layer": sec_per_step / pool_n * 1e6,
-                         "frac_of_nominal_8000": achieved / 8000.0,
-                         "note": "one launch per step: algorithmic bytes of the launch / its duration in the timed region "
-                                 "(graph replays held under load for 0.7 s before and after, clocks in `clocks`)",
-                         "prequantised_inputs_short_run": {"achieved": pre_q, "frac": pre_q / peaks["hbm_gbs"],
-                                                           "note": "kb_linear_group_forward_q8 alone, timed without the "
-                                                                   "sustained-load hold (burst clocks)"}})
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["src"], "kernel": kernel_name,
+                    "us_per_launch": sec_per_step * 1e6, "us_per_layer": sec_per_step / pool_n * 1e6,
+                    "frac_of_nominal_8000": achieved / 8000.0,
+                    "note": "one launch per step: algorithmic bytes of the launch / its duration in the timed region "
+                            "(graph replays held under load for 0.7 s before and after, clocks in `clocks`)",
+                    "prequantised_inputs_short_run": {"achieved": pre_q, "frac": pre_q / peaks["hbm_gbs"],
+                                                      "note": "kb_linear_group_forward_q8 alone, timed without the "
+                                                              "sustained-load hold (burst clocks)"}}
+    else:
+        per_launch_s = sec_per_step / pool_n
+        achieved = gemv_bytes(M_DEC, K_DEC, 1) / per_launch_s / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["src"],
+                    "kernel": "gemv_kernel<1,4,2>", "us_per_layer": per_launch_s * 1e6,
+                    "note": "step time / layers: launches of independent layers overlap across streams",
+                    "frac_of_nominal_8000": achieved / 8000.0}
     tpath = os.path.join(ROOT, "profiles", "gemv_traffic.json")
     if os.path.exists(tpath):
         with open(tpath) as f:
             tj = json.load(f)
-            roofline["traffic"] = tj.get("dram_bytes_per_launch_4096x4096_b1")
-            if grouped and tj.get("dram_bytes_per_layer_group_kernel_4096x4096"):
-                # captured on a 40-layer pool; the kernel's traffic grows with the number of layers
-                roofline["traffic"] = tj["dram_bytes_per_layer_group_kernel_4096x4096"] * pool_n
+        per_layer_traffic = tj.get("dram_bytes_per_layer", {}).get(kernel_name if grouped else "gemv_kernel")
+        if per_layer_traffic:
+            # captured on a smaller pool; the kernel's traffic grows in proportion to the number of layers
+            roofline["traffic"] = per_layer_traffic * pool_n
+            roofline["traffic_source"] = tj.get("source")
 
-    cpu = cpu_reference_arm(budget_s=12.0) if world == 1 else None
+    cpu = cpu_reference_arm(steps=40, warmup=2) if world == 1 else None
 
     extras = {}
+    prefill_obj = decoder_obj = chain_obj = None
     if not args.no_extras and world == 1:
         try:
             extras = side_measurements(torch, lib, _cabi, nn, kernels, dev, main_stream, peaks, args, pool, x_dev)
         except Exception as exc:  # side numbers must never cost the headline line
             extras = {"error": repr(exc)}
+        chain_obj = extras.pop("drop_in_chain", None)
+        prefill_obj = extras.pop("prefill", None)
 
     if streams_sec:
         gbs = pool_n * gemv_bytes(M_DEC, K_DEC, 1) / streams_sec / 1e9
         extras[f"gemv_4096x4096_batch1_{n_streams}_streams_2_launches_per_layer"] = {
             "GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "us_per_layer": streams_sec / pool_n * 1e6,
             "launches_per_step": 2 * pool_n}
+    config = headline_config(pool_n)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "decode_gemv_ternary_4096x4096_batch1",
-                   "pool": pool_n, "pool_bytes": pool_n * M_DEC * K_DEC // 4,
-                   "launch": ("one grouped launch (kb_linear_group_forward) over the pool's independent layers, f32 "
-                              "inputs [pool, K] quantised per token in its prologue") if grouped else
-                             f"per layer one quantiser and one GEMV launch, {n_streams} streams",
-                   "streams": 1 if grouped else n_streams,
-                   "l2": "inputs larger than L2 (pool of separately allocated weight copies)",
-                   "quantiser": "absmean per-tensor", "timing": "CUDA events around CUDA-graph replays of the step",
-                   "ranks": "every rank runs the step on its own pool of independent layers, no exchange; "
-                            "the column-sharded layers (with their exchange) are under extra" if world > 1 else None},
-        "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps * world, "clocks": clocks.summary(),
+        "dtype": "int8", "data": "synthetic", "config": config,
+        "step": ("one grouped launch (kb_linear_group_forward) over the pool's independent layers, f32 inputs [pool, K] "
+                 "quantised per token in its prologue; CUDA events around CUDA-graph replays") if grouped else
+                f"per layer one quantiser and one GEMV launch, {n_streams} streams",
+        "ranks": ("every rank runs the step on its own pool of independent layers, no exchange; the layer that needs "
+                  "an exchange is under sharded_projection") if world > 1 else None,
+        "roofline": roofline, "e2e": e2e, "e2e_drop_in": e2e_drop_in,
+        "gpu_launches": launches_per_step * args.steps * world, "clocks": clocks.summary(),
     }
+    if chain_obj:
+        line["drop_in_chain"] = chain_obj
+    if prefill_obj:
+        line["prefill"] = prefill_obj
     if cpu is not None:
         line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
     if world == 1 and not args.no_extras and not args.no_decoder:
         del pool
         torch.cuda.empty_cache()
         try:
-            extras["bitnet_3b_shaped_decoder"] = decoder_measurement(torch, dev, peaks)
+            line["decoder"] = decoder_measurement(torch, dev, peaks)
         except Exception as exc:
-            extras["bitnet_3b_shaped_decoder"] = {"error": repr(exc)}
+            line["decoder"] = {"error": repr(exc)}
     if sharded_step_extra:
         extras["column_sharded_4096_rows_per_rank_step"] = sharded_step_extra
     if sharded_extra:
-        extras["sharded_projection_8192_to_28672"] = sharded_extra
+        line["sharded_projection"] = sharded_extra
     if extras:
         line["extra"] = extras
     print(json.dumps(line), flush=True)
@@ -600,18 +640,23 @@ def column_sharded_step(torch, lib, _cabi, dist, dev, main_stream, rank, local_r
 
 
 def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, peaks):
-    """Sharded-projection configuration of the benchmark specification: ternary K=8192 x M=28672 split by output features over the
-    ranks (strong scaling: the layer is fixed), batch 1 / 8 / 64 / 512, every rank ends with
-    the full y.  Exchange: epilogue peer stores + flag barrier, and NCCL all-gather beside it.
-    A pool of separately allocated copies of the shard (> L2 in total) is cycled."""
-    from kore_b200 import sharded
+    """Sharded-projection configuration of the benchmark specification: ternary K=8192 x M=28672 split by output
+    features over the ranks (strong scaling: the layer is fixed), batch 1 / 8 / 64 / 512, every rank ends with the
+    full y.  Exchange: epilogue peer stores + flag barrier (p2p), and the NCCL all-gather variant beside it.  A pool of
+    separately allocated copies of the shard (> L2 in total) is cycled.  Rank 0 also keeps the unsharded layer: its
+    output is the check (every value of rank 0's gathered y, ==) and its time, measured in the same run, the yardstick."""
+    from kore_b200 import kernels, sharded
 
     m, k = 28672, 8192
     w = (torch.randn((m, k), generator=torch.Generator().manual_seed(5001)) * 0.02).numpy()
     full = nn.BitLinear.new(w, None, 0.3, quantiser="absmean", device=dev.index)  # scale from the full tensor
     del w
     packed, scales = full.packed_weights(), full.scales()
-    full.close()
+    full_pool = None
+    if rank == 0:
+        full_pool = [full] + [nn.BitLinear.from_packed(packed, scales, None, k, m, device=dev.index) for _ in range(3)]
+    else:
+        full.close()
     shard_bytes = (m // world) * k // 4
     copies = max(2, int(160e6 // shard_bytes) + 1)
     copies += copies & 1
@@ -619,9 +664,29 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
     layers = [sharded.ShardedLinear(0, packed, scales, None, k, m, rank, world, device=dev.index, ctx=ctx, dist=dist,
                                     exchange="p2p") for _ in range(copies)]
     sp = stream.cuda_stream
-    out = {"world": world, "shard_copies": copies}
+    link_gbs = 770.0  # measured peer-copy bandwidth per direction on this pool
+    out = {"world": world, "shard_copies": copies, "layer": "ternary 8192 -> 28672, absmean", "exchange": "p2p = epilogue peer "
+           "stores over NVLink + flag barrier; nccl = local slice then all_gather_into_tensor",
+           "matches_unsharded": True}
     for nb in (1, 8, 64, 512):
-        x = torch.from_numpy(gaussian(5002, (nb, k), 1.0)).to(dev)
+        x_host = gaussian(5002, (nb, k), 1.0)
+        x = torch.from_numpy(x_host).to(dev)
+        entry = {}
+        y_full = None
+        if rank == 0:  # the unsharded layer on this GPU, same run
+            y_full = torch.empty((nb, m), dtype=torch.float32, device=dev)
+            xq, sx, sm = kernels.quantize_act_i8(x)
+
+            def step_full():
+                for lay in full_pool:
+                    _cabi.check(lib.kb_linear_forward_q8(lay.handle, xq.data_ptr(), xq.stride(0), sx.data_ptr(), sm.data_ptr(),
+                                                         nb, y_full.data_ptr(), 0, None, _cabi.PATH_AUTO, sp))
+
+            sec_full, _ = time_graph(torch, step_full, 5, 3, stream)
+            entry["us_unsharded_1gpu_same_run"] = sec_full / len(full_pool) * 1e6
+            y_chk = np.zeros((nb, m), np.float32)
+            _cabi.check(lib.kb_linear_forward_host(full.handle, x_host.ctypes.data, nb, k, y_chk.ctypes.data))
+        dist.barrier()
 
         def step_p2p():
             for lay in layers:
@@ -631,8 +696,14 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
         t = torch.tensor([sec / copies], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         per = float(t.item())
-        entry = {"us_per_forward_p2p": per * 1e6, "GB/s": gemv_bytes(m, k, nb) / per / 1e9,
-                 "TOPS": 2.0 * nb * m * k / per / 1e12}
+        y_p2p = layers[-1].forward(x, stream_ptr=sp)  # one more forward whose result is read back
+        stream.synchronize()
+        ok_p2p = bool((y_p2p.cpu().numpy() == y_chk).all()) if rank == 0 else True
+        entry.update({"us_per_forward_p2p": per * 1e6, "GB/s": gemv_bytes(m, k, nb) / per / 1e9,
+                      "frac_of_measured_hbm_one_gpu": gemv_bytes(m, k, nb) / per / 1e9 / peaks["hbm_gbs"],
+                      "TOPS": 2.0 * nb * m * k / per / 1e12,
+                      "ingress_bound_us": (world - 1) / world * nb * m * 4 / (link_gbs * 1e9) * 1e6})
+        layers[-1].forward(x, stream_ptr=sp)  # keep the parity sequence even
         # NCCL all-gather variant (eager launches; collectives are not captured here)
         for lay in layers:
             lay.exchange = "collective"
@@ -640,7 +711,7 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
         dist.barrier()
         with torch.cuda.stream(stream):
             for lay in layers[:2]:
-                lay.forward(x, stream_ptr=sp)
+                y_nccl = lay.forward(x, stream_ptr=sp)
             stream.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
@@ -649,11 +720,16 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
                     lay.forward(x, stream_ptr=sp)
             e1.record(stream)
             stream.synchronize()
+        ok_nccl = bool((y_nccl.cpu().numpy() == y_chk).all()) if rank == 0 else True
         t = torch.tensor([e0.elapsed_time(e1) / 1e3 / (3 * copies)], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         entry["us_per_forward_nccl_allgather"] = float(t.item()) * 1e6
         for lay in layers:
             lay.exchange = "p2p"
+        if rank == 0:
+            entry["matches_unsharded"] = {"p2p": ok_p2p, "nccl": ok_nccl, "compared": f"all {nb} x {m} outputs of rank 0, =="}
+            entry["speedup_vs_unsharded"] = entry["us_unsharded_1gpu_same_run"] / entry["us_per_forward_p2p"]
+            out["matches_unsharded"] = out["matches_unsharded"] and ok_p2p and ok_nccl
         out[f"batch{nb}"] = entry
     ctx.check_status()
     for lay in layers:
@@ -665,7 +741,8 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
 def decoder_measurement(torch, dev, peaks):
     """Decoder configuration of the benchmark specification: BitNet-b1.58-3B-shaped decoder (26 layers, d 3200, 32 heads,
     FFN 8640, vocab 32000), random init, 512-token prompt then 128 greedy steps, batch 1 and 16.
-    Decode steps are CUDA-graph replays timed with CUDA events."""
+    Decode steps are CUDA-graph replays timed with CUDA events.  The roofline object counts the bytes a step must
+    move: packed projections, the dense f32 lm_head, and the f32 KV cache at the mean sequence length."""
     from kore_b200 import decoder
 
     cfg = decoder.DecoderConfig()
@@ -673,18 +750,17 @@ def decoder_measurement(torch, dev, peaks):
     weights = decoder.random_weights(cfg, seed=4000, device=dev.index)
     build_s = time.perf_counter() - t0
     wbytes = cfg.n_layers * (4 * cfg.d_model ** 2 + 3 * cfg.d_model * cfg.d_ff) // 4
-    out = {"weights_build_s": build_s, "packed_weight_bytes_per_token": wbytes,
-           "dense_parts": "embedding and lm_head are f32 torch matmuls", "prompt": 512, "steps": 128}
+    head_bytes = cfg.vocab * cfg.d_model * 4
+    out = {"weights_build_s": build_s, "packed_weight_bytes_per_token": wbytes, "lm_head_bytes": head_bytes,
+           "dense_parts": "embedding and lm_head are dense f32", "prompt": 512, "steps": 128}
     for batch in (1, 16):
         dec = decoder.BitNetDecoder(cfg, weights, batch=batch, device=dev.index)
         g = torch.Generator().manual_seed(4999)
         prompt = torch.randint(0, cfg.vocab, (batch, 512), generator=g).to(dev)
         torch.cuda.synchronize()
-        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        e0.record()
+        e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(2))
         logits = dec.prefill(prompt)
         torch.argmax(logits, dim=1, out=dec.tokens)
-        e1.record()
         torch.cuda.synchronize()
         dec.decode_step()  # builds the graph (one eager step + capture), then first replay
         torch.cuda.synchronize()
@@ -694,19 +770,24 @@ def decoder_measurement(torch, dev, peaks):
             dec.decode_step()
         e2.record()
         torch.cuda.synchronize()
-        prefill_ms = None
         dec_s = e1.elapsed_time(e2) / 1e3
+        mean_len = 512 + 1 + steps / 2
+        kv_bytes = batch * cfg.n_layers * 2 * cfg.d_model * 4 * mean_len
+        step_bytes = wbytes + head_bytes + kv_bytes
+        gbs = step_bytes * steps / dec_s / 1e9
         entry = {"decode_tok_per_s": batch * steps / dec_s, "ms_per_step": dec_s / steps * 1e3,
                  "weight_stream_GB/s": wbytes * steps / dec_s / 1e9,
-                 "frac_of_measured_hbm": wbytes * steps / dec_s / 1e9 / peaks["hbm_gbs"],
-                 "launches_per_step": dec.launches_per_step}
+                 "launches_per_step": dec.launches_per_step,
+                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                              "frac": gbs / peaks["hbm_gbs"], "bytes_per_step": step_bytes,
+                              "bytes": "packed projections + f32 lm_head + f32 KV cache at the mean length"}}
         # prefill timed on a second, fresh pass (buffers already allocated)
-        dec2_e0, dec2_e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        dec2_e0.record()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
         dec.prefill(prompt)
-        dec2_e1.record()
+        p1.record()
         torch.cuda.synchronize()
-        entry["prefill_ms"] = dec2_e0.elapsed_time(dec2_e1)
+        entry["prefill_ms"] = p0.elapsed_time(p1)
         entry["prefill_tok_per_s"] = batch * 512 / (entry["prefill_ms"] / 1e3)
         out[f"batch{batch}"] = entry
         dec.close()
@@ -716,12 +797,14 @@ def decoder_measurement(torch, dev, peaks):
 
 
 def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, pool, x_dev):
-    """Other configurations of the benchmark specification, measured briefly: quaternary GEMV, batch-8 GEMV,
-    prefill GEMM (2048 tokens, 4096 -> 11008 and 11008 -> 4096) with a library int8 GEMM
-    timed beside it as a local ceiling."""
+    """Other configurations of the benchmark specification, measured briefly.  Returns a dict whose entries
+    "drop_in_chain" and "prefill" are lifted to the top level of the JSON line."""
+    from oracle import kbref  # CPU port timed beside the small cases (the checker, never the measured GPU path)
+
     out = {}
     sptr = stream.cuda_stream
     steps, warm = 10, 3
+    hbm = peaks["hbm_gbs"]
 
     # the headline pool as one stream-ordered chain (each layer waits for the previous one)
     y1 = torch.empty((1, M_DEC), dtype=torch.float32, device=dev)
@@ -729,19 +812,21 @@ def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, 
 
     def chain_fused():
         for lay in pool:
-            _cabi.check(lib.kb_linear_forward_ex(lay.handle, x_dev.data_ptr(), 1, K_DEC, y1.data_ptr(), 0, None,
-                                                 _cabi.PATH_GEMV, None, 0, sptr))
+            _cabi.check(lib.kb_linear_forward(lay.handle, x_dev.data_ptr(), 1, y1.data_ptr(), sptr))
 
     def chain_q8():
         for lay in pool:
             _cabi.check(lib.kb_linear_forward_q8(lay.handle, xq.data_ptr(), xq.stride(0), sx.data_ptr(), sumq.data_ptr(), 1,
-                                                 y1.data_ptr(), 0, None, _cabi.PATH_GEMV, sptr))
+                                                 y1.data_ptr(), 0, None, _cabi.PATH_AUTO, sptr))
 
-    for name, fn in (("chain_fused_quantiser_1_launch_per_layer", chain_fused), ("chain_prequantised_input", chain_q8)):
+    chain = {"bound": "hbm", "peak": hbm, "unit": "GB/s",
+             "note": "the pool as ONE dependent chain of kb_linear_forward launches (a decoder's layers), CUDA-graph replays"}
+    for name, fn in (("f32_input", chain_fused), ("prequantised_input", chain_q8)):
         sec, _ = time_graph(torch, fn, steps, warm, stream)
         gbs = len(pool) * gemv_bytes(M_DEC, K_DEC, 1) / sec / 1e9
-        out[f"gemv_4096x4096_batch1_{name}"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                                                 "us_per_layer": sec / len(pool) * 1e6}
+        chain[name] = {"us_per_layer": sec / len(pool) * 1e6, "achieved": gbs, "frac": gbs / hbm}
+    chain["achieved"], chain["frac"] = chain["f32_input"]["achieved"], chain["f32_input"]["frac"]
+    out["drop_in_chain"] = chain
 
     # the 70B-class FFN shape on one GPU (58.7 MB per layer: launch overheads amortise)
     wbig = (torch.randn((28672, 8192), generator=torch.Generator().manual_seed(5001)) * 0.02).numpy()
@@ -749,9 +834,7 @@ def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, 
     bp, bs = big.packed_weights(), big.scales()
     bigpool = [big] + [nn.BitLinear.from_packed(bp, bs, None, 8192, 28672, device=dev.index) for _ in range(3)]
     del wbig
-    # batch 1: dp4a GEMV; 8 and 16: the kernel KB_PATH_AUTO picks (small-batch MMA kernel); 64: tcgen05
-    # tile with the weight operand in tensor memory
-    for nb in (1, 8, 16, 64):
+    for nb in (1, 8, 16, 32, 64):
         xb = torch.from_numpy(gaussian(5002, (nb, 8192), 1.0)).to(dev)
         yb = torch.empty((nb, 28672), dtype=torch.float32, device=dev)
         xqb, sxb, smb = kernels.quantize_act_i8(xb)
@@ -763,11 +846,11 @@ def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, 
 
         sec, _ = time_graph(torch, bigstep, steps, warm, stream)
         gbs = len(bigpool) * gemv_bytes(28672, 8192, nb) / sec / 1e9
-        out[f"gemv_8192x28672_batch{nb}_chain_prequantised"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+        out[f"gemv_8192x28672_batch{nb}_chain_prequantised"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / hbm,
                                                                 "us_per_layer": sec / len(bigpool) * 1e6}
     del bigpool, big
 
-    # quaternary twin of the headline layer, same pool scheme
+    # quaternary twin of the headline layer: per-layer chain, and the pool through the grouped launch
     w = gaussian(2001, (M_DEC, K_DEC), 0.02)
     qproto = nn.QuatLinear.new(w, device=dev.index)
     qp, qs = qproto.packed_weights(), qproto.scales()
@@ -786,11 +869,26 @@ def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, 
 
         sec, _ = time_graph(torch, qstep, steps, warm, stream)
         gbs = len(qpool) * gemv_bytes(M_DEC, K_DEC, nb) / sec / 1e9
-        out[f"quat_gemv_4096x4096_batch{nb}"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                                                  "us_per_launch": sec / len(qpool) * 1e6}
+        out[f"quat_gemv_4096x4096_batch{nb}_chain"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / hbm,
+                                                        "us_per_launch": sec / len(qpool) * 1e6}
+    qgroup = nn.LinearGroup(qpool)
+    xg = torch.from_numpy(gaussian(2002, (1, K_DEC), 1.0)).to(dev).expand(len(qpool), K_DEC).contiguous()
+    yg = torch.empty((len(qpool), M_DEC), dtype=torch.float32, device=dev)
+
+    def qgroup_step():
+        _cabi.check(lib.kb_linear_group_forward(qgroup.handle, xg.data_ptr(), K_DEC, yg.data_ptr(), 0, sptr))
+
+    sec, _ = time_graph(torch, qgroup_step, 20, warm, stream)
+    gbs = len(qpool) * gemv_bytes(M_DEC, K_DEC, 1) / sec / 1e9
+    out["quat_gemv_4096x4096_batch1_grouped_64_layers"] = {"GB/s": gbs, "frac_of_measured_hbm": gbs / hbm,
+                                                            "us_per_launch": sec * 1e6, "note": "256 MiB pool (2x L2)"}
+    qgroup.close()
     del qpool
 
     # prefill GEMM
+    prefill = {"bound": "tensor", "unit": "TOP/s", "peak": 4500.0,
+               "peak_source": "nominal dense int8 (no int8 figure among the measured peaks); 2x the measured bf16 burst "
+                              f"= {2 * peaks['bf16_tflops']:.0f} and a library int8 GEMM timed in the same run are given per shape"}
     for name, m, k, seed in (("up_4096_to_11008", 11008, 4096, 3001), ("down_11008_to_4096", 4096, 11008, 3003)):
         n = 2048
         wg = torch.Generator(device="cpu").manual_seed(seed)
@@ -835,8 +933,81 @@ def side_measurements(torch, lib, _cabi, nn, kernels, dev, stream, peaks, args, 
         except Exception as exc:
             entry["library_int8_gemm_TOPS"] = None
             entry["library_error"] = repr(exc)[:200]
-        out[f"prefill_gemm_2048tok_{name}"] = entry
+        prefill[name] = entry
         del lay
+    worst = min(prefill["up_4096_to_11008"]["gemm_TOPS"], prefill["down_11008_to_4096"]["gemm_TOPS"])
+    prefill["achieved"], prefill["frac"] = worst, worst / prefill["peak"]
+    prefill["kernel"] = "gemm_tc2_kernel (tcgen05.mma.cta_group::2.kind::i8)"
+    prefill["note"] = "achieved = the slower of the two 2048-token shapes, GEMM alone on pre-quantised activations"
+    out["prefill"] = prefill
+
+    # first configuration of the specification: BitLinear(256 -> 128), 32 tokens — too small for a bandwidth
+    # figure, so time only, with the CPU port beside it
+    w1, x1 = gaussian(1001, (128, 256), 0.02), gaussian(1002, (32, 256), 1.0)
+    lay1 = nn.BitLinear.new(w1, None, 0.3, quantiser="absmean", device=dev.index)
+    x1d = torch.from_numpy(x1).to(dev)
+    y1d = torch.empty((32, 128), dtype=torch.float32, device=dev)
+    ws_b = max(int(lib.kb_linear_workspace_bytes(lay1.handle, 32)), 256)
+    ws1 = torch.empty(ws_b + 256, dtype=torch.uint8, device=dev)
+    ws1_ptr = (ws1.data_ptr() + 255) // 256 * 256
+
+    def cfg1():
+        for _ in range(16):
+            _cabi.check(lib.kb_linear_forward_ex(lay1.handle, x1d.data_ptr(), 32, 256, y1d.data_ptr(), 0, None, _cabi.PATH_AUTO,
+                                                 ws1_ptr, ws_b, sptr))
+
+    sec, _ = time_graph(torch, cfg1, steps, warm, stream)
+    p1, s1 = lay1.packed_weights(), lay1.scales()
+    threads = kbref.host_cores()
+    t0 = time.perf_counter()
+    for _ in range(20):
+        kbref.linear_forward(kbref.TERNARY, p1, s1, None, 128, 256, x1, threads=threads)
+    cpu_us = (time.perf_counter() - t0) / 20 * 1e6
+    y_host = np.zeros((32, 128), np.float32)
+    t0 = time.perf_counter()
+    for _ in range(20):
+        _cabi.check(lib.kb_linear_forward_host(lay1.handle, x1.ctypes.data, 32, 256, y_host.ctypes.data))
+    out["bitlinear_256_to_128_32_tokens"] = {"us_per_forward_device": sec / 16 * 1e6,
+                                             "us_per_forward_host_buffers": (time.perf_counter() - t0) / 20 * 1e6,
+                                             "us_per_forward_cpu_port": cpu_us, "cpu_cores": threads}
+
+    # the reference's own benchmark: quat_matmul at square sizes (benches/matmul_bench.rs:42-78), GF/s = 2 n^3 / t
+    sq = {"note": "quaternary, M = N = K; device = resident layer + device buffers (graph replays); host = kb_quat_matmul "
+                  "one-shot with host buffers (uploads and repacks the weights every call, like the reference's signature); "
+                  "cpu = the reference's single-threaded quat_matmul restated in C"}
+    for nsq in (64, 128, 256, 512, 1024):
+        wq = gaussian(60 + nsq, (nsq, nsq), 0.02)
+        bq = gaussian(61 + nsq, (nsq, nsq), 1.0)
+        layq = nn.QuatLinear.new(wq, device=dev.index)
+        pq, sq_scales = layq.packed_weights(), layq.scales()
+        xd = torch.from_numpy(np.ascontiguousarray(bq.T)).to(dev)
+        yd = torch.empty((nsq, nsq), dtype=torch.float32, device=dev)
+        wsb = max(int(lib.kb_linear_workspace_bytes(layq.handle, nsq)), 256)
+        wsq = torch.empty(wsb + 256, dtype=torch.uint8, device=dev)
+        wsq_ptr = (wsq.data_ptr() + 255) // 256 * 256
+
+        def sq_step():
+            for _ in range(8):
+                _cabi.check(lib.kb_linear_forward_ex(layq.handle, xd.data_ptr(), nsq, nsq, yd.data_ptr(), 0, None, _cabi.PATH_AUTO,
+                                                     wsq_ptr, wsb, sptr))
+
+        sec, _ = time_graph(torch, sq_step, steps, warm, stream)
+        dev_s = sec / 8
+        kernels.quat_matmul(pq, sq_scales, bq, nsq, nsq, nsq)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            kernels.quat_matmul(pq, sq_scales, bq, nsq, nsq, nsq)
+        host_s = (time.perf_counter() - t0) / 3
+        reps = 3 if nsq <= 512 else 1
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            kbref.quat_matmul(pq, sq_scales, bq, nsq, nsq, nsq)
+        cpu_s = (time.perf_counter() - t0) / reps
+        fl = 2.0 * nsq ** 3
+        sq[str(nsq)] = {"device_us": dev_s * 1e6, "device_GF/s": fl / dev_s / 1e9, "host_one_shot_us": host_s * 1e6,
+                        "host_one_shot_GF/s": fl / host_s / 1e9, "cpu_port_us": cpu_s * 1e6, "cpu_port_GF/s": fl / cpu_s / 1e9}
+        del layq
+    out["reference_bench_quat_matmul_square"] = sq
     return out
 
 

@@ -7,22 +7,33 @@
 //
 //  * Work unit = 16 weight rows x a contiguous slice of K, owned by ONE warp.  Each warp runs a
 //    private ring of NST stages in shared memory; a stage holds CH = 256 bytes (1024 codes) of
-//    each of the 16 rows.  A stage is filled by 16 one-dimensional bulk copies
-//    (cp.async.bulk.shared::cluster.global, one row each, issued by lanes 0..15 as a single warp
-//    instruction) that complete on the stage's mbarrier.  Copies run NST stages ahead of the
+//    each of the 16 rows.  A stage is filled by 16-byte asynchronous copies (cp.async.cg, global ->
+//    shared without passing through registers or L1; one warp instruction moves 256 contiguous
+//    bytes of two rows) whose completion arrives on the stage's mbarrier
+//    (cp.async.mbarrier.arrive.noinc).  One-dimensional bulk copies (cp.async.bulk, one 256-byte
+//    row piece per request) were measured first and delivered only 2.8 TB/s: the copy engine's
+//    request rate, not HBM, was the limit at that size.  Copies run NST stages ahead of the
 //    arithmetic and across unit boundaries, they are first issued before the activation prologue
 //    and before griddepcontrol.wait, and no CTA-wide barrier exists in the main loop.  With 8
 //    warps x 4 stages an SM keeps 128 KB of weight bytes in flight.
-//  * Arithmetic = mma.sync.m16n8k32 (u8 x s8 -> s32): rows g / g + 8 of the unit are the A rows,
-//    tokens the B columns.  A 32-bit packed word holds 16 codes, element 4j + b in byte b at bits
+//  * Arithmetic, 3..32 tokens = mma.sync.m16n8k32 (u8 x s8 -> s32): rows g / g + 8 of the unit are the A
+//    rows, tokens the B columns.  A 32-bit packed word holds 16 codes, element 4j + b in byte b at bits
 //    2j, so word & (0x03030303 << 2j) is one A-fragment register whose bytes are 4^j x the codes:
 //    one AND per register, no shifts; the four j planes accumulate into four separate
 //    accumulators that are exact multiples of 1, 4, 16, 64 and are divided out once per unit.
 //    The MMA sums over k inside the instruction, so no shuffle reduction exists, and any k
 //    permutation applied to both operands is legal: lane (g, t) takes the 16-byte chunk 4i + t of
 //    rows g and g + 8 at step i, and the activation fragment it needs is the matching 64 bytes
-//    of token g.  Per 512 bytes of weights a warp issues 16 ANDs, 4 MMAs, 1 + 2 shared-memory
-//    loads and a few bookkeeping instructions (the dp4a form needed 72).
+//    of token g.  Per 512 bytes of weights a warp issues 16 ANDs, 4 MMAs and 1 + 4 shared-memory loads.
+//  * Arithmetic, 1..2 tokens = dp4a.  The warp-level int8 MMA of this GPU retires one m16n8k32 per
+//    ~4.5 cycles per SM (measured: 8 useful columns or 1, the cost is the same), which for a single
+//    token is slower than HBM delivers the weights.  Here lane (c = lane % 16, h = lane / 16) owns
+//    16-byte cell c of the stage's rows h, h + 2, ..., h + 14: its 64 activation codes are read
+//    once per stage and stay in registers for the eight rows, the same AND masks feed
+//    dp4a.u32.s32 into four scaled accumulators per row, and the sixteen lanes of a row meet once
+//    per unit in a transposing shuffle reduction (8 shuffles for 8 rows).  Per 512 bytes of weights:
+//    16 ANDs, 16 dp4a, 1.5 shared-memory loads, 1 copy instruction (the register-pipelined
+//    dp4a kernel this replaces needed 72 instructions and was issue-bound).
 //  * Shared-memory layouts are chosen so that every fragment read is conflict-free: stage rows
 //    are CH + 64 bytes apart; activation rows are round_up(Kp, 1024) + 64 bytes apart and every
 //    256-byte block of a row is stored with its 4 x 4 grid of 16-byte cells transposed.
@@ -48,12 +59,11 @@ namespace {
 
 using namespace ptx;
 
-constexpr int SW = 8;                // warps per CTA
 constexpr int CH = 256;              // bytes of one weight row per stage
 constexpr int RS = CH + 64;          // row stride inside a stage
 constexpr int STAGE_BYTES = 16 * RS;
 constexpr int NST_MAX = 6;
-constexpr int BAR_BYTES = 1024;      // SW * NST_MAX barriers, padded so that the stages stay 1 KB aligned
+constexpr int BAR_BYTES = 1024;      // 16 warps x NST_MAX barriers, padded so that the stages stay 1 KB aligned
 constexpr int MAX_ROWS = 32;         // activation rows a CTA may stage (tokens, or layers of a group)
 constexpr long long WAIT_CYCLES = 2000000000ll;
 constexpr int DEV_TIMEOUT_STREAM = 20;  // status code of a stage wait that gave up
@@ -89,14 +99,17 @@ struct StreamParams {
     float *y_more[MAX_PEERS - 1];
     int n_more;
     int mul, off;
-    int units_per_cta;  // groups: virtual row blocks per CTA (a multiple of SW)
+    int units_per_cta;  // groups: virtual row blocks per CTA (a multiple of the warps per CTA)
     int *status;
 };
 
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
+// 16-byte asynchronous copy global -> shared that bypasses L1 and the register file
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// the barrier receives one arrival from this thread once all its earlier cp.async have landed
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
@@ -246,27 +259,30 @@ struct Cursor {
     bool valid;
 };
 
-// NB = blocks of 8 tokens (single layer); GROUPED: one token per layer, NB = 1
-template <int NB, bool GROUPED>
-__global__ void __launch_bounds__(SW * 32, 1) gemv_stream_kernel(const StreamParams p) {
+// NT > 0: dp4a form for NT tokens (1 or 2; GROUPED: one token per layer, NT = 1).
+// NT == 0: MMA form for NB blocks of 8 tokens.  W = most warps per CTA (bounds the registers).
+template <int NB, bool GROUPED, int NT, int W>
+__global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamParams p) {
+    constexpr bool DP = NT > 0;
+    constexpr int NV = DP ? NT : NB * 4;  // values a lane holds when a unit ends
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ float s_sx[MAX_ROWS];
     __shared__ int s_sum[MAX_ROWS];
     __shared__ float red_f[64];
     __shared__ int red_i[64];
 
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sw = blockDim.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int nst = p.nst;
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t bar0 = smem_base + (uint32_t)(warp * NST_MAX * 8);
     const uint32_t stage0 = smem_base + BAR_BYTES + (uint32_t)(warp * nst * STAGE_BYTES);
-    uint8_t *xs = smem + BAR_BYTES + (size_t)SW * nst * STAGE_BYTES;
-    const uint32_t xs_addr = smem_base + BAR_BYTES + (uint32_t)(SW * nst * STAGE_BYTES);
+    uint8_t *xs = smem + BAR_BYTES + (size_t)sw * nst * STAGE_BYTES;
+    const uint32_t xs_addr = smem_base + BAR_BYTES + (uint32_t)(sw * nst * STAGE_BYTES);
     int *part = reinterpret_cast<int *>(xs + (size_t)p.x_rows * p.xs_stride);  // K split only
 
     // ---- this warp's units ----
-    const int ks = p.ks, slice = GROUPED ? 0 : warp % ks, gi = GROUPED ? 0 : warp / ks, gp = SW / ks;
+    const int ks = p.ks, slice = GROUPED ? 0 : warp % ks, gi = GROUPED ? 0 : warp / ks, gp = sw / ks;
     int begin = 0, end = 0, layer0 = 0;
     if (GROUPED) {
         const int total = p.count * p.row_blocks;
@@ -277,7 +293,7 @@ __global__ void __launch_bounds__(SW * 32, 1) gemv_stream_kernel(const StreamPar
     auto load_unit = [&](Cursor &u, int j) {
         u.j = j;
         if (GROUPED) {
-            const int v = begin + warp + j * SW;
+            const int v = begin + warp + j * sw;
             u.valid = v < end;
             u.layer = v / p.row_blocks;
             u.rb = v - u.layer * p.row_blocks;
@@ -292,11 +308,10 @@ __global__ void __launch_bounds__(SW * 32, 1) gemv_stream_kernel(const StreamPar
         }
     };
 
-    // ---- producer: 16 bulk copies fill one stage ----
+    // ---- producer: eight 16-byte asynchronous copies per lane fill one stage ----
     if (lane == 0) {
-        for (int s = 0; s < nst; ++s) mbar_init(bar0 + 8 * s, 1);
+        for (int s = 0; s < nst; ++s) mbar_init(bar0 + 8 * s, 32);  // one arrival per lane and fill
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncwarp();
     Cursor pc;
@@ -309,12 +324,16 @@ __global__ void __launch_bounds__(SW * 32, 1) gemv_stream_kernel(const StreamPar
         const uint32_t s = fills % (uint32_t)nst;
         if (GROUPED && pc.layer != p_layer) { p_layer = pc.layer; p_w2 = p.table[p_layer].w2; }
         const int off = pc.c * CH;
-        const uint32_t bytes = (uint32_t)min(CH, (int)p.row_bytes - off);
-        if (lane == 0) mbar_expect_tx(bar0 + 8 * s, 16u * bytes);
-        __syncwarp();
-        if (lane < 16)
-            bulk_g2s(stage0 + s * STAGE_BYTES + lane * RS, p_w2 + (size_t)(pc.rb * 16 + lane) * p.row_bytes + off, bytes,
-                     bar0 + 8 * s);
+        const int bytes = min(CH, (int)p.row_bytes - off);
+        // 256 cells of 16 bytes (16 rows x CH): cell e = 32 q + lane -> row e / 16, column e % 16, so one warp
+        // instruction copies two rows' 256 contiguous bytes
+        const uint8_t *src = p_w2 + (size_t)(pc.rb * 16 + (lane >> 4)) * p.row_bytes + off + (lane & 15) * 16;
+        const uint32_t dst = stage0 + s * STAGE_BYTES + (lane >> 4) * RS + (lane & 15) * 16;
+        if ((lane & 15) * 16 < bytes) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) cp_async16(dst + q * 2 * RS, src + (size_t)(q * 2) * p.row_bytes);
+        }
+        cp_async_arrive(bar0 + 8 * s);
         ++fills;
         if (++pc.c == pc.c_end) load_unit(pc, pc.j + 1);
     };
@@ -361,27 +380,32 @@ __global__ void __launch_bounds__(SW * 32, 1) gemv_stream_kernel(const StreamPar
     __syncthreads();
 
     // ---- consumer ----
-    int acc[NB][4][4];
+    constexpr int NACC = DP ? 8 * NT * 4 : NB * 16;
+    int acc[NACC];
 #pragma unroll
-    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[nb][j][0] = acc[nb][j][1] = acc[nb][j][2] = acc[nb][j][3] = 0;
+    for (int i = 0; i < NACC; ++i) acc[i] = 0;
 
     Cursor cc;
     load_unit(cc, 0);
-    // per-unit epilogue constants of rows g and g + 8, fetched when the unit starts
+    // epilogue constants of the rows this lane finishes (MMA: rows g and g + 8; dp4a: row h + 2 * ((lane >> 1) & 7)),
+    // fetched when the unit starts
     const LayerRef *ref_tab = p.table;
     LayerRef ref = p.one;
     int ref_layer = GROUPED ? -1 : 0;
     float sw0 = 0.f, sw1 = 0.f, bi0 = 0.f, bi1 = 0.f;
     bool has_bias = false;
+    const int my_row = DP ? (lane >> 4) + 2 * ((lane >> 1) & 7) : g;
     auto fetch_consts = [&](const Cursor &u) {
         if (!u.valid) return;
         if (GROUPED && u.layer != ref_layer) { ref_layer = u.layer; ref = ref_tab[ref_layer]; }
-        const int row = u.rb * 16 + g;  // rows up to m_alloc - 1 are allocated
-        sw0 = ref.sw[row]; sw1 = ref.sw[row + 8];
+        const int row = u.rb * 16 + my_row;  // rows up to m_alloc - 1 are allocated
+        sw0 = ref.sw[row];
+        if (!DP) sw1 = ref.sw[row + 8];
         has_bias = ref.bias != nullptr;
-        if (has_bias) { bi0 = ref.bias[row]; bi1 = ref.bias[row + 8]; }
+        if (has_bias) {
+            bi0 = ref.bias[row];
+            if (!DP) bi1 = ref.bias[row + 8];
+        }
     };
     fetch_consts(cc);
 
@@ -393,31 +417,64 @@ __global__ void __launch_bounds__(SW * 32, 1) gemv_stream_kernel(const StreamPar
         if (ok && !(ok = wait_stage(bar0 + 8 * s, ph))) pc.valid = false;  // gave up: no more copies, no more waits
         if (ok) {
             const int off = cc.c * CH;
-            const int bytes = min(CH, (int)p.row_bytes - off);
-            const int ni = (bytes + 63) >> 6;
-            const uint32_t sg = stage0 + s * STAGE_BYTES + g * RS + t * 16, sh = sg + 8 * RS;
-            const int xrow = GROUPED ? cc.layer - layer0 : g;
-            const uint32_t xa = xs_addr + (uint32_t)(xrow * p.xs_stride) + (uint32_t)(off * 4) + t * 16;
+            if constexpr (DP) {
+                // cell c of rows h, h + 2, ...: stale bytes beyond the row's end meet zero activation codes
+                const int c = lane & 15;
+                const uint32_t xcol = (uint32_t)(off * 4) + 256 * (c >> 2) + 16 * (c & 3);
+                uint32_t xr[NT][16];
 #pragma unroll
-            for (int i = 0; i < CH / 64; ++i) {
-                if (i < ni) {
-                    const uint4 wa = lds128(sg + 64 * i), wb = lds128(sh + 64 * i);
-                    const uint32_t a[4] = {wa.x, wa.y, wa.z, wa.w}, b[4] = {wb.x, wb.y, wb.z, wb.w};
+                for (int tk = 0; tk < NT; ++tk) {
+                    const int xrow = GROUPED ? cc.layer - layer0 : min(tk, p.x_rows - 1);
 #pragma unroll
-                    for (int nb = 0; nb < NB; ++nb) {
-                        const uint32_t xb = xa + (uint32_t)(nb * 8 * p.xs_stride) + 256 * i;
-                        uint4 xv[4];
+                    for (int u = 0; u < 4; ++u) {
+                        const uint4 v = lds128(xs_addr + (uint32_t)(xrow * p.xs_stride) + xcol + 64 * u);
+                        xr[tk][4 * u] = v.x; xr[tk][4 * u + 1] = v.y; xr[tk][4 * u + 2] = v.z; xr[tk][4 * u + 3] = v.w;
+                    }
+                }
+                const uint32_t wb = stage0 + s * STAGE_BYTES + (lane >> 4) * RS + c * 16;
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) xv[u] = lds128(xb + 64 * u);
+                for (int i = 0; i < 8; ++i) {
+                    const uint4 w4 = lds128(wb + 2 * i * RS);
+                    const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
-                        for (int pp = 0; pp < 2; ++pp) {
-                            const uint4 x0 = xv[2 * pp], x1 = xv[2 * pp + 1];
-                            const uint32_t xb0[4] = {x0.x, x0.y, x0.z, x0.w}, xb1[4] = {x1.x, x1.y, x1.z, x1.w};
+                    for (int q = 0; q < 4; ++q)
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const uint32_t mk = 0x03030303u << (2 * j);
-                                mma_u8s8(acc[nb][j], a[2 * pp] & mk, b[2 * pp] & mk, a[2 * pp + 1] & mk, b[2 * pp + 1] & mk,
-                                         xb0[j], xb1[j]);
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t a = ww[q] & (0x03030303u << (2 * j));
+#pragma unroll
+                            for (int tk = 0; tk < NT; ++tk)
+                                acc[(i * NT + tk) * 4 + j] = dp4a_u8s8(a, xr[tk][4 * q + j], acc[(i * NT + tk) * 4 + j]);
+                        }
+                }
+            } else {
+                const int bytes = min(CH, (int)p.row_bytes - off);
+                const int ni = (bytes + 63) >> 6;
+                const uint32_t sg = stage0 + s * STAGE_BYTES + g * RS + t * 16, sh = sg + 8 * RS;
+                // byte offset of this lane's activation cells inside a staged row; the row is token 8 nb + g's
+                // (columns of absent tokens repeat the last staged row: never stored)
+                const uint32_t xcol = (uint32_t)(off * 4) + t * 16;
+#pragma unroll
+                for (int i = 0; i < CH / 64; ++i) {
+                    if (i < ni) {
+                        const uint4 wa = lds128(sg + 64 * i), wb = lds128(sh + 64 * i);
+                        const uint32_t a[4] = {wa.x, wa.y, wa.z, wa.w}, b[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) {
+                            const int xrow = min(nb * 8 + g, p.x_rows - 1);
+                            const uint32_t xb = xs_addr + (uint32_t)(xrow * p.xs_stride) + xcol + 256 * i;
+                            uint4 xv[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) xv[u] = lds128(xb + 64 * u);
+#pragma unroll
+                            for (int pp = 0; pp < 2; ++pp) {
+                                const uint4 x0 = xv[2 * pp], x1 = xv[2 * pp + 1];
+                                const uint32_t xb0[4] = {x0.x, x0.y, x0.z, x0.w}, xb1[4] = {x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const uint32_t mk = 0x03030303u << (2 * j);
+                                    mma_u8s8(*reinterpret_cast<int(*)[4]>(&acc[(nb * 4 + j) * 4]), a[2 * pp] & mk, b[2 * pp] & mk,
+                                             a[2 * pp + 1] & mk, b[2 * pp + 1] & mk, xb0[j], xb1[j]);
+                                }
                             }
                         }
                     }
@@ -428,62 +485,97 @@ __global__ void __launch_bounds__(SW * 32, 1) gemv_stream_kernel(const StreamPar
         fill();
         if (ok) ++cons;
         if (++cc.c == cc.c_end) {
-            // ---- unit finished: combine the four scaled accumulators (exact), K-split partials, epilogue ----
-            int v[NB][4];
+            // ---- unit finished: combine the four scaled accumulators (exact), reduce, K-split partials, epilogue ----
+            int v[NV];
+            if constexpr (DP) {
+                // s[i] = this lane's share of row h + 2 i; the 16 lanes of a half-warp hold the 16 cells of a row.
+                // Transposing reduction: at each step a lane keeps half of its values and receives the partner's
+                // share of them, so 8 values need 4 + 2 + 1 + 1 shuffles; the lane ends with row h + 2 ((lane >> 1) & 7)
 #pragma unroll
-            for (int nb = 0; nb < NB; ++nb)
+                for (int tk = 0; tk < NT; ++tk) {
+                    int sres[8];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    v[nb][r] = acc[nb][0][r] + (acc[nb][1][r] >> 2) + (acc[nb][2][r] >> 4) + (acc[nb][3][r] >> 6);
-                    acc[nb][0][r] = acc[nb][1][r] = acc[nb][2][r] = acc[nb][3][r] = 0;
+                    for (int i = 0; i < 8; ++i) {
+                        const int b = (i * NT + tk) * 4;
+                        sres[i] = acc[b] + (acc[b + 1] >> 2) + (acc[b + 2] >> 4) + (acc[b + 3] >> 6);
+                        acc[b] = acc[b + 1] = acc[b + 2] = acc[b + 3] = 0;
+                    }
+                    const bool h8 = (lane & 8) != 0, h4 = (lane & 4) != 0, h2 = (lane & 2) != 0;
+                    int a4[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        a4[j] = (h8 ? sres[4 + j] : sres[j]) + __shfl_xor_sync(0xffffffffu, h8 ? sres[j] : sres[4 + j], 8);
+                    int b2[2];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        b2[j] = (h4 ? a4[2 + j] : a4[j]) + __shfl_xor_sync(0xffffffffu, h4 ? a4[j] : a4[2 + j], 4);
+                    int d = (h2 ? b2[1] : b2[0]) + __shfl_xor_sync(0xffffffffu, h2 ? b2[0] : b2[1], 2);
+                    d += __shfl_xor_sync(0xffffffffu, d, 1);
+                    v[tk] = d;
                 }
-            bool finisher = true;
-            if (!GROUPED && ks > 1) {
-                int *mine = part + (size_t)((gi * 2 + parity) * ks + slice) * (NB * 4 * 32);
-#pragma unroll
-                for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) mine[(nb * 4 + r) * 32 + lane] = v[nb][r];
-                asm volatile("bar.sync %0, %1;" ::"r"(1 + gi), "r"(ks * 32) : "memory");
-                finisher = slice == 0;
-                if (finisher) {
-                    const int *base = part + (size_t)((gi * 2 + parity) * ks) * (NB * 4 * 32);
-#pragma unroll
-                    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                        for (int r = 0; r < 4; ++r) {
-                            int sum = 0;
-                            for (int q = 0; q < ks; ++q) sum += base[q * (NB * 4 * 32) + (nb * 4 + r) * 32 + lane];
-                            v[nb][r] = sum;
-                        }
-                }
-                parity ^= 1;
-            }
-            if (finisher) {
-                // lane (g, t) holds rows g (r = 0, 1) and g + 8 (r = 2, 3) x tokens 8 nb + 2t (r even), + 1 (r odd)
-                const int row0 = cc.rb * 16 + g;
+            } else {
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
-                        const int row = row0 + (r >> 1) * 8;
-                        const int col = 2 * t + (r & 1);
-                        const int tok = GROUPED ? cc.layer : nb * 8 + col;
-                        const int xr = GROUPED ? cc.layer - layer0 : nb * 8 + col;
-                        const bool live = GROUPED ? col == 0 : tok < p.n;
-                        if (live && row < p.m) {
-                            const int a = p.mul * v[nb][r] - p.off * s_sum[xr];
-                            const size_t o = (size_t)tok * p.ldy + row;
-                            if (p.acc) p.acc[o] = a;
-                            if (p.y) {
-                                float out = dequant_out(a, (r >> 1) ? sw1 : sw0, s_sx[xr], (r >> 1) ? bi1 : bi0, has_bias);
-                                if (p.resid) out = __fadd_rn(out, p.resid[o]);
-                                if (p.relu) out = fmaxf(out, 0.0f);
-                                p.y[o] = out;
-                                for (int q = 0; q < p.n_more; ++q) p.y_more[q][o] = out;  // peer copies over NVLink
-                            }
+                        const int b = nb * 16 + r;
+                        v[nb * 4 + r] = acc[b] + (acc[b + 4] >> 2) + (acc[b + 8] >> 4) + (acc[b + 12] >> 6);
+                        acc[b] = acc[b + 4] = acc[b + 8] = acc[b + 12] = 0;
+                    }
+            }
+            bool finisher = true;
+            if (!GROUPED && ks > 1) {
+                int *mine = part + (size_t)((gi * 2 + parity) * ks + slice) * (NV * 32);
+#pragma unroll
+                for (int i = 0; i < NV; ++i) mine[i * 32 + lane] = v[i];
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + gi), "r"(ks * 32) : "memory");
+                finisher = slice == 0;
+                if (finisher) {
+                    const int *base = part + (size_t)((gi * 2 + parity) * ks) * (NV * 32);
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) {
+                        int sum = 0;
+                        for (int q = 0; q < ks; ++q) sum += base[q * (NV * 32) + i * 32 + lane];
+                        v[i] = sum;
+                    }
+                }
+                parity ^= 1;
+            }
+            if (finisher) {
+                auto store = [&](int value, int row, int tok, int xr_, float sw_, float bi_) {
+                    const int a = p.mul * value - p.off * s_sum[xr_];
+                    const size_t o = (size_t)tok * p.ldy + row;
+                    if (p.acc) p.acc[o] = a;
+                    if (p.y) {
+                        float out = dequant_out(a, sw_, s_sx[xr_], bi_, has_bias);
+                        if (p.resid) out = __fadd_rn(out, p.resid[o]);
+                        if (p.relu) out = fmaxf(out, 0.0f);
+                        p.y[o] = out;
+                        for (int q = 0; q < p.n_more; ++q) p.y_more[q][o] = out;  // peer copies over NVLink
+                    }
+                };
+                if constexpr (DP) {
+                    const int row = cc.rb * 16 + my_row;
+                    if ((lane & 1) == 0 && row < p.m) {
+#pragma unroll
+                        for (int tk = 0; tk < NT; ++tk) {
+                            const int tok = GROUPED ? cc.layer : tk;
+                            const int xr_ = GROUPED ? cc.layer - layer0 : tk;
+                            if (GROUPED || tk < p.n) store(v[tk], row, tok, xr_, sw0, bi0);
                         }
                     }
+                } else {
+                    // lane (g, t) holds rows g (r = 0, 1) and g + 8 (r = 2, 3) x tokens 8 nb + 2t (r even), + 1 (r odd)
+                    const int row0 = cc.rb * 16 + g;
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) {
+                            const int row = row0 + (r >> 1) * 8;
+                            const int tok = nb * 8 + 2 * t + (r & 1);
+                            if (tok < p.n && row < p.m) store(v[nb * 4 + r], row, tok, tok, (r >> 1) ? sw1 : sw0, (r >> 1) ? bi1 : bi0);
+                        }
+                }
             }
             load_unit(cc, cc.j + 1);
             fetch_consts(cc);
@@ -502,43 +594,81 @@ __global__ void __launch_bounds__(SW * 32, 1) gemv_stream_kernel(const StreamPar
 
 size_t xs_stride_for(size_t kp) { return (kp + 1023) / 1024 * 1024 + 64; }
 
-// stages per warp that fit beside `x_rows` staged activation rows and the K-split scratch (0: does not fit)
-int stages_that_fit(size_t kp, int x_rows, size_t part_bytes) {
-    const size_t budget = 224 * 1024;  // leaves room for the static arrays
-    const size_t fixed = BAR_BYTES + (size_t)x_rows * xs_stride_for(kp) + part_bytes;
-    if (fixed + (size_t)SW * 2 * STAGE_BYTES > budget) return 0;
-    size_t nst = (budget - fixed) / ((size_t)SW * STAGE_BYTES);
-    static const int env_nst = [] { const char *v = getenv("KB_STREAM_NST"); return v && *v ? atoi(v) : 0; }();
-    size_t cap = 4;
-    if (env_nst >= 2 && env_nst <= NST_MAX) cap = (size_t)env_nst;
-    return (int)(nst > cap ? cap : nst);
+int env_int(const char *name, int dflt) {
+    const char *v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
 }
 
-template <int NB, bool GROUPED>
-int launch_stream(const StreamParams &p, int device, int grid, size_t smem, cudaStream_t stream) {
-    auto kern = gemv_stream_kernel<NB, GROUPED>;
+// launch shape: warps per CTA and stages per warp that fit beside `x_rows` staged activation rows and the
+// K-split scratch.  Prefers many warps (the arithmetic of a warp is serial; more warps overlap more of it with
+// the copies) with at least two stages each.  warps == 0: does not fit.
+struct Shape { int warps, nst; };
+Shape pick_shape(size_t kp, int x_rows, size_t part_per_warp, int max_warps) {
+    static const int env_w = env_int("KB_STREAM_WARPS", 0), env_nst = env_int("KB_STREAM_NST", 0);
+    const size_t budget = 224 * 1024;  // leaves room for the static arrays
+    const size_t fixed = BAR_BYTES + (size_t)x_rows * xs_stride_for(kp);
+    int w = max_warps;
+    if (env_w >= 4 && env_w <= max_warps && env_w % 4 == 0) w = env_w;
+    for (; w >= 4; w -= 4) {
+        const size_t need2 = fixed + (size_t)w * (part_per_warp + 2 * STAGE_BYTES);
+        if (need2 > budget) continue;
+        size_t nst = (budget - fixed - (size_t)w * part_per_warp) / ((size_t)w * STAGE_BYTES);
+        size_t cap = (env_nst >= 2 && env_nst <= NST_MAX) ? (size_t)env_nst : 4;
+        return Shape{w, (int)(nst > cap ? cap : nst)};
+    }
+    return Shape{0, 0};
+}
+
+template <int NB, bool GROUPED, int NT, int W>
+int launch_stream(const StreamParams &p, int device, int grid, int warps, size_t smem, cudaStream_t stream) {
+    auto kern = gemv_stream_kernel<NB, GROUPED, NT, W>;
     if (int rc = set_dyn_smem_once(reinterpret_cast<const void *>(kern), device, 227 * 1024 - 2048, "stream smem attribute")) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
-    cfg.blockDim = dim3(SW * 32, 1, 1);
+    cfg.blockDim = dim3((unsigned)(warps * 32), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    static const bool pdl = [] { const char *v = getenv("KB_GEMV_PDL"); return !(v && *v == '0'); }();
+    static const bool pdl = env_int("KB_GEMV_PDL", 1) != 0;
     cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "stream launch");
+}
+
+// values a lane parks in shared memory per unit when K is split
+int nv_for(size_t n) { return n <= 2 ? (int)n : (n <= 8 ? 4 : (n <= 16 ? 8 : 16)); }
+// most warps per CTA of the kernel instance that serves n tokens (register bound)
+int max_warps_for(size_t n) { return n == 2 ? 12 : (n <= 8 ? 16 : (n <= 16 ? 12 : 8)); }
+
+struct SinglePlan { int ks, warps, nst; size_t part_bytes; };
+// launch shape of a single layer (warps == 0: does not fit)
+SinglePlan plan_single(const Linear *lin, size_t n) {
+    const int nchunks = (int)((lin->row_bytes + CH - 1) / CH);
+    const int row_blocks = (int)((lin->m + 15) / 16);
+    const int sms = sm_count(lin->device);
+    static const int env_ks = env_int("KB_STREAM_KS", 0);
+    const int maxw = max_warps_for(n);
+    // K split: enough (row block, slice) units to give every warp of every SM one
+    int ks = 1;
+    while (ks < 8 && ks * 2 <= nchunks && (long long)row_blocks * ks < (long long)sms * maxw) ks *= 2;
+    if ((env_ks == 1 || env_ks == 2 || env_ks == 4 || env_ks == 8) && env_ks <= nchunks) ks = env_ks;
+    for (;; ks /= 2) {  // a smaller K split needs less scratch
+        const size_t part_per_warp = ks > 1 ? (size_t)2 * nv_for(n) * 32 * 4 : 0;
+        Shape sh = pick_shape(lin->kp, (int)n, part_per_warp, maxw);
+        while (sh.warps && sh.warps % ks) sh.warps -= 4;  // whole groups of ks warps
+        if (sh.warps >= ks && sh.warps > 0 && sh.nst >= 2) return SinglePlan{ks, sh.warps, sh.nst, (size_t)sh.warps * part_per_warp};
+        if (ks == 1) return SinglePlan{1, 0, 0, 0};
+    }
 }
 
 }  // namespace
 
 bool gemv_stream_supports(const Linear *lin, size_t n) {
     if (n < 1 || n > 32 || lin->kp > 80000) return false;  // 64 * 3 * 127 * K must stay below 2^31
-    const int nb = n <= 8 ? 1 : (n <= 16 ? 2 : 4);
-    return stages_that_fit(lin->kp, nb * 8, (size_t)SW * 2 * nb * 512) >= 2;
+    return plan_single(lin, n).warps > 0;
 }
 
 int launch_gemv_stream(const FwdArgs &a, cudaStream_t stream) {
@@ -552,7 +682,7 @@ int launch_gemv_stream(const FwdArgs &a, cudaStream_t stream) {
         if ((reinterpret_cast<uintptr_t>(a.xq) & 15) || (a.ldq % 16) || a.ldq < L->kp)
             return fail(KB_ERR_INVALID, "gemv: xq must be 16-byte aligned with ldq >= %zu and ldq %% 16 == 0", L->kp);
     }
-    const int nb = a.n <= 8 ? 1 : (a.n <= 16 ? 2 : 4);
+    const SinglePlan plan = plan_single(L, a.n);
     StreamParams p = {};
     p.table = nullptr;
     p.one = LayerRef{L->w2, L->scales, L->bias};
@@ -561,17 +691,10 @@ int launch_gemv_stream(const FwdArgs &a, cudaStream_t stream) {
     p.row_bytes = L->row_bytes;
     p.row_blocks = (int)((L->m + 15) / 16);
     p.nchunks = (int)((L->row_bytes + CH - 1) / CH);
-    const int sms = sm_count(L->device);
-    // K split: enough (row block, slice) units to give every warp of every SM one
-    int ks = 1;
-    static const int env_ks = [] { const char *v = getenv("KB_STREAM_KS"); return v && *v ? atoi(v) : 0; }();
-    while (ks < SW && ks * 2 <= p.nchunks && (long long)p.row_blocks * ks < (long long)sms * SW) ks *= 2;
-    if (env_ks == 1 || env_ks == 2 || env_ks == 4 || env_ks == 8) ks = env_ks <= p.nchunks ? env_ks : ks;
-    p.ks = ks;
-    const size_t part_bytes = ks > 1 ? (size_t)SW * 2 * nb * 512 : 0;
-    p.x_rows = nb * 8;
+    p.ks = plan.ks;
+    p.x_rows = (int)a.n;
     p.xs_stride = (int)xs_stride_for(L->kp);
-    p.nst = stages_that_fit(L->kp, p.x_rows, part_bytes);
+    p.nst = plan.nst;
     p.x = a.x; p.ldx = L->k;
     p.x_vec4 = a.x && (L->k % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
     p.xq = a.xq; p.ldq = a.ldq; p.sx = a.sx; p.sumq = a.sumq;
@@ -584,13 +707,16 @@ int launch_gemv_stream(const FwdArgs &a, cudaStream_t stream) {
     p.mul = L->mul; p.off = L->off;
     p.units_per_cta = 0;
     p.status = L->dev_status;
-    const int gp = SW / ks;
+    const int gp = plan.warps / plan.ks;
     int grid = (p.row_blocks + gp - 1) / gp;
+    const int sms = sm_count(L->device);
     if (grid > sms) grid = sms;
-    const size_t smem = BAR_BYTES + (size_t)SW * p.nst * STAGE_BYTES + (size_t)p.x_rows * p.xs_stride + part_bytes;
-    if (nb == 1) return launch_stream<1, false>(p, L->device, grid, smem, stream);
-    if (nb == 2) return launch_stream<2, false>(p, L->device, grid, smem, stream);
-    return launch_stream<4, false>(p, L->device, grid, smem, stream);
+    const size_t smem = BAR_BYTES + (size_t)plan.warps * p.nst * STAGE_BYTES + (size_t)p.x_rows * p.xs_stride + plan.part_bytes;
+    if (a.n == 1) return launch_stream<1, false, 1, 16>(p, L->device, grid, plan.warps, smem, stream);
+    if (a.n == 2) return launch_stream<1, false, 2, 12>(p, L->device, grid, plan.warps, smem, stream);
+    if (a.n <= 8) return launch_stream<1, false, 0, 16>(p, L->device, grid, plan.warps, smem, stream);
+    if (a.n <= 16) return launch_stream<2, false, 0, 12>(p, L->device, grid, plan.warps, smem, stream);
+    return launch_stream<4, false, 0, 8>(p, L->device, grid, plan.warps, smem, stream);
 }
 
 int launch_group_stream(const GroupArgs &a, cudaStream_t stream) {
@@ -608,21 +734,22 @@ int launch_group_stream(const GroupArgs &a, cudaStream_t stream) {
     // one CTA per SM; grown (shorter ranges touch fewer layers) until a CTA's activation rows fit
     long long grid = sm_count(a.device);
     long long per_cta = 0, staged = 0;
-    int nst = 0;
+    Shape sh = {0, 0};
     for (;;) {
+        // staged rows for the largest CTA shape first; the warp count only rounds the range
         per_cta = (total + grid - 1) / grid;
-        per_cta = (per_cta + SW - 1) / SW * SW;
-        staged = (per_cta + p.row_blocks - 2) / p.row_blocks + 1;
+        staged = (per_cta + 15 + p.row_blocks - 2) / p.row_blocks + 1;
         if (staged > (long long)a.count) staged = (long long)a.count;
-        nst = staged <= MAX_ROWS ? stages_that_fit(a.kp, (int)staged, 0) : 0;
-        if (nst >= 2 || per_cta <= SW) break;
+        sh = staged <= MAX_ROWS ? pick_shape(a.kp, (int)staged, 0, 16) : Shape{0, 0};
+        if ((sh.warps > 0 && sh.nst >= 2) || per_cta <= 16) break;
         grid *= 2;
     }
-    if (nst < 2)
+    if (sh.warps == 0 || sh.nst < 2)
         return fail(KB_ERR_UNSUPPORTED, "group: %lld activation rows of %zu bytes per CTA do not fit in shared memory", staged,
                     xs_stride_for(a.kp));
+    per_cta = (per_cta + sh.warps - 1) / sh.warps * sh.warps;
     grid = (total + per_cta - 1) / per_cta;
-    p.nst = nst;
+    p.nst = sh.nst;
     p.x = a.x; p.ldx = a.ldx;
     p.x_vec4 = a.x && (a.k % 4 == 0) && (a.ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
     p.xq = a.xq; p.ldq = a.ldq; p.sx = a.sx; p.sumq = a.sumq;
@@ -633,8 +760,8 @@ int launch_group_stream(const GroupArgs &a, cudaStream_t stream) {
     p.mul = a.mul; p.off = a.off;
     p.units_per_cta = (int)per_cta;
     p.status = a.status;
-    const size_t smem = BAR_BYTES + (size_t)SW * p.nst * STAGE_BYTES + (size_t)p.x_rows * p.xs_stride;
-    return launch_stream<1, true>(p, a.device, (int)grid, smem, stream);
+    const size_t smem = BAR_BYTES + (size_t)sh.warps * p.nst * STAGE_BYTES + (size_t)p.x_rows * p.xs_stride;
+    return launch_stream<1, true, 1, 16>(p, a.device, (int)grid, sh.warps, smem, stream);
 }
 
 }  // namespace kb

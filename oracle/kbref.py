@@ -102,6 +102,18 @@ def max_threads() -> int:
     return int(lib().kbref_max_threads())
 
 
+def host_cores() -> int:
+    """Cores this process may run on.  Every entry point here takes its thread count as an
+    argument (``num_threads`` clauses in kbref.c), so passing this value uses all of them even
+    where a launcher has set OMP_NUM_THREADS=1 for its workers (torch.distributed.run does)."""
+    import os
+
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def k_packed(kind: int, k: int) -> int:
     return (k + 4) // 5 if kind == TERNARY else (k + 3) // 4
 

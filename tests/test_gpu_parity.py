@@ -159,6 +159,8 @@ def test_forward_bit_exact(torch, kb, path, kind, quantiser, m, k, n):
         pytest.skip("decode kernel is exercised up to a few token groups")
     if path in ("gemv_mma", "gemv_stream") and n > 32:
         pytest.skip("small-batch kernels take up to 32 tokens")
+    if path == "gemv_stream" and n > 8 and k > 8192:
+        pytest.skip("more than 8 tokens of K > 8192 do not fit in the streaming kernel's shared memory")
     w = cases.gaussian(1000 + m + k, (m, k), 0.02)
     packed, scales = cases.make_weights(kind, quantiser, w)
     bias = cases.gaussian(3, (m,), 0.1) if (m + n) % 2 else None
