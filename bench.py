@@ -261,7 +261,7 @@ def main():
     ap.add_argument("--launch", default="grouped", choices=["grouped", "streams"],
                     help="headline step: one grouped launch over the pool of independent layers (default), or one "
                          "quantiser + one GEMV launch per layer spread over --streams streams")
-    ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "small_batch", "medium_batch", "prefill_up", "prefill_down"],
+    ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "group_4096", "small_batch", "medium_batch", "prefill_up", "prefill_down"],
                     help="run one small case and print its own JSON line (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -458,7 +458,7 @@ def main():
             dist.destroy_process_group()
         return
 
-    kernel_name = "gemv_stream_kernel<1,grouped>" if os.environ.get("KB_GROUP_IMPL", "1") == "1" else "gemv_group_kernel"
+    kernel_name = "gemv_stream_kernel<grouped,dp4a>"
     if grouped:
         # the step IS one launch of the dominant kernel: its launch duration is the step time
         achieved = pool_n * gemv_bytes(M_DEC, K_DEC, 1) / sec_per_step / 1e9
@@ -547,7 +547,8 @@ def main():
 
 def single_case(torch, lib, _cabi, nn, kernels, dev, args):
     """One kernel on one small case, a handful of eager launches: the command profiled with ncu."""
-    shapes = {"gemv_big": (28672, 8192, 1, 3), "gemv_4096": (4096, 4096, 1, 40), "small_batch": (28672, 8192, 16, 3),
+    shapes = {"gemv_big": (28672, 8192, 1, 3), "gemv_4096": (4096, 4096, 1, 40), "group_4096": (4096, 4096, 1, 40),
+              "small_batch": (28672, 8192, 16, 3),
               "medium_batch": (28672, 8192, 64, 3),
               "prefill_up": (11008, 4096, 2048, 1), "prefill_down": (4096, 11008, 2048, 1)}
     m, k, n, copies = shapes[args.only]
@@ -567,6 +568,14 @@ def single_case(torch, lib, _cabi, nn, kernels, dev, args):
             _cabi.check(lib.kb_linear_forward_q8(lay.handle, xq.data_ptr(), xq.stride(0), sx.data_ptr(), sumq.data_ptr(), n,
                                                  y.data_ptr(), 0, None, path, sp))
 
+    if args.only == "group_4096":  # the headline launch on a 40-layer pool (160 MiB > L2): one launch per step
+        group = nn.LinearGroup(layers)
+        xg = x.expand(copies, k).contiguous()
+        yg = torch.empty((copies, m), dtype=torch.float32, device=dev)
+
+        def once():  # noqa: F811
+            _cabi.check(lib.kb_linear_group_forward(group.handle, xg.data_ptr(), k, yg.data_ptr(), 0, sp))
+
     for _ in range(max(1, args.warmup)):
         once()
     torch.cuda.synchronize()
@@ -577,6 +586,11 @@ def single_case(torch, lib, _cabi, nn, kernels, dev, args):
     e1.record()
     torch.cuda.synchronize()
     per = e0.elapsed_time(e1) / 1e3 / (args.steps * copies)
+    if args.only == "group_4096":
+        per *= copies  # one launch covers all copies
+        print(json.dumps({"case": args.only, "m": m, "k": k, "layers": copies, "us_per_launch": per * 1e6,
+                          "GB/s": copies * gemv_bytes(m, k, 1) / per / 1e9}), flush=True)
+        return
     print(json.dumps({"case": args.only, "m": m, "k": k, "n": n, "copies": copies, "us_per_launch": per * 1e6,
                       "GB/s": gemv_bytes(m, k, n) / per / 1e9, "TOPS": 2.0 * m * k * n / per / 1e12}), flush=True)
 

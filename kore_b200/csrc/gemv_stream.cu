@@ -99,21 +99,24 @@ struct StreamParams {
     float *y_more[MAX_PEERS - 1];
     int n_more;
     int mul, off;
-    int units_per_cta;  // groups: virtual row blocks per CTA (a multiple of the warps per CTA)
+    int units_per_cta;  // groups: virtual row blocks per CTA
     int *status;
 };
 
 // 16-byte asynchronous copy global -> shared that bypasses L1 and the register file
+template <int DST_OFF>
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0 + %2], [%1], 16;" ::"r"(dst), "l"(src), "n"(DST_OFF) : "memory");
 }
 // the barrier receives one arrival from this thread once all its earlier cp.async have landed
 __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
+// 16-byte shared-memory read at base + a compile-time offset (the offset folds into the instruction)
+template <int OFF>
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4 + %5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
     return v;
 }
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -290,22 +293,35 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
         end = min(begin + p.units_per_cta, total);
         layer0 = begin / p.row_blocks;
     }
-    auto load_unit = [&](Cursor &u, int j) {
-        u.j = j;
+    // a warp's units are visited in order; (layer, rb) follow without divisions
+    const int c_first = GROUPED ? 0 : slice * p.nchunks / ks;  // every slice is non-empty: ks <= nchunks
+    const int c_last = GROUPED ? p.nchunks : (slice + 1) * p.nchunks / ks;
+    auto first_unit = [&](Cursor &u) {
+        u.j = 0;
         if (GROUPED) {
-            const int v = begin + warp + j * sw;
+            const int v = begin + warp;
             u.valid = v < end;
             u.layer = v / p.row_blocks;
             u.rb = v - u.layer * p.row_blocks;
-            u.c = 0;
-            u.c_end = p.nchunks;
         } else {
-            u.rb = ((int)blockIdx.x * gp + gi) + j * ((int)gridDim.x * gp);
+            u.rb = (int)blockIdx.x * gp + gi;
             u.valid = u.rb < p.row_blocks;
             u.layer = 0;
-            u.c = slice * p.nchunks / ks;          // every slice is non-empty: ks <= nchunks
-            u.c_end = (slice + 1) * p.nchunks / ks;
         }
+        u.c = c_first;
+        u.c_end = c_last;
+    };
+    auto next_unit = [&](Cursor &u) {
+        ++u.j;
+        if (GROUPED) {
+            u.rb += sw;
+            while (u.rb >= p.row_blocks) { u.rb -= p.row_blocks; ++u.layer; }
+            u.valid = begin + warp + u.j * sw < end;
+        } else {
+            u.rb += (int)gridDim.x * gp;
+            u.valid = u.rb < p.row_blocks;
+        }
+        u.c = c_first;
     };
 
     // ---- producer: eight 16-byte asynchronous copies per lane fill one stage ----
@@ -315,27 +331,41 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
     }
     __syncwarp();
     Cursor pc;
-    load_unit(pc, 0);
+    first_unit(pc);
     const uint8_t *p_w2 = GROUPED ? nullptr : p.one.w2;
     int p_layer = -1;
-    uint32_t fills = 0;
+    uint32_t fills = 0, fs = 0;  // fills issued, and the stage the next one goes to
+    // 256 cells of 16 bytes per stage (16 rows x CH): cell e = 32 q + lane -> row e / 16, column e % 16, so one
+    // warp instruction copies two rows' 256 contiguous bytes.  p_src = this lane's first cell of the current unit
+    const uint32_t lane_dst = stage0 + (lane >> 4) * RS + (lane & 15) * 16;
+    const int lane_col = (lane & 15) * 16;
+    const size_t two_rows = 2 * p.row_bytes;
+    const uint8_t *p_src = nullptr;
+    auto unit_src = [&]() {
+        if (!pc.valid) return;
+        if (GROUPED && pc.layer != p_layer) { p_layer = pc.layer; p_w2 = p.table[p_layer].w2; }
+        p_src = p_w2 + (size_t)(pc.rb * 16 + (lane >> 4)) * p.row_bytes + lane_col;
+    };
+    unit_src();
     auto fill = [&]() {
         if (!pc.valid) return;
-        const uint32_t s = fills % (uint32_t)nst;
-        if (GROUPED && pc.layer != p_layer) { p_layer = pc.layer; p_w2 = p.table[p_layer].w2; }
+        const uint32_t dst = lane_dst + fs * STAGE_BYTES, bar = bar0 + 8 * fs;
+        fs = fs + 1 == (uint32_t)nst ? 0 : fs + 1;
         const int off = pc.c * CH;
-        const int bytes = min(CH, (int)p.row_bytes - off);
-        // 256 cells of 16 bytes (16 rows x CH): cell e = 32 q + lane -> row e / 16, column e % 16, so one warp
-        // instruction copies two rows' 256 contiguous bytes
-        const uint8_t *src = p_w2 + (size_t)(pc.rb * 16 + (lane >> 4)) * p.row_bytes + off + (lane & 15) * 16;
-        const uint32_t dst = stage0 + s * STAGE_BYTES + (lane >> 4) * RS + (lane & 15) * 16;
-        if ((lane & 15) * 16 < bytes) {
-#pragma unroll
-            for (int q = 0; q < 8; ++q) cp_async16(dst + q * 2 * RS, src + (size_t)(q * 2) * p.row_bytes);
+        if (lane_col < (int)p.row_bytes - off) {  // cells beyond the row's end are not copied (they meet zero codes)
+            const uint8_t *src = p_src + off;
+            cp_async16<0 * 2 * RS>(dst, src); src += two_rows;
+            cp_async16<1 * 2 * RS>(dst, src); src += two_rows;
+            cp_async16<2 * 2 * RS>(dst, src); src += two_rows;
+            cp_async16<3 * 2 * RS>(dst, src); src += two_rows;
+            cp_async16<4 * 2 * RS>(dst, src); src += two_rows;
+            cp_async16<5 * 2 * RS>(dst, src); src += two_rows;
+            cp_async16<6 * 2 * RS>(dst, src); src += two_rows;
+            cp_async16<7 * 2 * RS>(dst, src);
         }
-        cp_async_arrive(bar0 + 8 * s);
+        cp_async_arrive(bar);
         ++fills;
-        if (++pc.c == pc.c_end) load_unit(pc, pc.j + 1);
+        if (++pc.c == pc.c_end) { next_unit(pc); unit_src(); }
     };
     for (int s = 0; s < nst; ++s) fill();
 
@@ -386,7 +416,7 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
     for (int i = 0; i < NACC; ++i) acc[i] = 0;
 
     Cursor cc;
-    load_unit(cc, 0);
+    first_unit(cc);
     // epilogue constants of the rows this lane finishes (MMA: rows g and g + 8; dp4a: row h + 2 * ((lane >> 1) & 7)),
     // fetched when the unit starts
     const LayerRef *ref_tab = p.table;
@@ -409,11 +439,11 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
     };
     fetch_consts(cc);
 
-    uint32_t cons = 0;
+    uint32_t cons = 0, cs = 0, cph = 0;  // stages consumed, the next one's index and barrier phase
     int parity = 0;
     bool ok = true;
     while (cc.valid) {
-        const uint32_t s = cons % (uint32_t)nst, ph = (cons / (uint32_t)nst) & 1u;
+        const uint32_t s = cs, ph = cph;
         if (ok && !(ok = wait_stage(bar0 + 8 * s, ph))) pc.valid = false;  // gave up: no more copies, no more waits
         if (ok) {
             const int off = cc.c * CH;
@@ -425,16 +455,21 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
 #pragma unroll
                 for (int tk = 0; tk < NT; ++tk) {
                     const int xrow = GROUPED ? cc.layer - layer0 : min(tk, p.x_rows - 1);
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const uint4 v = lds128(xs_addr + (uint32_t)(xrow * p.xs_stride) + xcol + 64 * u);
-                        xr[tk][4 * u] = v.x; xr[tk][4 * u + 1] = v.y; xr[tk][4 * u + 2] = v.z; xr[tk][4 * u + 3] = v.w;
-                    }
+                    const uint32_t xb = xs_addr + (uint32_t)(xrow * p.xs_stride) + xcol;
+                    const uint4 v0 = lds128<0>(xb), v1 = lds128<64>(xb), v2 = lds128<128>(xb), v3 = lds128<192>(xb);
+                    xr[tk][0] = v0.x; xr[tk][1] = v0.y; xr[tk][2] = v0.z; xr[tk][3] = v0.w;
+                    xr[tk][4] = v1.x; xr[tk][5] = v1.y; xr[tk][6] = v1.z; xr[tk][7] = v1.w;
+                    xr[tk][8] = v2.x; xr[tk][9] = v2.y; xr[tk][10] = v2.z; xr[tk][11] = v2.w;
+                    xr[tk][12] = v3.x; xr[tk][13] = v3.y; xr[tk][14] = v3.z; xr[tk][15] = v3.w;
                 }
-                const uint32_t wb = stage0 + s * STAGE_BYTES + (lane >> 4) * RS + c * 16;
+                const uint32_t wb = lane_dst + s * STAGE_BYTES;  // this lane's copy cell is also its first read cell
+                uint4 wrow[8];
+                wrow[0] = lds128<0 * 2 * RS>(wb); wrow[1] = lds128<1 * 2 * RS>(wb); wrow[2] = lds128<2 * 2 * RS>(wb);
+                wrow[3] = lds128<3 * 2 * RS>(wb); wrow[4] = lds128<4 * 2 * RS>(wb); wrow[5] = lds128<5 * 2 * RS>(wb);
+                wrow[6] = lds128<6 * 2 * RS>(wb); wrow[7] = lds128<7 * 2 * RS>(wb);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const uint4 w4 = lds128(wb + 2 * i * RS);
+                    const uint4 w4 = wrow[i];
                     const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
@@ -456,7 +491,7 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
 #pragma unroll
                 for (int i = 0; i < CH / 64; ++i) {
                     if (i < ni) {
-                        const uint4 wa = lds128(sg + 64 * i), wb = lds128(sh + 64 * i);
+                        const uint4 wa = lds128<0>(sg + 64 * i), wb = lds128<0>(sh + 64 * i);
                         const uint32_t a[4] = {wa.x, wa.y, wa.z, wa.w}, b[4] = {wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
                         for (int nb = 0; nb < NB; ++nb) {
@@ -464,7 +499,7 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
                             const uint32_t xb = xs_addr + (uint32_t)(xrow * p.xs_stride) + xcol + 256 * i;
                             uint4 xv[4];
 #pragma unroll
-                            for (int u = 0; u < 4; ++u) xv[u] = lds128(xb + 64 * u);
+                            for (int u = 0; u < 4; ++u) xv[u] = lds128<0>(xb + 64 * u);
 #pragma unroll
                             for (int pp = 0; pp < 2; ++pp) {
                                 const uint4 x0 = xv[2 * pp], x1 = xv[2 * pp + 1];
@@ -483,7 +518,10 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
         }
         __syncwarp();  // every lane has read the stage: it can be refilled
         fill();
-        if (ok) ++cons;
+        if (ok) {
+            ++cons;
+            if (++cs == (uint32_t)nst) { cs = 0; cph ^= 1u; }
+        }
         if (++cc.c == cc.c_end) {
             // ---- unit finished: combine the four scaled accumulators (exact), reduce, K-split partials, epilogue ----
             int v[NV];
@@ -577,7 +615,7 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
                         }
                 }
             }
-            load_unit(cc, cc.j + 1);
+            next_unit(cc);
             fetch_consts(cc);
         }
     }
@@ -608,8 +646,8 @@ Shape pick_shape(size_t kp, int x_rows, size_t part_per_warp, int max_warps) {
     const size_t budget = 224 * 1024;  // leaves room for the static arrays
     const size_t fixed = BAR_BYTES + (size_t)x_rows * xs_stride_for(kp);
     int w = max_warps;
-    if (env_w >= 4 && env_w <= max_warps && env_w % 4 == 0) w = env_w;
-    for (; w >= 4; w -= 4) {
+    if (env_w >= 4 && env_w <= max_warps) w = env_w;
+    for (; w >= 4; w -= (w % 4 ? w % 4 : 4)) {
         const size_t need2 = fixed + (size_t)w * (part_per_warp + 2 * STAGE_BYTES);
         if (need2 > budget) continue;
         size_t nst = (budget - fixed - (size_t)w * part_per_warp) / ((size_t)w * STAGE_BYTES);
@@ -736,18 +774,17 @@ int launch_group_stream(const GroupArgs &a, cudaStream_t stream) {
     long long per_cta = 0, staged = 0;
     Shape sh = {0, 0};
     for (;;) {
-        // staged rows for the largest CTA shape first; the warp count only rounds the range
         per_cta = (total + grid - 1) / grid;
-        staged = (per_cta + 15 + p.row_blocks - 2) / p.row_blocks + 1;
+        staged = (per_cta + p.row_blocks - 2) / p.row_blocks + 1;  // layers a range of per_cta row blocks can touch
         if (staged > (long long)a.count) staged = (long long)a.count;
-        sh = staged <= MAX_ROWS ? pick_shape(a.kp, (int)staged, 0, 16) : Shape{0, 0};
-        if ((sh.warps > 0 && sh.nst >= 2) || per_cta <= 16) break;
+        // 12 warps x 3 stages measured 4 % faster under sustained load than 16 x 2 (and than 10, 11, 13, 14 warps)
+        sh = staged <= MAX_ROWS ? pick_shape(a.kp, (int)staged, 0, 12) : Shape{0, 0};
+        if ((sh.warps > 0 && sh.nst >= 2) || per_cta <= 12) break;
         grid *= 2;
     }
     if (sh.warps == 0 || sh.nst < 2)
         return fail(KB_ERR_UNSUPPORTED, "group: %lld activation rows of %zu bytes per CTA do not fit in shared memory", staged,
                     xs_stride_for(a.kp));
-    per_cta = (per_cta + sh.warps - 1) / sh.warps * sh.warps;
     grid = (total + per_cta - 1) / per_cta;
     p.nst = sh.nst;
     p.x = a.x; p.ldx = a.ldx;
@@ -761,7 +798,7 @@ int launch_group_stream(const GroupArgs &a, cudaStream_t stream) {
     p.units_per_cta = (int)per_cta;
     p.status = a.status;
     const size_t smem = BAR_BYTES + (size_t)sh.warps * p.nst * STAGE_BYTES + (size_t)p.x_rows * p.xs_stride;
-    return launch_stream<1, true, 1, 16>(p, a.device, (int)grid, sh.warps, smem, stream);
+    return launch_stream<1, true, 1, 12>(p, a.device, (int)grid, sh.warps, smem, stream);
 }
 
 }  // namespace kb
