@@ -200,12 +200,13 @@ int kb_swiglu_quant(const float *gate_up, size_t n, size_t f, size_t ld, float *
 int kb_swiglu_quant_pairs(const float *gate_up, size_t n, size_t f, size_t ld, float *h, int8_t *xq,
                           size_t ldq, float *sx, int32_t *sumq, kb_stream stream);
 /* Half-split RoPE (crates/kore-edge/src/ops/rope.rs:9-36) on the q and k parts of rows
- * [q|k|v] with cos/sin tables [max_pos][head_dim/2]; k and v go to row cache_rows[t] of
- * caches laid out [rows][n_heads*head_dim]. */
+ * [q|k|v] with cos/sin tables [max_pos][head_dim/2]; k and v go to the caches, which are laid
+ * out head-major, [sequence][n_heads][lmax][head_dim] (a head's keys are contiguous, so decode
+ * attention streams them page by page); cache_rows[t] = sequence * lmax + position. */
 int kb_rope_kv(const float *qkv, const int *positions, const long long *cache_rows,
                const float *cos_table, const float *sin_table, size_t n, int n_heads, int head_dim,
-               float *q_out, float *k_cache, float *v_cache, kb_stream stream);
-/* One query token per sequence against its cache [batch][lmax][n_heads*head_dim]
+               int lmax, float *q_out, float *k_cache, float *v_cache, kb_stream stream);
+/* One query token per sequence against its cache [batch][n_heads][lmax][head_dim]
  * (crates/kore-edge/src/ops/attention.rs:74-135); lens[b] counts the current token. */
 int kb_attn_decode(const float *q, const float *k_cache, const float *v_cache, const int *lens,
                    size_t batch, int n_heads, int head_dim, int lmax, float *out, float *scratch,
@@ -213,6 +214,31 @@ int kb_attn_decode(const float *q, const float *k_cache, const float *v_cache, c
 /* scratch (zero-initialised once by the caller, reusable across calls on one stream) lets the
  * kernel split long caches over several CTAs per head; without it one CTA serves a head. */
 size_t kb_attn_decode_scratch_bytes(size_t batch, int n_heads);
+
+/* ---- persistent decode step: one greedy step of the decoder loop of
+ * crates/kore-edge/src/runtime.rs:106-294 (pre-norm, q/k/v, half-split RoPE, KV cache, causal attention,
+ * output projection + residual, SwiGLU feed-forward + residual, final norm, lm_head, argmax) for one or two
+ * sequences as ONE cooperative kernel: a grid of one CTA per SM walks the phases of every layer, separated by a
+ * bounded device-side grid barrier, and streams the next phase's weights while it waits.  Device pointers.
+ *   qkv[l]      [3d, d] rows q | k | v;  o[l] [d, d];  gate_up[l] [2f, d] rows gate_0, up_0, gate_1, ...;
+ *   down[l]     [d, f] — ternary handles without bias, all on one device (borrowed: destroy the decoder first)
+ *   norm1/2[l]  RMSNorm weights [d];  k_cache/v_cache[l]  [batch, n_heads, max_len, head_dim] f32
+ *   embed, lm_head [vocab, d] f32 dense;  norm_f [d];  cos/sin tables [max_len, head_dim / 2]
+ * kb_decoder_step consumes tokens[b] (int64) at positions[b] (cache row cache_rows[b] = b * max_len + position,
+ * lens[b] = position + 1) and leaves the chosen tokens in tokens[b], the logits in logits [batch, vocab]
+ * (nullable) and all four counters advanced by one.  hidden is a [batch, d] f32 work buffer of the caller. */
+typedef struct kb_decoder kb_decoder;
+int kb_decoder_create(const kb_linear *const *qkv, const kb_linear *const *o, const kb_linear *const *gate_up,
+                      const kb_linear *const *down, const float *const *norm1, const float *const *norm2,
+                      float *const *k_cache, float *const *v_cache, size_t n_layers, size_t batch,
+                      size_t n_heads, size_t max_len, size_t vocab, float eps, const float *embed,
+                      const float *lm_head, const float *norm_f, const float *cos_table,
+                      const float *sin_table, kb_decoder **out);
+void kb_decoder_destroy(kb_decoder *h);
+int kb_decoder_step(kb_decoder *h, long long *tokens, int *positions, int *lens, long long *cache_rows,
+                    float *hidden, float *logits, kb_stream stream);
+/* 0 = clean; otherwise KB_ERR_TIMEOUT and the code of the bounded wait that gave up (the word is cleared) */
+int kb_decoder_status(kb_decoder *h, kb_stream stream, int *status);
 
 /* ---- forward (host pointers; what a Tensor-in/Tensor-out caller uses) ---- */
 

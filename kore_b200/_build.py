@@ -9,7 +9,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_DIR = os.path.join(_PKG, "_lib")
 LIB_PATH = os.path.join(LIB_DIR, "libkore_b200.so")
-SOURCES = ["api.cu", "quant.cu", "gemv.cu", "gemv_group.cu", "gemv_mma.cu", "gemv_stream.cu", "gemm_tc.cu", "gemm_tcs.cu", "gemm_tc2.cu", "static_scratch.cu", "shard.cu", "decoder_ops.cu"]
+SOURCES = ["api.cu", "quant.cu", "gemv.cu", "gemv_group.cu", "gemv_mma.cu", "gemv_stream.cu", "gemm_tc.cu", "gemm_tcs.cu", "gemm_tc2.cu", "static_scratch.cu", "shard.cu", "decoder_ops.cu", "decode_step.cu"]
 HEADERS = ["common.cuh", "device_utils.cuh", "tc_ptx.cuh", os.path.join("..", "..", "include", "kore_b200.h")]
 
 NVCC_FLAGS = [

@@ -44,9 +44,14 @@ SIGNATURES = {
     "kb_rmsnorm_quant": (C.c_int, [_vp, _vp, _sz, _sz, C.c_float, _vp, _vp, _sz, _vp, _vp, _vp]),
     "kb_swiglu_quant": (C.c_int, [_vp, _sz, _sz, _sz, _vp, _vp, _sz, _vp, _vp, _vp]),
     "kb_swiglu_quant_pairs": (C.c_int, [_vp, _sz, _sz, _sz, _vp, _vp, _sz, _vp, _vp, _vp]),
-    "kb_rope_kv": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
+    "kb_rope_kv": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
     "kb_attn_decode": (C.c_int, [_vp, _vp, _vp, _vp, _sz, C.c_int, C.c_int, C.c_int, _vp, _vp, _sz, _vp]),
     "kb_attn_decode_scratch_bytes": (_sz, [_sz, C.c_int]),
+    "kb_decoder_create": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, C.c_float, _vp, _vp, _vp, _vp, _vp,
+                                    C.POINTER(_vp)]),
+    "kb_decoder_destroy": (None, [_vp]),
+    "kb_decoder_step": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "kb_decoder_status": (C.c_int, [_vp, _vp, C.POINTER(C.c_int)]),
     "kb_linear_forward_host": (C.c_int, [_vp, _vp, _sz, _sz, _vp]),
     "kb_linear_forward_static": (C.c_int, [_vp, _vp, _sz, _sz, _vp, _vp]),
     "kb_linear_group_create": (C.c_int, [_vp, _sz, _vp]),

@@ -8,7 +8,7 @@
 //   swiglu_quant    h = (g / (1 + exp(-g))) * u, g|u = the two halves of a row -> int8
 //                   (crates/kore-edge/src/ops/activation.rs:21-26, runtime.rs:232-265)
 //   rope_kv         half-split rotary embedding of q and k from a [q|k|v] row with
-//                   host-supplied cos/sin tables, k and v appended to the cache
+//                   host-supplied cos/sin tables, k and v appended to the head-major cache
 //                   (crates/kore-edge/src/ops/rope.rs:9-36)
 //   attn_decode     one query token per sequence against its KV cache, softmax in f32
 //                   (crates/kore-edge/src/ops/attention.rs:74-135, causal rule of
@@ -176,14 +176,17 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restri
 __global__ void __launch_bounds__(256) rope_kv_kernel(const float *__restrict__ qkv, const int *__restrict__ positions,
                                                       const long long *__restrict__ cache_rows,
                                                       const float *__restrict__ cos_t, const float *__restrict__ sin_t,
-                                                      int n_heads, int hd, float *__restrict__ q_out,
+                                                      int n_heads, int hd, int lmax, float *__restrict__ q_out,
                                                       float *__restrict__ k_cache, float *__restrict__ v_cache) {
     const size_t t = blockIdx.x;
     const int d = n_heads * hd, half = hd / 2;
     const float *q = qkv + t * (size_t)(3 * d), *k = q + d, *v = k + d;
     pdl_release_and_wait();
     const int pos = positions[t];
-    const size_t crow = (size_t)cache_rows[t] * d;
+    // caches are head-major, [sequence][head][lmax][hd]: a head's keys are contiguous, so decode attention streams
+    // them at full DRAM page efficiency; cache_rows[t] = sequence * lmax + position
+    const long long crow_flat = cache_rows[t];
+    const size_t seq = (size_t)(crow_flat / lmax), cpos = (size_t)(crow_flat % lmax);
     const int idx = blockIdx.y * blockDim.x + threadIdx.x;  // pair index, 0 .. n_heads*half-1
     if (idx < n_heads * half) {
         const int h = idx / half, i = idx - h * half;
@@ -192,10 +195,11 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const float *__restrict__ 
         const float q0 = q[a], q1 = q[b], k0 = k[a], k1 = k[b], va = v[a], vb2 = v[b];
         q_out[t * (size_t)d + a] = __fsub_rn(__fmul_rn(q0, c), __fmul_rn(q1, s));
         q_out[t * (size_t)d + b] = __fadd_rn(__fmul_rn(q0, s), __fmul_rn(q1, c));
-        k_cache[crow + a] = __fsub_rn(__fmul_rn(k0, c), __fmul_rn(k1, s));
-        k_cache[crow + b] = __fadd_rn(__fmul_rn(k0, s), __fmul_rn(k1, c));
-        v_cache[crow + a] = va;
-        v_cache[crow + b] = vb2;
+        const size_t crow = ((seq * n_heads + h) * lmax + cpos) * hd;
+        k_cache[crow + i] = __fsub_rn(__fmul_rn(k0, c), __fmul_rn(k1, s));
+        k_cache[crow + i + half] = __fadd_rn(__fmul_rn(k0, s), __fmul_rn(k1, c));
+        v_cache[crow + i] = va;
+        v_cache[crow + i + half] = vb2;
     }
 }
 
@@ -244,8 +248,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
     const float scale = __fdiv_rn(1.0f, sqrtf((float)hd));
-    const float *kb_ = k_cache + (size_t)b * lmax * d + h * hd;
-    const float *vb = v_cache + (size_t)b * lmax * d + h * hd;
+    const float *kb_ = k_cache + ((size_t)b * n_heads + h) * lmax * hd;  // head-major cache: rows of hd floats
+    const float *vb = v_cache + ((size_t)b * n_heads + h) * lmax * hd;
     float m = -INFINITY, l = 0.0f;
     // ATT_UNROLL positions per warp iteration: all their key and value loads are issued before
     // the first use, so a warp pays one memory round trip per ATT_UNROLL positions
@@ -255,8 +259,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
         for (int u = 0; u < ATT_UNROLL; ++u) {
             const int j = jb + u * ATT_WARPS;
             const bool ok = j < j1;
-            load_row(kb_ + (size_t)(ok ? j : j0) * d, ok, kk[u]);
-            load_row(vb + (size_t)(ok ? j : j0) * d, ok, vv[u]);
+            load_row(kb_ + (size_t)(ok ? j : j0) * hd, ok, kk[u]);
+            load_row(vb + (size_t)(ok ? j : j0) * hd, ok, vv[u]);
         }
 #pragma unroll
         for (int u = 0; u < ATT_UNROLL; ++u) {
@@ -366,15 +370,16 @@ int kb_swiglu_quant_pairs(const float *gate_up, size_t n, size_t f, size_t ld, f
 }
 
 int kb_rope_kv(const float *qkv, const int *positions, const long long *cache_rows, const float *cos_table,
-               const float *sin_table, size_t n, int n_heads, int head_dim, float *q_out, float *k_cache, float *v_cache,
-               kb_stream stream) {
+               const float *sin_table, size_t n, int n_heads, int head_dim, int lmax, float *q_out, float *k_cache,
+               float *v_cache, kb_stream stream) {
     if (!qkv || !positions || !cache_rows || !cos_table || !sin_table || !q_out || !k_cache || !v_cache)
         return fail(KB_ERR_INVALID, "null pointer");
     if (n_heads < 1 || head_dim < 2 || head_dim % 2) return fail(KB_ERR_INVALID, "rope: head_dim must be even");
+    if (lmax < 1) return fail(KB_ERR_INVALID, "rope: cache length %d", lmax);
     if (n == 0) return KB_OK;
     const unsigned chunks = (unsigned)((n_heads * (head_dim / 2) + 255) / 256);
     cudaError_t e = launch_pdl(rope_kv_kernel, dim3((unsigned)n, chunks), dim3(256), static_cast<cudaStream_t>(stream), qkv,
-                               positions, cache_rows, cos_table, sin_table, n_heads, head_dim, q_out, k_cache, v_cache);
+                               positions, cache_rows, cos_table, sin_table, n_heads, head_dim, lmax, q_out, k_cache, v_cache);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "rope launch");
 }
 

@@ -7,8 +7,12 @@ projection + residual, RMSNorm, SwiGLU feed-forward + residual, final RMSNorm, d
 lm_head, greedy argmax.  q/k/v share one launch (their packed rows are concatenated, each
 keeping its own per-tensor scale through the per-row scale vector) and so do gate/up.
 RMSNorm and SwiGLU end in the per-token int8 quantiser, the residual adds live in the
-projection epilogues.  Embedding and lm_head are dense f32 (torch); prefill attention uses
-torch's scaled_dot_product_attention, decode attention the library's own kernel.
+projection epilogues.  Embedding and lm_head are dense f32; prefill attention uses torch's
+scaled_dot_product_attention, decode attention the library's own kernel.
+
+For one or two sequences a decode step is ONE launch of the library's persistent decode-step
+kernel (``kb_decoder_step``: every phase of every layer, the lm_head GEMV and the argmax inside
+one cooperative grid); larger batches run the step as a CUDA graph of the separate kernels.
 """
 from __future__ import annotations
 
@@ -98,7 +102,8 @@ def _interleave_rows(a, b):
 
 
 class BitNetDecoder:
-    def __init__(self, cfg: DecoderConfig, weights: Dict, batch: int, device: int = 0, max_prefill_tokens: int = 0):
+    def __init__(self, cfg: DecoderConfig, weights: Dict, batch: int, device: int = 0, max_prefill_tokens: int = 0,
+                 persistent: bool = True):
         import torch
 
         self.cfg, self.batch, self.device = cfg, batch, device
@@ -115,12 +120,14 @@ class BitNetDecoder:
                 "qkv": mk(qkv), "o": mk(lw["o"]), "gu": mk(gu), "down": mk(lw["down"]),
                 "norm1": torch.from_numpy(lw["norm1"]).to(self.dev), "norm2": torch.from_numpy(lw["norm2"]).to(self.dev)})
         self.embed = torch.from_numpy(weights["embed"]).to(self.dev)
-        self.lm_head_t = torch.from_numpy(weights["lm_head"]).to(self.dev).t().contiguous()
+        self.lm_head = torch.from_numpy(weights["lm_head"]).to(self.dev).contiguous()  # [vocab, d] row-major
         self.norm_f = torch.from_numpy(weights["norm_f"]).to(self.dev)
         cos, sin = rope_tables(cfg)
         self.cos, self.sin = torch.from_numpy(cos).to(self.dev), torch.from_numpy(sin).to(self.dev)
-        self.kc = [torch.zeros((batch, cfg.max_len, d), dtype=torch.float32, device=self.dev) for _ in range(cfg.n_layers)]
-        self.vc = [torch.zeros((batch, cfg.max_len, d), dtype=torch.float32, device=self.dev) for _ in range(cfg.n_layers)]
+        # KV caches are head-major, [batch, heads, max_len, head_dim]: a head's keys and values are contiguous
+        kv_shape = (batch, cfg.n_heads, cfg.max_len, cfg.head_dim)
+        self.kc = [torch.zeros(kv_shape, dtype=torch.float32, device=self.dev) for _ in range(cfg.n_layers)]
+        self.vc = [torch.zeros(kv_shape, dtype=torch.float32, device=self.dev) for _ in range(cfg.n_layers)]
         self.ld_d, self.ld_f = int(self.lib.kb_act_ld(d)), int(self.lib.kb_act_ld(f))
         self._bufs = {}
         self._alloc(batch)
@@ -135,8 +142,29 @@ class BitNetDecoder:
         self.att_scratch = torch.zeros(self.att_bytes, dtype=torch.uint8, device=self.dev)
         self.graph = None
         self.launches_per_step = 0
+        # persistent decode step (one launch per step) where the library supports the shape
+        self.persistent = None
+        self.hidden_step = torch.zeros((batch, d), dtype=torch.float32, device=self.dev)
+        if batch <= 2 and persistent:
+            n = cfg.n_layers
+            arr = lambda ptrs: (C.c_void_p * n)(*ptrs)
+            h = C.c_void_p()
+            rc = self.lib.kb_decoder_create(
+                arr([L["qkv"].handle.value for L in self.layers]), arr([L["o"].handle.value for L in self.layers]),
+                arr([L["gu"].handle.value for L in self.layers]), arr([L["down"].handle.value for L in self.layers]),
+                arr([L["norm1"].data_ptr() for L in self.layers]), arr([L["norm2"].data_ptr() for L in self.layers]),
+                arr([t.data_ptr() for t in self.kc]), arr([t.data_ptr() for t in self.vc]), n, batch, cfg.n_heads, cfg.max_len,
+                cfg.vocab, C.c_float(cfg.eps), self.embed.data_ptr(), self.lm_head.data_ptr(), self.norm_f.data_ptr(),
+                self.cos.data_ptr(), self.sin.data_ptr(), C.byref(h))
+            if rc == _cabi.OK:
+                self.persistent = h
+            elif rc != _cabi.ERR_UNSUPPORTED:
+                _cabi.check(rc)
 
     def close(self):
+        if self.persistent is not None:
+            self.lib.kb_decoder_destroy(self.persistent)
+            self.persistent = None
         for lay in self.layers:
             for name in ("qkv", "o", "gu", "down"):
                 lay[name].close()
@@ -173,7 +201,8 @@ class BitNetDecoder:
                 ck(lib.kb_linear_forward_fused(L["qkv"].handle, None, B["xq_d"].data_ptr(), self.ld_d, B["sx"].data_ptr(),
                                                B["sum"].data_ptr(), n, None, B["qkv"].data_ptr(), 0, _cabi.PATH_AUTO, None, 0, sp))
             ck(lib.kb_rope_kv(B["qkv"].data_ptr(), positions.data_ptr(), cache_rows.data_ptr(), self.cos.data_ptr(),
-                              self.sin.data_ptr(), n, H, hd, B["q"].data_ptr(), self.kc[li].data_ptr(), self.vc[li].data_ptr(), sp))
+                              self.sin.data_ptr(), n, H, hd, cfg.max_len, B["q"].data_ptr(), self.kc[li].data_ptr(),
+                              self.vc[li].data_ptr(), sp))
             if prefill_shape is None:
                 ck(lib.kb_attn_decode(B["q"].data_ptr(), self.kc[li].data_ptr(), self.vc[li].data_ptr(), lens.data_ptr(),
                                       n, H, hd, cfg.max_len, B["attn"].data_ptr(), self.att_scratch.data_ptr(),
@@ -182,8 +211,8 @@ class BitNetDecoder:
             else:
                 b, t = prefill_shape
                 qh = B["q"].view(b, t, H, hd).transpose(1, 2)
-                kh = self.kc[li][:b, :t].view(b, t, H, hd).transpose(1, 2)
-                vh = self.vc[li][:b, :t].view(b, t, H, hd).transpose(1, 2)
+                kh = self.kc[li][:b, :, :t]
+                vh = self.vc[li][:b, :, :t]
                 o = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=True)
                 B["attn"].view(b, t, H, hd).copy_(o.transpose(1, 2))
                 launches += 4
@@ -218,7 +247,7 @@ class BitNetDecoder:
         xn = self._bufs[self.batch]["xn"][:n]
         _cabi.check(lib.kb_rmsnorm_quant(hidden_rows.data_ptr(), self.norm_f.data_ptr(), n, cfg.d_model, C.c_float(cfg.eps),
                                          xn.data_ptr(), None, 0, None, None, sp))
-        torch.matmul(xn, self.lm_head_t, out=self.logits[:n])
+        torch.matmul(xn, self.lm_head.t(), out=self.logits[:n])
         return self.logits[:n]
 
     # ---- public API --------------------------------------------------------------------------
@@ -253,6 +282,13 @@ class BitNetDecoder:
         """One greedy decode step for every sequence: consumes self.tokens (the tokens chosen
         by the previous step), leaves the next tokens in self.tokens and logits in self.logits."""
         torch = self.torch
+        if self.persistent is not None:
+            sp = torch.cuda.current_stream(self.device).cuda_stream
+            _cabi.check(self.lib.kb_decoder_step(self.persistent, self.tokens.data_ptr(), self.positions.data_ptr(),
+                                                 self.lens.data_ptr(), self.cache_rows.data_ptr(), self.hidden_step.data_ptr(),
+                                                 self.logits.data_ptr(), sp))
+            self.launches_per_step = 1
+            return
         if not use_graph:
             return self._decode_body()
         if self.graph is None:
@@ -271,6 +307,12 @@ class BitNetDecoder:
             for dst, src in zip((self.tokens, self.positions, self.lens, self.cache_rows), saved):
                 dst.copy_(src)
         self.graph.replay()
+
+    def check_status(self):
+        """Raises KoreError(Timeout) if a bounded wait inside a persistent decode step gave up."""
+        if self.persistent is not None:
+            st = C.c_int(0)
+            _cabi.check(self.lib.kb_decoder_status(self.persistent, None, C.byref(st)))
 
     def generate(self, prompt, steps: int, use_graph: bool = True):
         """Greedy generation: returns int64 [batch, steps] of new tokens."""

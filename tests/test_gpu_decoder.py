@@ -169,8 +169,8 @@ def test_rope_kv_and_attention(env, d_model):
     cos, sin = env.decoder.rope_tables(cfg)
     H, hd, d = cfg.n_heads, cfg.head_dim, cfg.d_model
     batch, lmax = 3, cfg.max_len
-    kc = t.zeros((batch, lmax, d), device="cuda")
-    vc = t.zeros((batch, lmax, d), device="cuda")
+    kc = t.zeros((batch, H, lmax, hd), device="cuda")  # head-major caches
+    vc = t.zeros((batch, H, lmax, hd), device="cuda")
     cosd, sind = t.from_numpy(cos).cuda(), t.from_numpy(sin).cuda()
     lens = [5, 1, 9]
     k_ref = [np.zeros((0, H, hd), np.float32) for _ in range(batch)]
@@ -184,7 +184,7 @@ def test_rope_kv_and_attention(env, d_model):
             pos_d = t.tensor([pos], dtype=t.int32, device="cuda")
             row_d = t.tensor([b * lmax + pos], dtype=t.int64, device="cuda")
             env.cabi.check(env.lib.kb_rope_kv(qkv_d.data_ptr(), pos_d.data_ptr(), row_d.data_ptr(), cosd.data_ptr(),
-                                              sind.data_ptr(), 1, H, hd, q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), env.sp))
+                                              sind.data_ptr(), 1, H, hd, lmax, q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), env.sp))
             t.cuda.synchronize()
             q_r = dr.rope(qkv[:, :d].reshape(1, H, hd), np.array([pos]), cos, sin)
             k_r = dr.rope(qkv[:, d:2 * d].reshape(1, H, hd), np.array([pos]), cos, sin)
@@ -192,8 +192,8 @@ def test_rope_kv_and_attention(env, d_model):
             k_ref[b] = np.concatenate([k_ref[b], k_r])
             v_ref[b] = np.concatenate([v_ref[b], qkv[:, 2 * d:].reshape(1, H, hd)])
             q_last[b] = q_r[0]
-        assert (kc[b, :lens[b]].cpu().numpy().reshape(-1, H, hd) == k_ref[b]).all()
-        assert (vc[b, :lens[b]].cpu().numpy().reshape(-1, H, hd) == v_ref[b]).all()
+        assert (kc[b, :, :lens[b]].transpose(0, 1).cpu().numpy() == k_ref[b]).all()
+        assert (vc[b, :, :lens[b]].transpose(0, 1).cpu().numpy() == v_ref[b]).all()
     out = t.empty((batch, d), device="cuda")
     q_d = t.from_numpy(q_last.reshape(batch, d)).cuda()
     lens_d = t.tensor(lens, dtype=t.int32, device="cuda")
@@ -358,12 +358,12 @@ def test_reference_known_answers_rope_and_attention_kernels(env):
         data = np.array(c["data"], np.float32)
         qkv = t.from_numpy(np.concatenate([data, data, data])[None, :]).cuda()  # q = k = v = the case's row
         q_out = t.empty((1, d), device="cuda")
-        kc, vc = t.zeros((1, d), device="cuda"), t.zeros((1, d), device="cuda")
+        kc, vc = t.zeros((1, H, 1, hd), device="cuda"), t.zeros((1, H, 1, hd), device="cuda")
         pos = t.tensor([c["pos"]], dtype=t.int32, device="cuda")
         row = t.tensor([0], dtype=t.int64, device="cuda")
         cosd, sind = t.from_numpy(cos).cuda(), t.from_numpy(sin).cuda()
         env.cabi.check(env.lib.kb_rope_kv(qkv.data_ptr(), pos.data_ptr(), row.data_ptr(), cosd.data_ptr(), sind.data_ptr(), 1, H, hd,
-                                          q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), env.sp))
+                                          1, q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), env.sp))
         t.cuda.synchronize()
         for y in (q_out.cpu().numpy().ravel(), kc.cpu().numpy().ravel()):  # q and the cached k are both rotated
             if "expect" in c:
@@ -382,8 +382,9 @@ def test_reference_known_answers_rope_and_attention_kernels(env):
         v = np.array(c["v"], np.float32).reshape(seq, d)
         # the decode kernel serves one query per sequence: query i becomes sequence i over the same
         # cache, seeing i + 1 positions (causal) or all of them
-        kc = t.from_numpy(np.broadcast_to(kk, (seq, seq, d)).copy()).cuda()
-        vc = t.from_numpy(np.broadcast_to(v, (seq, seq, d)).copy()).cuda()
+        # [sequence][head][position][hd]
+        kc = t.from_numpy(np.broadcast_to(kk.reshape(seq, H, hd).transpose(1, 0, 2), (seq, H, seq, hd)).copy()).cuda()
+        vc = t.from_numpy(np.broadcast_to(v.reshape(seq, H, hd).transpose(1, 0, 2), (seq, H, seq, hd)).copy()).cuda()
         lens = t.tensor([i + 1 if c["causal"] else seq for i in range(seq)], dtype=t.int32, device="cuda")
         out = t.empty((seq, d), device="cuda")
         nbytes = int(env.lib.kb_attn_decode_scratch_bytes(seq, H))
@@ -400,3 +401,31 @@ def test_reference_known_answers_rope_and_attention_kernels(env):
         ref = dr.attention(q.reshape(seq, H, hd), kk.reshape(seq, H, hd), v.reshape(seq, H, hd), 0).reshape(seq, d) if c["causal"] else None
         if ref is not None:
             assert np.abs(o - ref).max() < 1e-5
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+def test_persistent_decode_step_matches_the_separate_kernels(env, batch):
+    """One cooperative launch per step (kb_decoder_step) against the step built from the separate kernels:
+    same tokens, logits within the tolerance the int8 activation codes allow, clean status word."""
+    t = env.torch
+    cfg = env.decoder.DecoderConfig(n_layers=3, d_model=256, n_heads=4, d_ff=640, vocab=301, max_len=48)
+    weights = env.decoder.random_weights(cfg, seed=4100)
+    prompt = t.from_numpy(np.array([[7, 300, 12, 99, 150, 3, 42, 8, 250][: 9 - b] + [1] * b for b in range(batch)], np.int64)).cuda()
+    outs = []
+    for persistent in (True, False):
+        dec = env.decoder.BitNetDecoder(cfg, weights, batch=batch, persistent=persistent)
+        assert (dec.persistent is not None) == persistent
+        logits = dec.prefill(prompt)
+        t.argmax(logits, dim=1, out=dec.tokens)
+        toks, lgs = [dec.tokens.cpu().numpy().copy()], []
+        for _ in range(8):
+            dec.decode_step()
+            toks.append(dec.tokens.cpu().numpy().copy())
+            lgs.append(dec.logits.cpu().numpy().copy())
+        dec.check_status()
+        assert int(dec.positions[0]) == prompt.shape[1] + 8 and int(dec.lens[0]) == prompt.shape[1] + 9
+        outs.append((np.stack(toks), np.stack(lgs)))
+        dec.close()
+    (tok_p, lg_p), (tok_s, lg_s) = outs
+    assert (tok_p == tok_s).all()
+    assert np.abs(lg_p - lg_s).max() <= 0.02 * np.abs(lg_s).max()
