@@ -175,19 +175,27 @@ static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim
 // later calls of the same thread, released when the thread ends.
 struct HostStaging {
     int device = -1;
-    void *dx = nullptr, *dy = nullptr;
+    void *dx = nullptr, *dy = nullptr, *ws = nullptr;
     void *hy = nullptr;  // pinned twin of dy: a device -> pageable copy would be staged by the driver anyway
-    size_t dx_cap = 0, dy_cap = 0;
+    size_t dx_cap = 0, dy_cap = 0, ws_cap = 0;
     ~HostStaging() { release(); }
     void release() {
         if (dx) cudaFree(dx);
         if (dy) cudaFree(dy);
+        if (ws) cudaFree(ws);
         if (hy) cudaFreeHost(hy);
-        dx = dy = hy = nullptr;
-        dx_cap = dy_cap = 0;
+        dx = dy = hy = ws = nullptr;
+        dx_cap = dy_cap = ws_cap = 0;
     }
-    int ensure(int dev, size_t xb, size_t yb) {
+    int ensure(int dev, size_t xb, size_t yb, size_t wsb) {
         if (dev != device) { release(); device = dev; }
+        if (wsb > ws_cap) {  // quantised activations of the multi-token kernels
+            if (ws) cudaFree(ws);
+            ws = nullptr; ws_cap = 0;
+            cudaError_t e = cudaMalloc(&ws, wsb);
+            if (e != cudaSuccess) return cuda_fail(e, "workspace staging");
+            ws_cap = wsb;
+        }
         if (xb > dx_cap) {
             if (dx) cudaFree(dx);
             dx = nullptr; dx_cap = 0;
@@ -217,13 +225,13 @@ static int forward_host_impl(const Linear *L, const float *x, size_t n, size_t i
     if (!x || !y) return fail(KB_ERR_INVALID, "null activation or output pointer");
     if (n == 0) return KB_OK;
     cudaStream_t st = cudaStreamPerThread;
-    int rc = g_staging.ensure(L->device, n * L->k * sizeof(float), n * L->m * sizeof(float));
+    int rc = g_staging.ensure(L->device, n * L->k * sizeof(float), n * L->m * sizeof(float), workspace_bytes(L, n));
     if (rc) return rc;
     float *dx = static_cast<float *>(g_staging.dx), *dy = static_cast<float *>(g_staging.dy);
     cudaError_t e;
     if ((e = cudaMemcpyAsync(dx, x, n * L->k * sizeof(float), cudaMemcpyHostToDevice, st)) != cudaSuccess)
         rc = cuda_fail(e, "activation upload");
-    if (rc == KB_OK) rc = forward_impl(L, dx, n, in_dim, dy, 0, nullptr, KB_PATH_AUTO, nullptr, 0, st);
+    if (rc == KB_OK) rc = forward_impl(L, dx, n, in_dim, dy, 0, nullptr, KB_PATH_AUTO, g_staging.ws, g_staging.ws_cap, st);
     const size_t yb = n * L->m * sizeof(float);
     void *landing = (g_staging.hy && yb <= (4u << 20)) ? g_staging.hy : static_cast<void *>(y);
     if (rc == KB_OK && (e = cudaMemcpyAsync(landing, dy, yb, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
@@ -358,7 +366,9 @@ static int ternary_ternary(const uint8_t *a_packed, size_t a_len, const float *a
         FwdArgs a = {};
         a.lin = L; a.xq = xq; a.ldq = L->kp; a.sx = sx; a.sumq = sumq; a.n = n; a.y = dy; a.ldy = 0;
         const int path = auto_path(L, n, true);
-        rc = path == KB_PATH_GEMV ? launch_gemv(a, st) : (path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, st) : launch_gemm_tc(a, st));
+        rc = path == KB_PATH_GEMV ? launch_gemv(a, st)
+             : (path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, st)
+                : (path == KB_PATH_GEMV_STREAM ? launch_gemv_stream(a, st) : launch_gemm_tc(a, st)));
     }
     if (rc == KB_OK) rc = launch_transpose_f32(dy, n, m, dc, st);  // [N,M] -> [M,N]
     if (rc == KB_OK && (e = cudaMemcpyAsync(c, dc, yb, cudaMemcpyDeviceToHost, st)) != cudaSuccess) rc = cuda_fail(e, "c download");
