@@ -357,6 +357,21 @@ int kb_linear_forward_sharded_q8(const kb_linear *h, const int8_t *xq, size_t ld
                                  const int32_t *sumq, size_t n, float *const *y_bases, int world, int rank,
                                  size_t m_total, size_t col_offset, int path, int *const *flag_arrays_dev,
                                  int *sync_words_dev, kb_stream stream);
+/* Chain form for a sequence of sharded layers (up to 32 tokens, pre-quantised activations): the launch first
+ * streams its weights, then waits (bounded) until every peer has published the PREVIOUS forward of the chain —
+ * so the cross-GPU latency hides behind the weight stream and launches keep programmatic dependent launch —
+ * and publishes its own slice at its end WITHOUT waiting.  Every rank must issue the same sequence of chain
+ * forwards on the same exchange state; call kb_peer_wait after the last one before reading its output.  Where
+ * the streaming kernel does not take the shape, the call behaves like kb_linear_forward_sharded_q8 (full
+ * barrier), which is stronger. */
+int kb_linear_forward_sharded_chain_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const float *sx,
+                                       const int32_t *sumq, size_t n, float *const *y_bases, int world,
+                                       int rank, size_t m_total, size_t col_offset,
+                                       int *const *flag_arrays_dev, int *sync_words_dev, kb_stream stream);
+/* waits (bounded) until every rank has published as many forwards as this rank (epoch_counter_dev = the first
+ * of the three sync words) */
+int kb_peer_wait(int *const *flag_arrays_dev, int world, int rank, const int *epoch_counter_dev,
+                 int *status_dev, kb_stream stream);
 /* flag_arrays_dev: device array of `world` pointers, entry q = rank q's int32[world]
  * flag array (local or peer mapping); epoch_counter_dev: one local int32, starts at 0 and
  * is bumped by every barrier (all ranks must issue the same sequence of barriers);

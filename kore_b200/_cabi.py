@@ -71,6 +71,8 @@ SIGNATURES = {
     "kb_pack_weights_quaternary": (C.c_int, [_vp, _sz, _sz, _vp, _sz, _vp, _sz, C.c_int]),
     "kb_linear_forward_sharded": (C.c_int, [_vp, _vp, _sz, _sz, _vp, C.c_int, C.c_int, _sz, _sz, C.c_int, _vp, _sz, _vp, _vp, _vp]),
     "kb_linear_forward_sharded_q8": (C.c_int, [_vp, _vp, _sz, _vp, _vp, _sz, _vp, C.c_int, C.c_int, _sz, _sz, C.c_int, _vp, _vp, _vp]),
+    "kb_linear_forward_sharded_chain_q8": (C.c_int, [_vp, _vp, _sz, _vp, _vp, _sz, _vp, C.c_int, C.c_int, _sz, _sz, _vp, _vp, _vp]),
+    "kb_peer_wait": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp, _vp]),
     "kb_peer_barrier": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp, _vp]),
     "kb_symm_alloc": (C.c_int, [_sz, C.POINTER(_vp)]),
     "kb_symm_free": (C.c_int, [_vp]),

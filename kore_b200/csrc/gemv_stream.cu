@@ -101,6 +101,10 @@ struct StreamParams {
     int mul, off;
     int units_per_cta;  // groups: virtual row blocks per CTA
     int *status;
+    // column-sharded layers in a chain (sync.world > 0): before it touches its activations the launch waits,
+    // bounded, until every peer has published the PREVIOUS forward of the chain (the wait hides behind the weight
+    // stream that is already in flight); after its last store it publishes this one without waiting
+    PeerSync sync;
 };
 
 // 16-byte asynchronous copy global -> shared that bypasses L1 and the register file
@@ -372,6 +376,25 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
+    if (p.sync.world > 0) {
+        // every peer's previous forward has landed in this rank's buffers (and, by the same token, every peer
+        // has finished reading the buffer this forward is about to overwrite)
+        if ((int)threadIdx.x < p.sync.world) {
+            const int j = threadIdx.x;
+            const int want = *reinterpret_cast<volatile int *>(p.sync.epoch_counter);  // forwards published so far by this rank
+            const volatile int *mine = p.sync.flag_arrays[p.sync.rank] + j;
+            const long long t0 = clock64();
+            bool ok = false;
+            for (;;) {
+                if (*mine - want >= 0) { ok = true; break; }
+                if (clock64() - t0 > WAIT_CYCLES) break;
+            }
+            __threadfence_system();  // acquire side: later reads of the peers' slices see their data
+            if (!ok) atomicCAS(p.sync.status, 0, 100 + j);  // peer j never arrived
+        }
+        __syncthreads();
+    }
+
     // ---- activations -> shared memory (int8, transposed cells) ----
     const int cells = (p.xs_stride - 64) >> 4;
     if (p.x) {
@@ -627,7 +650,25 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
         for (uint32_t f = cons; f < fills; ++f)
             if (!wait_stage(bar0 + 8 * (f % (uint32_t)nst), (f / (uint32_t)nst) & 1u)) break;
     }
-    if (p.n_more) __threadfence_system();
+    if (p.sync.world > 0) {
+        // publish this rank's slice: every CTA orders its peer stores at system scope before it is counted; the
+        // last CTA of the launch bumps the epoch and writes it into slot [rank] of every rank's flag array
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            const int ticket = atomicAdd(p.sync.done_counter, 1);
+            if (ticket == (int)gridDim.x - 1) {
+                __threadfence_system();  // cumulative: every counted CTA's stores are ordered before the flags
+                *p.sync.done_counter = 0;
+                const int epoch = *p.sync.epoch_counter + 1;
+                for (int j = 0; j < p.sync.world; ++j) *reinterpret_cast<volatile int *>(p.sync.flag_arrays[j] + p.sync.rank) = epoch;
+                __threadfence_system();
+                *reinterpret_cast<volatile int *>(p.sync.epoch_counter) = epoch;
+            }
+        }
+    } else if (p.n_more) {
+        __threadfence_system();
+    }
 }
 
 size_t xs_stride_for(size_t kp) { return (kp + 1023) / 1024 * 1024 + 64; }
@@ -693,9 +734,14 @@ SinglePlan plan_single(const Linear *lin, size_t n) {
     int ks = 1;
     while (ks < 8 && ks * 2 <= nchunks && (long long)row_blocks * ks < (long long)sms * maxw) ks *= 2;
     if ((env_ks == 1 || env_ks == 2 || env_ks == 4 || env_ks == 8) && env_ks <= nchunks) ks = env_ks;
+    // a layer of a few tens of KB per SM is over before a second launch could start behind it: take half an SM's
+    // shared memory (8 warps x 2 stages), so that the next launch of a chain is resident early (programmatic
+    // dependent launch) and streams its first weights while this one finishes
+    const bool small = lin->m_alloc * lin->row_bytes / (size_t)sms < ((size_t)64 << 10);
     for (;; ks /= 2) {  // a smaller K split needs less scratch
         const size_t part_per_warp = ks > 1 ? (size_t)2 * nv_for(n) * 32 * 4 : 0;
         Shape sh = pick_shape(lin->kp, (int)n, part_per_warp, maxw);
+        if (small && sh.warps > 8 && (size_t)n * xs_stride_for(lin->kp) <= ((size_t)24 << 10)) { sh.warps = 8; sh.nst = 2; }
         while (sh.warps && sh.warps % ks) sh.warps -= 4;  // whole groups of ks warps
         if (sh.warps >= ks && sh.warps > 0 && sh.nst >= 2) return SinglePlan{ks, sh.warps, sh.nst, (size_t)sh.warps * part_per_warp};
         if (ks == 1) return SinglePlan{1, 0, 0, 0};
@@ -745,6 +791,8 @@ int launch_gemv_stream(const FwdArgs &a, cudaStream_t stream) {
     p.mul = L->mul; p.off = L->off;
     p.units_per_cta = 0;
     p.status = L->dev_status;
+    p.sync = PeerSync{};
+    if (a.sync && a.y) p.sync = *a.sync;
     const int gp = plan.warps / plan.ks;
     int grid = (p.row_blocks + gp - 1) / gp;
     const int sms = sm_count(L->device);
@@ -797,6 +845,7 @@ int launch_group_stream(const GroupArgs &a, cudaStream_t stream) {
     p.mul = a.mul; p.off = a.off;
     p.units_per_cta = (int)per_cta;
     p.status = a.status;
+    p.sync = PeerSync{};
     const size_t smem = BAR_BYTES + (size_t)sh.warps * p.nst * STAGE_BYTES + (size_t)p.x_rows * p.xs_stride;
     return launch_stream<1, true, 1, 12>(p, a.device, (int)grid, sh.warps, smem, stream);
 }

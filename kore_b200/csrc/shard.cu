@@ -45,6 +45,25 @@ __global__ void peer_barrier_kernel(int *const *flag_arrays, int world, int rank
     }
 }
 
+// Wait-only counterpart for chains of sharded forwards that publish without waiting: thread j waits, bounded,
+// until rank j has published as many forwards as this rank has.
+__global__ void peer_wait_kernel(int *const *flag_arrays, int world, int rank, const int *epoch_counter, int *status,
+                                 long long max_cycles) {
+    const int j = threadIdx.x;
+    if (j < world) {
+        const int want = *reinterpret_cast<const volatile int *>(epoch_counter);
+        const volatile int *mine = flag_arrays[rank] + j;
+        const long long t0 = clock64();
+        bool ok = false;
+        for (;;) {
+            if (*mine - want >= 0) { ok = true; break; }
+            if (clock64() - t0 > max_cycles) break;
+        }
+        __threadfence_system();
+        if (!ok) atomicCAS(status, 0, 100 + j);
+    }
+}
+
 }  // namespace kb
 
 using namespace kb;
@@ -102,11 +121,22 @@ int kb_peer_barrier(int *const *flag_arrays_dev, int world, int rank, int *epoch
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "peer barrier launch");
 }
 
+int kb_peer_wait(int *const *flag_arrays_dev, int world, int rank, const int *epoch_counter_dev, int *status_dev,
+                 kb_stream stream) {
+    if (!flag_arrays_dev || !status_dev || !epoch_counter_dev) return fail(KB_ERR_INVALID, "null pointer");
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world)
+        return fail(KB_ERR_INVALID, "world %d / rank %d outside 1..%d", world, rank, MAX_PEERS);
+    peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flag_arrays_dev, world, rank, epoch_counter_dev, status_dev,
+                                                                      2000000000ll);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "peer wait launch");
+}
+
 // x (f32) or xq/sx/sumq (already quantised) -> this rank's slice of y in every rank's buffer
 static int sharded_forward(const kb_linear *h, const float *x, const int8_t *xq, size_t ldq, const float *sx,
                            const int32_t *sumq, size_t n, size_t in_dim, float *const *y_bases, int world, int rank,
                            size_t m_total, size_t col_offset, int path, void *workspace, size_t workspace_bytes,
-                           int *const *flag_arrays_dev, int *sync_words_dev, kb_stream stream) {
+                           int *const *flag_arrays_dev, int *sync_words_dev, kb_stream stream, bool chain = false) {
     const Linear *L = reinterpret_cast<const Linear *>(h);
     if (!L || L->magic != HANDLE_MAGIC) return fail(KB_ERR_BAD_HANDLE, "null or destroyed kb_linear handle");
     if (!y_bases || (!x && !(xq && sx && sumq))) return fail(KB_ERR_INVALID, "null pointer");
@@ -140,6 +170,15 @@ static int sharded_forward(const kb_linear *h, const float *x, const int8_t *xq,
     PeerSync sync = {flag_arrays_dev, sync_words_dev, sync_words_dev ? sync_words_dev + 1 : nullptr,
                      sync_words_dev ? sync_words_dev + 2 : nullptr, world, rank};
     const bool want_sync = flag_arrays_dev && sync_words_dev;
+    if (chain && want_sync && xq && gemv_stream_supports(L, n)) {
+        // chain form: the streaming kernel waits for the peers' previous publication in its prologue and
+        // publishes its own at its end, without waiting
+        a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq;
+        a.sync = &sync;
+        rc = launch_gemv_stream(a, st);
+        if (prev != L->device) cudaSetDevice(prev);
+        return rc;
+    }
     if (path == KB_PATH_GEMV) {
         if (xq) { a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq; } else { a.x = x; }
         a.sync = want_sync ? &sync : nullptr;  // barrier fused into the kernel's tail
@@ -195,6 +234,16 @@ int kb_linear_forward_sharded_q8(const kb_linear *h, const int8_t *xq, size_t ld
     if (!xq || !sx || !sumq) return fail(KB_ERR_INVALID, "null pointer");
     return sharded_forward(h, nullptr, xq, ldq, sx, sumq, n, L->k, y_bases, world, rank, m_total, col_offset, path, nullptr, 0,
                            flag_arrays_dev, sync_words_dev, stream);
+}
+
+int kb_linear_forward_sharded_chain_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const float *sx, const int32_t *sumq,
+                                       size_t n, float *const *y_bases, int world, int rank, size_t m_total,
+                                       size_t col_offset, int *const *flag_arrays_dev, int *sync_words_dev, kb_stream stream) {
+    const Linear *L = reinterpret_cast<const Linear *>(h);
+    if (!L || L->magic != HANDLE_MAGIC) return fail(KB_ERR_BAD_HANDLE, "null or destroyed kb_linear handle");
+    if (!xq || !sx || !sumq || !flag_arrays_dev || !sync_words_dev) return fail(KB_ERR_INVALID, "null pointer");
+    return sharded_forward(h, nullptr, xq, ldq, sx, sumq, n, L->k, y_bases, world, rank, m_total, col_offset, KB_PATH_AUTO,
+                           nullptr, 0, flag_arrays_dev, sync_words_dev, stream, true);
 }
 
 }  // extern "C"

@@ -148,6 +148,12 @@ class ShardContext:
         _cabi.check(self.lib.kb_peer_barrier(self.flag_table.data_ptr(), self.world, self.rank,
                                              self.epoch_counter.data_ptr(), self.status.data_ptr(), stream_ptr))
 
+    def wait(self, stream_ptr: int):
+        """Waits (on the stream, bounded) until every rank has published as many forwards as this one: ends a
+        chain of ``forward_chain_q8`` calls before the last output is read."""
+        _cabi.check(self.lib.kb_peer_wait(self.flag_table.data_ptr(), self.world, self.rank, self.epoch_counter.data_ptr(),
+                                          self.status.data_ptr(), stream_ptr))
+
     def check_status(self):
         code = int(self.status.item())
         if code:
@@ -211,6 +217,25 @@ class ShardedLinear:
         if n == 1 and all(s == smax for _, s in self.parts):
             return out.reshape(1, self.world * smax)
         return assemble_gathered([out[q] for q in range(self.world)], [s for _, s in self.parts])
+
+    def forward_chain_q8(self, xq, sx, sumq, stream_ptr: Optional[int] = None):
+        """One link of a chain of sharded layers on pre-quantised activations: the launch waits for the peers'
+        PREVIOUS publication after it has started streaming its weights, and publishes its own slice without
+        waiting.  Call ``ctx.wait(stream)`` after the last link before reading its output (returned view)."""
+        import torch
+
+        ctx, n = self.ctx, xq.shape[0]
+        if self.exchange != "p2p" or ctx is None:
+            raise _cabi.KoreError(_cabi.ERR_UNSUPPORTED, "forward_chain_q8 uses the p2p exchange")
+        if n > ctx.max_tokens or self.m_total != ctx.m_total:
+            raise _cabi.KoreError(_cabi.ERR_UNSUPPORTED, "tokens or features exceed the shard context")
+        if stream_ptr is None:
+            stream_ptr = torch.cuda.current_stream(xq.device.index).cuda_stream
+        par = ctx.next_parity()
+        _cabi.check(ctx.lib.kb_linear_forward_sharded_chain_q8(
+            self.layer.handle, xq.data_ptr(), xq.stride(0), sx.data_ptr(), sumq.data_ptr(), n, ctx.y_tables_host[par],
+            self.world, self.rank, self.m_total, self.start, ctx.flag_table.data_ptr(), ctx.sync_words.data_ptr(), stream_ptr))
+        return ctx.local_y[par][:n]
 
     def _local_forward(self, x, n, smax, path, stream_ptr):
         """This rank's slice of the output in a [N, smax] staging block (columns beyond the slice stay zero)."""

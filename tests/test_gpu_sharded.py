@@ -62,6 +62,20 @@ def _rank_main(rank, world, port, q):
                         if not bool((y.cpu().numpy() == y_ref).all()):
                             ok = False
                             msgs.append(f"rank {rank} kind {kind} q8 n={n} differs")
+                    # chain form: every link waits for the peers' previous publication only; one wait at the end
+                    sp = torch.cuda.current_stream().cuda_stream
+                    for n in (1, 2, 5, 20):
+                        x = cases.gaussian(950 + n, (n, k), 1.0)
+                        xq, sx, sumq = kernels.quantize_act_i8(torch.from_numpy(x).cuda())
+                        y_ref = kbref.q_forward(kind, packed, scales, bias, m, k, x, threads=2)[0]
+                        outs = [lay.forward_chain_q8(xq, sx, sumq) for _ in range(5)]
+                        ctx.wait(sp)
+                        torch.cuda.synchronize()
+                        for i in (3, 4):  # the two buffers still hold the last two links' outputs
+                            if not bool((outs[i].cpu().numpy() == y_ref).all()):
+                                ok = False
+                                msgs.append(f"rank {rank} kind {kind} chain n={n} link {i} differs")
+                        dist.barrier()
         ctx.check_status()
         ctx.close()
     except Exception as exc:  # report instead of hanging the peers
