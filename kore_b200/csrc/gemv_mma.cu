@@ -291,6 +291,11 @@ bool gemv_mma_supports(const Linear *lin, size_t n) {
 
 int auto_path(const Linear *lin, size_t n, bool prequantised) {
     const size_t gemv_max = prequantised ? 2 : 4;
+    // one or two pre-quantised tokens of a small layer in a chain of launches: the streaming kernel's dp4a form
+    // (3.1 us per dependent 4096 x 4096 layer against 3.7); large layers keep the register-pipelined GEMV, whose
+    // single launch has the shorter ramp
+    if (prequantised && n <= 2 && lin->m_alloc * lin->row_bytes <= ((size_t)16 << 20) && gemv_stream_supports(lin, n))
+        return KB_PATH_GEMV_STREAM;
     if (n <= gemv_max && gemv_supports(lin, n)) return KB_PATH_GEMV;
     // 3..8 tokens of a large layer: the streaming kernel's MMA form (19 us against 23 for 4 tokens of 8192 -> 28672);
     // small layers are latency-bound and the kernel below has the shorter prologue

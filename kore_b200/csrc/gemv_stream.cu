@@ -257,6 +257,89 @@ __device__ __forceinline__ void quantise_rows2(const float *r0, const float *r1,
     }
 }
 
+// The same for 16-byte aligned rows of at most CPT cells per thread: the rows stay in registers between the maximum
+// and the quantisation, so a launch pays one memory round trip for its activations instead of two.
+template <int CPT>
+__device__ __forceinline__ void quantise_rows2_regs(const float *r0, const float *r1, bool live0, bool live1, bool have1, int k,
+                                                    uint8_t *d0, uint8_t *d1, int cells, float *sc_out, int *sum_out, float *red_f,
+                                                    int *red_i) {
+    const float *row[2] = {r0, r1};
+    const bool live[2] = {live0, live1};
+    const int nv4 = k >> 2;
+    float4 v[2][CPT][4];
+    float amax[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const int j = c * 4 + w;
+                v[u][i][w] = (live[u] && j < nv4) ? reinterpret_cast<const float4 *>(row[u])[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+    }
+#pragma unroll
+    for (int i = 0; i < CPT; ++i)
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+                amax[u] = fmaxf(amax[u], fmaxf(fmaxf(fabsf(v[u][i][w].x), fabsf(v[u][i][w].y)), fmaxf(fabsf(v[u][i][w].z), fabsf(v[u][i][w].w))));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        amax[0] = fmaxf(amax[0], __shfl_xor_sync(0xffffffffu, amax[0], o));
+        amax[1] = fmaxf(amax[1], __shfl_xor_sync(0xffffffffu, amax[1], o));
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) { red_f[warp] = amax[0]; red_f[32 + warp] = amax[1]; }
+    __syncthreads();
+    amax[0] = amax[1] = 0.0f;
+    for (int w = 0; w < nwarps; ++w) { amax[0] = fmaxf(amax[0], red_f[w]); amax[1] = fmaxf(amax[1], red_f[32 + w]); }
+    float sc[2], rs[2];
+    int local_sum[2] = {0, 0};
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        sc[u] = amax[u] < 1e-8f ? 1.0f : __fdiv_rn(amax[u], 127.0f);
+        rs[u] = __frcp_rn(sc[u]);
+    }
+    uint8_t *dst[2] = {d0, d1};
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < cells) {
+            const int phys = xs_offset(c * 16);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (u == 1 && !have1) continue;
+                uint32_t out[4];
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const int q0 = quantise_one_fast(v[u][i][w].x, sc[u], rs[u]), q1 = quantise_one_fast(v[u][i][w].y, sc[u], rs[u]);
+                    const int q2 = quantise_one_fast(v[u][i][w].z, sc[u], rs[u]), q3 = quantise_one_fast(v[u][i][w].w, sc[u], rs[u]);
+                    local_sum[u] += q0 + q1 + q2 + q3;
+                    out[w] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+                }
+                *reinterpret_cast<uint4 *>(dst[u] + phys) = make_uint4(out[0], out[1], out[2], out[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        local_sum[0] += __shfl_xor_sync(0xffffffffu, local_sum[0], o);
+        local_sum[1] += __shfl_xor_sync(0xffffffffu, local_sum[1], o);
+    }
+    if (lane == 0) { red_i[warp] = local_sum[0]; red_i[32 + warp] = local_sum[1]; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int a = 0, b = 0;
+        for (int w = 0; w < nwarps; ++w) { a += red_i[w]; b += red_i[32 + w]; }
+        sc_out[0] = live[0] ? sc[0] : 1.0f; sum_out[0] = live[0] ? a : 0;
+        if (have1) { sc_out[1] = live[1] ? sc[1] : 1.0f; sum_out[1] = live[1] ? b : 0; }
+    }
+}
+
 // a position in a warp's sequence of (unit, chunk)
 struct Cursor {
     int j;         // ordinal of the unit among this warp's units
@@ -410,9 +493,17 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
                 if (threadIdx.x < 2 && r0 + (int)threadIdx.x < p.x_rows) { s_sx[r0 + threadIdx.x] = 1.0f; s_sum[r0 + threadIdx.x] = 0; }
                 continue;
             }
-            quantise_rows2(p.x + (size_t)(i0 < lim ? i0 : 0) * p.ldx, p.x + (size_t)(i1 < lim ? i1 : 0) * p.ldx, i0 < lim,
-                           have1 && i1 < lim, have1, p.k, p.x_vec4 != 0, xs + (size_t)r0 * p.xs_stride,
-                           xs + (size_t)(r0 + 1) * p.xs_stride, cells, s_sx + r0, s_sum + r0, red_f, red_i);
+            const float *ra = p.x + (size_t)(i0 < lim ? i0 : 0) * p.ldx, *rb_ = p.x + (size_t)(i1 < lim ? i1 : 0) * p.ldx;
+            uint8_t *da = xs + (size_t)r0 * p.xs_stride, *db = xs + (size_t)(r0 + 1) * p.xs_stride;
+            const int cpt = p.x_vec4 ? (cells + (int)blockDim.x - 1) / (int)blockDim.x : 99;
+            if (r0 > 0) __syncthreads();  // the reduction scratch of the previous pair is no longer read
+            if (cpt == 1)
+                quantise_rows2_regs<1>(ra, rb_, i0 < lim, have1 && i1 < lim, have1, p.k, da, db, cells, s_sx + r0, s_sum + r0, red_f, red_i);
+            else if (cpt == 2)
+                quantise_rows2_regs<2>(ra, rb_, i0 < lim, have1 && i1 < lim, have1, p.k, da, db, cells, s_sx + r0, s_sum + r0, red_f, red_i);
+            else
+                quantise_rows2(ra, rb_, i0 < lim, have1 && i1 < lim, have1, p.k, p.x_vec4 != 0, da, db, cells, s_sx + r0, s_sum + r0,
+                               red_f, red_i);
         }
     } else {
         const int lim = GROUPED ? p.count : p.n;

@@ -81,10 +81,68 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const float *__restrict_
     }
 }
 
+// Single-pass form for 16-byte aligned rows of up to G * 4096 elements: a thread keeps its G groups of 16
+// elements in registers between the maximum and the quantisation, so the row is read from memory once
+// (the two-pass form reads it twice; at 2048 x 11008 that second read is a third of the kernel).
+template <int G>
+__global__ void __launch_bounds__(256) act_quant_regs_kernel(const float *__restrict__ x, int k, int8_t *__restrict__ xq,
+                                                             int ldq, float *__restrict__ sx, int32_t *__restrict__ sumq) {
+    __shared__ float red_f[32];
+    __shared__ int red_i[32];
+    const size_t t = blockIdx.x;
+    const float4 *row4 = reinterpret_cast<const float4 *>(x + t * (size_t)k);
+    const int nv4 = k >> 2;
+    float4 v[G][4];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+        const int g = threadIdx.x + i * 256;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const int j = g * 4 + w;
+            v[i][w] = j < nv4 ? row4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i][w].x), fabsf(v[i][w].y)), fmaxf(fabsf(v[i][w].z), fabsf(v[i][w].w))));
+        }
+    }
+    amax = block_reduce_max(amax, red_f);
+    const float s = amax < 1e-8f ? 1.0f : __fdiv_rn(amax, 127.0f);
+    const float rs = __frcp_rn(s);
+    int local_sum = 0;
+    int8_t *qrow = xq + t * (size_t)ldq;
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+        const int g = threadIdx.x + i * 256;
+        if (g < ldq / 16) {
+            uint32_t out[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const int q0 = quantise_one_fast(v[i][w].x, s, rs), q1 = quantise_one_fast(v[i][w].y, s, rs);
+                const int q2 = quantise_one_fast(v[i][w].z, s, rs), q3 = quantise_one_fast(v[i][w].w, s, rs);
+                local_sum += q0 + q1 + q2 + q3;
+                out[w] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+            }
+            *reinterpret_cast<uint4 *>(qrow + g * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+    }
+    local_sum = block_reduce_sum(local_sum, red_i);
+    if (threadIdx.x == 0) {
+        sx[t] = s;
+        if (sumq) sumq[t] = local_sum;
+    }
+}
+
 int launch_act_quant(const float *x, size_t n, size_t k, int8_t *xq, size_t ldq, float *sx,
                      int32_t *sumq, cudaStream_t stream) {
     if (n == 0) return KB_OK;
     const bool vec4 = (k % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    if (vec4 && ldq <= 4 * 4096) {
+        const unsigned grid = (unsigned)n;
+        if (ldq <= 4096) act_quant_regs_kernel<1><<<grid, 256, 0, stream>>>(x, (int)k, xq, (int)ldq, sx, sumq);
+        else if (ldq <= 2 * 4096) act_quant_regs_kernel<2><<<grid, 256, 0, stream>>>(x, (int)k, xq, (int)ldq, sx, sumq);
+        else if (ldq <= 3 * 4096) act_quant_regs_kernel<3><<<grid, 256, 0, stream>>>(x, (int)k, xq, (int)ldq, sx, sumq);
+        else act_quant_regs_kernel<4><<<grid, 256, 0, stream>>>(x, (int)k, xq, (int)ldq, sx, sumq);
+        return launch_status("act_quant launch");
+    }
     if (vec4)
         act_quant_kernel<true><<<(unsigned)n, 256, 0, stream>>>(x, (int)k, xq, (int)ldq, sx, sumq);
     else
