@@ -261,7 +261,8 @@ def main():
     ap.add_argument("--launch", default="grouped", choices=["grouped", "streams"],
                     help="headline step: one grouped launch over the pool of independent layers (default), or one "
                          "quantiser + one GEMV launch per layer spread over --streams streams")
-    ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "group_4096", "small_batch", "medium_batch", "prefill_up", "prefill_down"],
+    ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "group_4096", "small_batch", "medium_batch", "prefill_up", "prefill_down",
+                             "decode_step", "attn_decode"],
                     help="run one small case and print its own JSON line (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -545,8 +546,64 @@ def main():
         dist.destroy_process_group()
 
 
+def decoder_case(torch, lib, _cabi, dev, args):
+    """Small cases of the decoder kernels for ncu: the persistent decode step on an 8-layer slice of the decoder
+    configuration (batch 1, 512-token prompt), or the batch-16 decode attention kernel on one layer's cache."""
+    from kore_b200 import decoder
+
+    if args.only == "decode_step":
+        cfg = decoder.DecoderConfig(n_layers=8)
+        weights = decoder.random_weights(cfg, seed=4000, device=dev.index)
+        dec = decoder.BitNetDecoder(cfg, weights, batch=1, device=dev.index)
+        prompt = torch.randint(0, cfg.vocab, (1, 512), generator=torch.Generator().manual_seed(4999)).to(dev)
+        torch.argmax(dec.prefill(prompt), dim=1, out=dec.tokens)
+        for _ in range(max(1, args.warmup)):
+            dec.decode_step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            dec.decode_step()
+        e1.record()
+        torch.cuda.synchronize()
+        dec.check_status()
+        per = e0.elapsed_time(e1) / 1e3 / args.steps
+        wbytes = cfg.n_layers * (4 * cfg.d_model ** 2 + 3 * cfg.d_model * cfg.d_ff) // 4 + cfg.vocab * cfg.d_model * 4
+        print(json.dumps({"case": args.only, "layers": cfg.n_layers, "us_per_step": per * 1e6, "weight_GB/s": wbytes / per / 1e9}), flush=True)
+        return
+    cfg = decoder.DecoderConfig()
+    batch, H, hd, lmax, length = 16, cfg.n_heads, cfg.head_dim, cfg.max_len, 576
+    kc = torch.randn((batch, H, lmax, hd), device=dev)
+    vc = torch.randn((batch, H, lmax, hd), device=dev)
+    q = torch.randn((batch, H * hd), device=dev)
+    out = torch.empty((batch, H * hd), device=dev)
+    lens = torch.full((batch,), length, dtype=torch.int32, device=dev)
+    nbytes = int(lib.kb_attn_decode_scratch_bytes(batch, H))
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    sp = torch.cuda.current_stream().cuda_stream
+
+    def once():
+        _cabi.check(lib.kb_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens.data_ptr(), batch, H, hd, lmax, out.data_ptr(),
+                                       scratch.data_ptr(), nbytes, sp))
+
+    for _ in range(max(1, args.warmup)):
+        once()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        once()
+    e1.record()
+    torch.cuda.synchronize()
+    per = e0.elapsed_time(e1) / 1e3 / args.steps
+    kv = batch * 2 * length * H * hd * 4
+    print(json.dumps({"case": args.only, "batch": batch, "len": length, "us_per_launch": per * 1e6, "GB/s": kv / per / 1e9}), flush=True)
+
+
 def single_case(torch, lib, _cabi, nn, kernels, dev, args):
     """One kernel on one small case, a handful of eager launches: the command profiled with ncu."""
+    if args.only in ("decode_step", "attn_decode"):
+        return decoder_case(torch, lib, _cabi, dev, args)
     shapes = {"gemv_big": (28672, 8192, 1, 3), "gemv_4096": (4096, 4096, 1, 40), "group_4096": (4096, 4096, 1, 40),
               "small_batch": (28672, 8192, 16, 3),
               "medium_batch": (28672, 8192, 64, 3),

@@ -208,7 +208,9 @@ static int sharded_forward(const kb_linear *h, const float *x, const int8_t *xq,
                 a.xq = wq; a.ldq = L->kp; a.sx = wsx; a.sumq = wsum;
             }
         }
-        if (rc == KB_OK) rc = path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, st) : launch_gemm_tc(a, st);
+        if (rc == KB_OK)
+            rc = path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, st)
+                 : (path == KB_PATH_GEMV_STREAM ? launch_gemv_stream(a, st) : launch_gemm_tc(a, st));
         if (own && ws) cudaFreeAsync(ws, st);
         if (rc == KB_OK && want_sync)
             rc = kb_peer_barrier(flag_arrays_dev, world, rank, sync_words_dev, sync_words_dev + 2, stream);
