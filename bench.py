@@ -800,6 +800,29 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
             entry["chain_matches_unsharded"] = ok_chain
             if rank == 0:
                 out["matches_unsharded"] = out["matches_unsharded"] and ok_chain
+        # flagged exchange (up to 32 pre-quantised tokens): every value crosses NVLink as an 8-byte (value, epoch)
+        # word, nothing is fenced and the producer does not wait; the unpack that follows every forward waits per
+        # word and leaves the plain y [nb, m] on every rank
+        if nb <= 32:
+            y_fl = torch.empty((nb, m), dtype=torch.float32, device=dev)
+
+            def step_flagged():
+                for lay in layers:
+                    ctx.unpack(lay.forward_flagged_q8(xq_c, sx_c, sm_c, stream_ptr=sp), sp, out=y_fl)
+
+            dist.barrier()
+            sec_f, _ = time_graph(torch, step_flagged, 5, 3, stream)
+            t = torch.tensor([sec_f / copies], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            y_fl.zero_()
+            ctx.unpack(layers[-1].forward_flagged_q8(xq_c, sx_c, sm_c, stream_ptr=sp), sp, out=y_fl)
+            ctx.unpack(layers[-1].forward_flagged_q8(xq_c, sx_c, sm_c, stream_ptr=sp), sp, out=y_fl)
+            stream.synchronize()
+            ok_fl = bool((y_fl.cpu().numpy() == y_chk).all()) if rank == 0 else True
+            entry["us_per_forward_flagged"] = float(t.item()) * 1e6
+            entry["flagged_matches_unsharded"] = ok_fl
+            if rank == 0:
+                out["matches_unsharded"] = out["matches_unsharded"] and ok_fl
         # NCCL all-gather variant (eager launches; collectives are not captured here)
         for lay in layers:
             lay.exchange = "collective"
@@ -824,12 +847,85 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
             lay.exchange = "p2p"
         if rank == 0:
             entry["matches_unsharded"] = {"p2p": ok_p2p, "nccl": ok_nccl, "compared": f"all {nb} x {m} outputs of rank 0, =="}
-            best = min(entry["us_per_forward_p2p"], entry.get("us_per_forward_p2p_chain", 1e30))
+            best = min(entry["us_per_forward_p2p"], entry.get("us_per_forward_p2p_chain", 1e30),
+                       entry.get("us_per_forward_flagged", 1e30))
             entry["speedup_vs_unsharded"] = entry["us_unsharded_1gpu_same_run"] / best
             out["matches_unsharded"] = out["matches_unsharded"] and ok_p2p and ok_nccl
         out[f"batch{nb}"] = entry
     ctx.check_status()
     for lay in layers:
+        lay.layer.close()
+    # dependent chain: up (8192 -> 28672) and down (28672 -> 8192) projections alternate, both sharded by output
+    # features, every link reading the previous link's flagged words (the wait sits in its quantiser prologue, behind
+    # its own weight stream); one unpack ends the chain.  Rank 0 runs the same chain unsharded in the same run.
+    wd = (torch.randn((k, m), generator=torch.Generator().manual_seed(5003)) * 0.02).numpy()
+    full_d = nn.BitLinear.new(wd, None, 0.3, quantiser="absmean", device=dev.index)
+    del wd
+    packed_d, scales_d = full_d.packed_weights(), full_d.scales()
+    pairs = max(2, copies // 2)
+    ups = [sharded.ShardedLinear(0, packed, scales, None, k, m, rank, world, device=dev.index, ctx=ctx, dist=dist)
+           for _ in range(pairs)]
+    downs = [sharded.ShardedLinear(0, packed_d, scales_d, None, m, k, rank, world, device=dev.index, ctx=ctx, dist=dist)
+             for _ in range(pairs)]
+    chain = {"links": 2 * pairs, "layers": "ternary 8192 -> 28672 -> 8192 -> ... (absmean), batch 1 and 2, f32 in, f32 out"}
+    for nb in (1, 2):
+        x_host = gaussian(5004, (nb, k), 1.0)
+        x = torch.from_numpy(x_host).to(dev)
+        y_end = torch.empty((nb, k), dtype=torch.float32, device=dev)
+        entry = {}
+        if rank == 0:
+            fu = [full] + [nn.BitLinear.from_packed(packed, scales, None, k, m, device=dev.index) for _ in range(2)]
+            fd = [full_d] + [nn.BitLinear.from_packed(packed_d, scales_d, None, m, k, device=dev.index) for _ in range(2)]
+            mid = torch.empty((nb, m), dtype=torch.float32, device=dev)
+            y_one = torch.empty((nb, k), dtype=torch.float32, device=dev)
+            for name, path in (("auto", _cabi.PATH_AUTO), ("streaming_kernel", _cabi.PATH_GEMV_STREAM)):
+                def step_one():
+                    src = x
+                    for i in range(pairs):
+                        _cabi.check(lib.kb_linear_forward_ex(fu[i % 3].handle, src.data_ptr(), nb, k, mid.data_ptr(), m, None,
+                                                             path, None, 0, sp))
+                        _cabi.check(lib.kb_linear_forward_ex(fd[i % 3].handle, mid.data_ptr(), nb, m, y_one.data_ptr(), k, None,
+                                                             path, None, 0, sp))
+                        src = y_one
+
+                sec_one, _ = time_graph(torch, step_one, 5, 3, stream)
+                entry[f"us_per_link_unsharded_1gpu_{name}"] = sec_one / (2 * pairs) * 1e6
+            stream.synchronize()
+            y_chk = y_one.cpu().numpy().copy()
+            for lay in fu[1:] + fd[1:]:
+                lay.close()
+        dist.barrier()
+
+        ok = True
+        # where the consumer waits for the words: 0 = the library's choice (here the cluster quantiser), 1 = in the
+        # forward kernel's own prologue (every CTA reads the whole row)
+        for name, fuse in (("us_per_link_flagged", 0), ("us_per_link_flagged_wait_in_prologue", 1)):
+            def step_links():
+                f = ups[0].forward_flagged(x, False, sp)
+                f = downs[0].forward_flagged(f, True, sp, fuse)
+                for i in range(1, pairs):
+                    f = ups[i].forward_flagged(f, True, sp, fuse)
+                    f = downs[i].forward_flagged(f, True, sp, fuse)
+                ctx.unpack(f, sp, out=y_end)
+
+            y_end.zero_()
+            dist.barrier()
+            sec_l, _ = time_graph(torch, step_links, 5, 3, stream)
+            t = torch.tensor([sec_l / (2 * pairs)], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            stream.synchronize()
+            entry[name] = float(t.item()) * 1e6
+            if rank == 0:
+                ok = ok and bool((y_end.cpu().numpy() == y_chk).all())
+        if rank == 0:
+            entry["matches_unsharded_chain"] = ok
+            entry["speedup_vs_unsharded"] = min(entry["us_per_link_unsharded_1gpu_auto"],
+                                                entry["us_per_link_unsharded_1gpu_streaming_kernel"]) / entry["us_per_link_flagged"]
+            out["matches_unsharded"] = out["matches_unsharded"] and ok
+        chain[f"batch{nb}"] = entry
+    out["dependent_chain_flagged"] = chain
+    ctx.check_status()
+    for lay in ups + downs:
         lay.layer.close()
     ctx.close()
     return out

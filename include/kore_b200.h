@@ -368,6 +368,38 @@ int kb_linear_forward_sharded_chain_q8(const kb_linear *h, const int8_t *xq, siz
                                        const int32_t *sumq, size_t n, float *const *y_bases, int world,
                                        int rank, size_t m_total, size_t col_offset,
                                        int *const *flag_arrays_dev, int *sync_words_dev, kb_stream stream);
+/* Flagged exchange for chains of dependent sharded layers of one to eight tokens (up to 32 pre-quantised): every
+ * output value travels as an 8-byte word (f32 bits in the low half, an epoch in the high half) written with a
+ * single 8-byte store into every rank's buffer, so a reader that finds the expected epoch has the value too — no
+ * fence, no flag array, no barrier, and nothing waits in the producer.  y_bases[q] = rank q's buffer of
+ * [n][m_total] such words (16-byte aligned, m_total even; local or peer mapping).
+ *   A chain is forwards seq = 1, 2, ... (at most 255), each consuming the previous one's words, ended by ONE
+ * kb_flagged_unpack of the last result; every rank issues the same chain.  seq = 1 takes plain f32 x [n][in_dim]
+ * (x_is_flagged = 0, ldx 0 or in_dim) or pre-quantised activations; seq >= 2 takes x_is_flagged = 1: x is this
+ * rank's buffer of forward seq - 1, ldx its leading dimension in words, K a multiple of 4.  The consumer waits,
+ * bounded, per word: either in the forward kernel's own quantiser prologue (fuse = 1; every CTA reads the whole
+ * row, good for short rows) or in a cluster kernel that quantises the row once for all CTAs (fuse = 2; needs
+ * `workspace`, 256-byte aligned, twice (n * kb_act_ld(K) rounded up to 256 + 2 * (4 n rounded up to 256))
+ * bytes, or NULL to allocate on the stream); fuse = 0 chooses.  Either way the forward kernel has issued its first
+ * weight copies before it waits.  Epoch = (round << 8) | seq with the round in sync_words_dev[3], advanced by the
+ * unpack, so chains are graph-replayable.  sync_words_dev: 8 int32, zero-initialised ({0,1}: the fence protocol
+ * of the other sharded entry points, [2] status, [3] round, [4] counter of the unpack).
+ *   Buffer rule: consecutive flagged forwards — across chains too — alternate between two buffers.  Then a rank
+ * cannot overwrite words a peer still has to read, because it needs that peer's next words first.
+ *   A word that never arrives ends the wait after about a second with status 110 (sync_words_dev[2], or
+ * kb_linear_last_device_status for the fused prologue). */
+int kb_linear_forward_sharded_flagged(const kb_linear *h, const void *x, int x_is_flagged, size_t ldx, size_t n,
+                                      size_t in_dim, unsigned long long *const *y_bases, int world, int rank,
+                                      size_t m_total, size_t col_offset, int seq, int fuse, void *workspace,
+                                      size_t workspace_bytes, int *sync_words_dev, kb_stream stream);
+int kb_linear_forward_sharded_flagged_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const float *sx,
+                                         const int32_t *sumq, size_t n, unsigned long long *const *y_bases,
+                                         int world, int rank, size_t m_total, size_t col_offset, int seq,
+                                         int *sync_words_dev, kb_stream stream);
+/* end of a chain: flagged words [n][ld_src] of forward `seq` -> plain f32 [n][ld_dst], first m columns; waits
+ * (bounded) until every word has arrived, then advances the round */
+int kb_flagged_unpack(const unsigned long long *src, size_t ld_src, size_t n, size_t m, float *dst, size_t ld_dst,
+                      int seq, int *sync_words_dev, kb_stream stream);
 /* waits (bounded) until every rank has published as many forwards as this rank (epoch_counter_dev = the first
  * of the three sync words) */
 int kb_peer_wait(int *const *flag_arrays_dev, int world, int rank, const int *epoch_counter_dev,

@@ -73,6 +73,11 @@ SIGNATURES = {
     "kb_linear_forward_sharded_q8": (C.c_int, [_vp, _vp, _sz, _vp, _vp, _sz, _vp, C.c_int, C.c_int, _sz, _sz, C.c_int, _vp, _vp, _vp]),
     "kb_linear_forward_sharded_chain_q8": (C.c_int, [_vp, _vp, _sz, _vp, _vp, _sz, _vp, C.c_int, C.c_int, _sz, _sz, _vp, _vp, _vp]),
     "kb_peer_wait": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp, _vp]),
+    "kb_linear_forward_sharded_flagged": (C.c_int, [_vp, _vp, C.c_int, _sz, _sz, _sz, _vp, C.c_int, C.c_int, _sz, _sz, C.c_int,
+                                                   C.c_int, _vp, _sz, _vp, _vp]),
+    "kb_linear_forward_sharded_flagged_q8": (C.c_int, [_vp, _vp, _sz, _vp, _vp, _sz, _vp, C.c_int, C.c_int, _sz, _sz, C.c_int, _vp,
+                                                      _vp]),
+    "kb_flagged_unpack": (C.c_int, [_vp, _sz, _sz, _sz, _vp, _sz, C.c_int, _vp, _vp]),
     "kb_peer_barrier": (C.c_int, [_vp, C.c_int, C.c_int, _vp, _vp, _vp]),
     "kb_symm_alloc": (C.c_int, [_sz, C.POINTER(_vp)]),
     "kb_symm_free": (C.c_int, [_vp]),

@@ -131,20 +131,31 @@ static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim
     if (ldy != 0 && ldy < L->m) return fail(KB_ERR_INVALID, "ldy %zu smaller than out_features %zu", ldy, L->m);
     if (act != KB_ACT_NONE && act != KB_ACT_RELU) return fail(KB_ERR_INVALID, "unknown activation %d", act);
     if (n == 0) return KB_OK;
-    if (path == KB_PATH_AUTO) path = auto_path(L, n, false);
+    bool separate = false;  // quantise in a kernel of its own even where the forward kernel could do it
+    if (path == KB_PATH_AUTO) {
+        path = auto_path(L, n, false);
+        // long rows, or several tokens of a large layer: every CTA of a fused launch would read and quantise all
+        // the rows again in its prologue (8192 -> 28672, 2 / 4 tokens: 25.9 / 37.0 us fused against 20.2 / 20.9 us;
+        // 28672 -> 8192, one token: 23.1 against 18.0 us); short rows of small layers stay fused (8192 -> 3584,
+        // one / two tokens: 7.0 / 9.5 against 8.0 / 9.9 us)
+        if (path == KB_PATH_GEMV && (L->kp >= 16384 || n * L->kp >= 32768 || (n >= 2 && L->m_alloc * L->row_bytes > ((size_t)16 << 20)))) {
+            path = auto_path(L, n, true);
+            separate = true;
+        }
+    }
     FwdArgs a = {};
     a.lin = L; a.n = n; a.y = y; a.acc = acc; a.ldy = ldy;
     a.relu = act == KB_ACT_RELU;
     if (path == KB_PATH_GEMV_SHARED) { a.shared_grid = true; path = KB_PATH_GEMV; }
-    if (path == KB_PATH_GEMV) {
+    if (path == KB_PATH_GEMV && !separate) {
         a.x = x;
         return launch_gemv(a, stream);
     }
-    if (path == KB_PATH_GEMV_STREAM && n <= 8) {  // the quantiser runs in the kernel's prologue
+    if (path == KB_PATH_GEMV_STREAM && n <= 8 && !separate) {  // the quantiser runs in the kernel's prologue
         a.x = x;
         return launch_gemv_stream(a, stream);
     }
-    if (path != KB_PATH_GEMM_TC && path != KB_PATH_GEMV_MMA && path != KB_PATH_GEMV_STREAM)
+    if (path != KB_PATH_GEMM_TC && path != KB_PATH_GEMV_MMA && path != KB_PATH_GEMV_STREAM && path != KB_PATH_GEMV)
         return fail(KB_ERR_INVALID, "unknown path %d", path);
     const size_t need = workspace_bytes(L, n);
     uint8_t *ws = static_cast<uint8_t *>(workspace);
@@ -162,7 +173,8 @@ static int forward_impl(const Linear *L, const float *x, size_t n, size_t in_dim
     if (rc == KB_OK) {
         a.xq = xq; a.ldq = L->kp; a.sx = sx; a.sumq = sumq;
         rc = path == KB_PATH_GEMV_MMA ? launch_gemv_mma(a, stream)
-             : (path == KB_PATH_GEMV_STREAM ? launch_gemv_stream(a, stream) : launch_gemm_tc(a, stream));
+             : (path == KB_PATH_GEMV_STREAM ? launch_gemv_stream(a, stream)
+                : (path == KB_PATH_GEMV ? launch_gemv(a, stream) : launch_gemm_tc(a, stream)));
     }
     if (own) {
         cudaError_t e = cudaFreeAsync(ws, stream);

@@ -78,6 +78,9 @@ int cuda_fail(cudaError_t e, const char *what);
 int set_dyn_smem_once(const void *kernel, int device, int bytes, const char *what);
 
 // ---- launchers (each returns a KB_* status; all work is enqueued on `stream`) ----
+// the same quantiser on rows of flagged words (see FwdArgs::xf): waits, bounded, for epoch (*round << 8) | seq
+int launch_act_quant_flagged(const unsigned long long *x, size_t ldx, size_t n, size_t k, const int *round, int seq, int8_t *xq,
+                             size_t ldq, float *sx, int32_t *sumq, int *status, cudaStream_t stream);
 int launch_act_quant(const float *x, size_t n, size_t k, int8_t *xq, size_t ldq, float *sx,
                      int32_t *sumq, cudaStream_t stream);
 
@@ -138,6 +141,17 @@ struct FwdArgs {
     bool swiglu;
     float *absmax_out;
     float *clear_word;
+    // streaming kernel only, column-sharded layers exchanging "flagged" words: every f32 value travels as an
+    // 8-byte pair (value bits, epoch), stored with one 8-byte store, so a reader that finds the epoch it expects
+    // has the value as well and no fence, flag array or barrier is needed.  xf: activations [n][ldxf] in that
+    // form (produced by the previous flagged forward; the prologue waits, bounded, per pair); y_flagged: y and
+    // y_more point at such buffers (ldy in pairs).  epoch = (*flag_round << 8) | position in the chain of
+    // dependent forwards: flag_seq for y, flag_seq - 1 for xf; the unpack that ends a chain advances the round.
+    const unsigned long long *xf;
+    size_t ldxf;
+    bool y_flagged;
+    const int *flag_round;
+    int flag_seq;
 };
 // kernel choice for `n` tokens when the caller passes KB_PATH_AUTO: the dp4a GEMV for one or two
 // tokens (up to four when it also has to quantise, which it does in its prologue), the

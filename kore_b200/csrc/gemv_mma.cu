@@ -291,10 +291,14 @@ bool gemv_mma_supports(const Linear *lin, size_t n) {
 
 int auto_path(const Linear *lin, size_t n, bool prequantised) {
     const size_t gemv_max = prequantised ? 2 : 4;
-    // one or two pre-quantised tokens of a small layer in a chain of launches: the streaming kernel's dp4a form
-    // (3.1 us per dependent 4096 x 4096 layer against 3.7); large layers keep the register-pipelined GEMV, whose
-    // single launch has the shorter ramp
-    if (prequantised && n <= 2 && lin->m_alloc * lin->row_bytes <= ((size_t)16 << 20) && gemv_stream_supports(lin, n))
+    // one or two pre-quantised tokens: the streaming kernel (3.1 us per dependent 4096 x 4096 layer against 3.7),
+    // except for the largest layers with short rows (one token) or long rows (two), where the register-pipelined
+    // GEMV's shorter ramp wins
+    // (measured, one / two tokens, streaming kernel against the GEMV: 14336 x 8192 8.6 / 11.2 against 8.9 / 11.8 us,
+    // 4096 x 28672 9.3 / 14.1 against 12.6 / 17.4, 8192 x 28672 14.8 / 22.0 against 16.9 / 19.6, 28672 x 8192
+    // 13.9 / 17.1 against 13.4 / 17.9)
+    const bool big = lin->m_alloc * lin->row_bytes > ((size_t)32 << 20), wide = lin->kp >= 16384;
+    if (prequantised && ((n == 1 && (!big || wide)) || (n == 2 && !(big && wide))) && gemv_stream_supports(lin, n))
         return KB_PATH_GEMV_STREAM;
     if (n <= gemv_max && gemv_supports(lin, n)) return KB_PATH_GEMV;
     // 3..8 tokens of a large layer: the streaming kernel's MMA form (19 us against 23 for 4 tokens of 8192 -> 28672);

@@ -105,6 +105,13 @@ struct StreamParams {
     // bounded, until every peer has published the PREVIOUS forward of the chain (the wait hides behind the weight
     // stream that is already in flight); after its last store it publishes this one without waiting
     PeerSync sync;
+    // flagged words (see FwdArgs): activations as (value, epoch) pairs, outputs stored as such pairs;
+    // epoch = (*flag_round << 8) | position in the chain (x: flag_seq - 1, y: flag_seq)
+    const uint2 *xf;
+    size_t ldxf;
+    int y_flagged;
+    const int *flag_round;
+    int flag_seq;
 };
 
 // 16-byte asynchronous copy global -> shared that bypasses L1 and the register file
@@ -340,6 +347,153 @@ __device__ __forceinline__ void quantise_rows2_regs(const float *r0, const float
     }
 }
 
+constexpr int DEV_TIMEOUT_FLAGGED = 110;  // status code: a flagged activation pair never showed its epoch
+
+// two (value, epoch) pairs with one 16-byte load that is neither cached in L1 nor reordered by the compiler
+__device__ __forceinline__ uint4 ld_pairs(const uint2 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// one pair, one 8-byte store: value and epoch become visible together
+__device__ __forceinline__ void st_pair(float *base, size_t o, float value, uint32_t epoch) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(reinterpret_cast<uint2 *>(base) + o), "r"(__float_as_uint(value)),
+                 "r"(epoch)
+                 : "memory");
+}
+
+// 16 consecutive values of a flagged row from element e0 (k is a multiple of 4, rows are 16-byte aligned, so the
+// 16-byte loads never straddle the row's end): waits, bounded, until every pair carries `epoch`.  Elements from k on are 0.
+__device__ __forceinline__ bool load_cell_flagged(const uint2 *row, bool live, int e0, int k, uint32_t epoch, float (&v)[16],
+                                                  long long &t0) {
+    uint4 raw[8];
+    bool need[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        need[w] = live && e0 + 2 * w < k;
+        raw[w] = need[w] ? ld_pairs(row + e0 + 2 * w) : make_uint4(0u, epoch, 0u, epoch);
+    }
+    bool ok = true;
+    for (;;) {
+        bool all = true;
+#pragma unroll
+        for (int w = 0; w < 8; ++w)
+            if (raw[w].y != epoch || raw[w].w != epoch) {
+                all = false;
+                raw[w] = ld_pairs(row + e0 + 2 * w);
+            }
+        if (all) break;
+        const long long now = clock64();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > WAIT_CYCLES) { ok = false; break; }
+    }
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        v[2 * w] = __uint_as_float(raw[w].x);
+        v[2 * w + 1] = __uint_as_float(raw[w].z);
+    }
+    return ok;
+}
+
+// Block-wide: the quantiser of quantise_rows2 on up to two rows of flagged words.  CPT > 0: a thread owns at most CPT
+// cells of 16 values per row and keeps them in registers between the maximum and the quantisation; CPT == 0: any
+// number of cells, read twice (the second read finds the pairs it has already seen).  A pair that never shows its
+// epoch ends the wait after about a second with a status code; the launch then runs on with whatever it read.
+template <int CPT>
+__device__ __forceinline__ void quantise_rows2_flagged(const uint2 *r0, const uint2 *r1, bool live0, bool live1, bool have1, int k,
+                                                       uint32_t epoch, int *status, uint8_t *d0, uint8_t *d1, int cells,
+                                                       float *sc_out, int *sum_out, float *red_f, int *red_i) {
+    constexpr int HOLD = CPT > 0 ? CPT : 1;
+    const uint2 *row[2] = {r0, r1};
+    const bool live[2] = {live0, live1};
+    float v[2][HOLD][16];
+    float amax[2] = {0.0f, 0.0f};
+    long long t0 = 0;
+    bool ok = true;
+    if (CPT > 0) {
+#pragma unroll
+        for (int i = 0; i < HOLD; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                ok &= load_cell_flagged(row[u], live[u] && c < cells, c * 16, k, epoch, v[u][i], t0);
+#pragma unroll
+                for (int e = 0; e < 16; ++e) amax[u] = fmaxf(amax[u], fabsf(v[u][i][e]));
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < cells; c += blockDim.x)
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                ok &= load_cell_flagged(row[u], live[u], c * 16, k, epoch, v[u][0], t0);
+#pragma unroll
+                for (int e = 0; e < 16; ++e) amax[u] = fmaxf(amax[u], fabsf(v[u][0][e]));
+            }
+    }
+    if (!ok && status) atomicCAS(status, 0, DEV_TIMEOUT_FLAGGED);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        amax[0] = fmaxf(amax[0], __shfl_xor_sync(0xffffffffu, amax[0], o));
+        amax[1] = fmaxf(amax[1], __shfl_xor_sync(0xffffffffu, amax[1], o));
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) { red_f[warp] = amax[0]; red_f[32 + warp] = amax[1]; }
+    __syncthreads();
+    amax[0] = amax[1] = 0.0f;
+    for (int w = 0; w < nwarps; ++w) { amax[0] = fmaxf(amax[0], red_f[w]); amax[1] = fmaxf(amax[1], red_f[32 + w]); }
+    float sc[2], rs[2];
+    int local_sum[2] = {0, 0};
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        sc[u] = amax[u] < 1e-8f ? 1.0f : __fdiv_rn(amax[u], 127.0f);
+        rs[u] = __frcp_rn(sc[u]);
+    }
+    uint8_t *dst[2] = {d0, d1};
+    auto emit = [&](int c, int u, const float (&val)[16]) {
+        uint32_t out[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const int q0 = quantise_one_fast(val[4 * w], sc[u], rs[u]), q1 = quantise_one_fast(val[4 * w + 1], sc[u], rs[u]);
+            const int q2 = quantise_one_fast(val[4 * w + 2], sc[u], rs[u]), q3 = quantise_one_fast(val[4 * w + 3], sc[u], rs[u]);
+            local_sum[u] += q0 + q1 + q2 + q3;
+            out[w] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+        }
+        *reinterpret_cast<uint4 *>(dst[u] + xs_offset(c * 16)) = make_uint4(out[0], out[1], out[2], out[3]);
+    };
+    if (CPT > 0) {
+#pragma unroll
+        for (int i = 0; i < HOLD; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            if (c < cells) {
+                emit(c, 0, v[0][i]);
+                if (have1) emit(c, 1, v[1][i]);
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < cells; c += blockDim.x)
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (u == 1 && !have1) continue;
+                load_cell_flagged(row[u], live[u], c * 16, k, epoch, v[u][0], t0);
+                emit(c, u, v[u][0]);
+            }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        local_sum[0] += __shfl_xor_sync(0xffffffffu, local_sum[0], o);
+        local_sum[1] += __shfl_xor_sync(0xffffffffu, local_sum[1], o);
+    }
+    if (lane == 0) { red_i[warp] = local_sum[0]; red_i[32 + warp] = local_sum[1]; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int a = 0, b = 0;
+        for (int w = 0; w < nwarps; ++w) { a += red_i[w]; b += red_i[32 + w]; }
+        sc_out[0] = live[0] ? sc[0] : 1.0f; sum_out[0] = live[0] ? a : 0;
+        if (have1) { sc_out[1] = live[1] ? sc[1] : 1.0f; sum_out[1] = live[1] ? b : 0; }
+    }
+}
+
 // a position in a warp's sequence of (unit, chunk)
 struct Cursor {
     int j;         // ordinal of the unit among this warp's units
@@ -459,6 +613,15 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
+    __shared__ uint32_t s_epoch;
+    const bool flagged = p.xf != nullptr || p.y_flagged != 0;
+    if (flagged) {
+        // the round changes only in the unpack that ends a chain, which is complete once the wait above returns
+        if (threadIdx.x == 0) s_epoch = (uint32_t)(*reinterpret_cast<const volatile int *>(p.flag_round)) << 8;
+        __syncthreads();
+    }
+    const uint32_t x_epoch = flagged ? (s_epoch | (uint32_t)(p.flag_seq - 1)) : 0u, y_epoch = flagged ? (s_epoch | (uint32_t)p.flag_seq) : 0u;
+
     if (p.sync.world > 0) {
         // every peer's previous forward has landed in this rank's buffers (and, by the same token, every peer
         // has finished reading the buffer this forward is about to overwrite)
@@ -480,7 +643,19 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
 
     // ---- activations -> shared memory (int8, transposed cells) ----
     const int cells = (p.xs_stride - 64) >> 4;
-    if (p.x) {
+    if (p.xf) {
+        for (int r0 = 0; r0 < p.x_rows; r0 += 2) {
+            const bool have1 = r0 + 1 < p.x_rows;
+            const uint2 *ra = p.xf + (size_t)r0 * p.ldxf, *rb_ = p.xf + (size_t)(have1 ? r0 + 1 : r0) * p.ldxf;
+            uint8_t *da = xs + (size_t)r0 * p.xs_stride, *db = xs + (size_t)(r0 + 1) * p.xs_stride;
+            const int cpt = (cells + (int)blockDim.x - 1) / (int)blockDim.x;
+            if (r0 > 0) __syncthreads();
+            if (cpt == 1)
+                quantise_rows2_flagged<1>(ra, rb_, true, have1, have1, p.k, x_epoch, p.status, da, db, cells, s_sx + r0, s_sum + r0, red_f, red_i);
+            else
+                quantise_rows2_flagged<0>(ra, rb_, true, have1, have1, p.k, x_epoch, p.status, da, db, cells, s_sx + r0, s_sum + r0, red_f, red_i);
+        }
+    } else if (p.x) {
         for (int r0 = 0; r0 < p.x_rows; r0 += 2) {
             const int i0 = GROUPED ? layer0 + r0 : r0, i1 = i0 + 1;
             const int lim = GROUPED ? p.count : p.n;
@@ -702,8 +877,13 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
                         float out = dequant_out(a, sw_, s_sx[xr_], bi_, has_bias);
                         if (p.resid) out = __fadd_rn(out, p.resid[o]);
                         if (p.relu) out = fmaxf(out, 0.0f);
-                        p.y[o] = out;
-                        for (int q = 0; q < p.n_more; ++q) p.y_more[q][o] = out;  // peer copies over NVLink
+                        if (p.y_flagged) {  // (value, epoch) pairs, locally and into the peers' buffers over NVLink
+                            st_pair(p.y, o, out, y_epoch);
+                            for (int q = 0; q < p.n_more; ++q) st_pair(p.y_more[q], o, out, y_epoch);
+                        } else {
+                            p.y[o] = out;
+                            for (int q = 0; q < p.n_more; ++q) p.y_more[q][o] = out;  // peer copies over NVLink
+                        }
                     }
                 };
                 if constexpr (DP) {
@@ -757,7 +937,7 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
                 *reinterpret_cast<volatile int *>(p.sync.epoch_counter) = epoch;
             }
         }
-    } else if (p.n_more) {
+    } else if (p.n_more && !flagged) {
         __threadfence_system();
     }
 }
@@ -808,10 +988,16 @@ int launch_stream(const StreamParams &p, int device, int grid, int warps, size_t
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "stream launch");
 }
 
+// two tokens: the dp4a form (NT = 2) for layers of up to 16 MB, where the launch is latency-bound; above, its
+// doubled dp4a work no longer hides behind the copies and the MMA form is faster (17.1 against 24.7 us for
+// 8192 -> 28672, 5.9 against 6.3 us for its eighth)
+bool two_tokens_dp4a(const Linear *lin) { return lin->m_alloc * lin->row_bytes <= ((size_t)16 << 20); }
+// the instance that serves n tokens: 1 / 2 = dp4a form for that many tokens, 0 = MMA form
+int dp4a_tokens(const Linear *lin, size_t n) { return n == 1 ? 1 : (n == 2 && two_tokens_dp4a(lin) ? 2 : 0); }
 // values a lane parks in shared memory per unit when K is split
-int nv_for(size_t n) { return n <= 2 ? (int)n : (n <= 8 ? 4 : (n <= 16 ? 8 : 16)); }
-// most warps per CTA of the kernel instance that serves n tokens (register bound)
-int max_warps_for(size_t n) { return n == 2 ? 12 : (n <= 8 ? 16 : (n <= 16 ? 12 : 8)); }
+int nv_for(const Linear *lin, size_t n) { return dp4a_tokens(lin, n) ? (int)n : (n <= 8 ? 4 : (n <= 16 ? 8 : 16)); }
+// most warps per CTA of that instance (register bound)
+int max_warps_for(const Linear *lin, size_t n) { return dp4a_tokens(lin, n) == 2 ? 12 : (n <= 8 ? 16 : (n <= 16 ? 12 : 8)); }
 
 struct SinglePlan { int ks, warps, nst; size_t part_bytes; };
 // launch shape of a single layer (warps == 0: does not fit)
@@ -820,17 +1006,17 @@ SinglePlan plan_single(const Linear *lin, size_t n) {
     const int row_blocks = (int)((lin->m + 15) / 16);
     const int sms = sm_count(lin->device);
     static const int env_ks = env_int("KB_STREAM_KS", 0);
-    const int maxw = max_warps_for(n);
+    const int maxw = max_warps_for(lin, n);
     // K split: enough (row block, slice) units to give every warp of every SM one
     int ks = 1;
-    while (ks < 8 && ks * 2 <= nchunks && (long long)row_blocks * ks < (long long)sms * maxw) ks *= 2;
-    if ((env_ks == 1 || env_ks == 2 || env_ks == 4 || env_ks == 8) && env_ks <= nchunks) ks = env_ks;
+    while (ks < 16 && ks * 2 <= nchunks && ks * 2 <= maxw && (long long)row_blocks * ks < (long long)sms * maxw) ks *= 2;
+    if ((env_ks == 1 || env_ks == 2 || env_ks == 4 || env_ks == 8 || env_ks == 16) && env_ks <= nchunks && env_ks <= maxw) ks = env_ks;
     // a layer of a few tens of KB per SM is over before a second launch could start behind it: take half an SM's
     // shared memory (8 warps x 2 stages), so that the next launch of a chain is resident early (programmatic
     // dependent launch) and streams its first weights while this one finishes
     const bool small = lin->m_alloc * lin->row_bytes / (size_t)sms < ((size_t)64 << 10);
     for (;; ks /= 2) {  // a smaller K split needs less scratch
-        const size_t part_per_warp = ks > 1 ? (size_t)2 * nv_for(n) * 32 * 4 : 0;
+        const size_t part_per_warp = ks > 1 ? (size_t)2 * nv_for(lin, n) * 32 * 4 : 0;
         Shape sh = pick_shape(lin->kp, (int)n, part_per_warp, maxw);
         if (small && sh.warps > 8 && (size_t)n * xs_stride_for(lin->kp) <= ((size_t)24 << 10)) { sh.warps = 8; sh.nst = 2; }
         while (sh.warps && sh.warps % ks) sh.warps -= 4;  // whole groups of ks warps
@@ -851,8 +1037,18 @@ int launch_gemv_stream(const FwdArgs &a, cudaStream_t stream) {
     if (a.n == 0) return KB_OK;
     if (!gemv_stream_supports(L, a.n))
         return fail(KB_ERR_UNSUPPORTED, "streaming kernel: %zu tokens x K=%zu do not fit in shared memory", a.n, L->k);
-    if (a.x && a.n > 8) return fail(KB_ERR_UNSUPPORTED, "streaming kernel: the fused quantiser takes up to 8 tokens");
-    if (!a.x) {
+    if ((a.x || a.xf) && a.n > 8) return fail(KB_ERR_UNSUPPORTED, "streaming kernel: the fused quantiser takes up to 8 tokens");
+    const bool flagged = a.xf || a.y_flagged;
+    if (flagged) {
+        if (!a.flag_round || a.flag_seq < 1 || a.flag_seq > 255 || (a.xf && a.flag_seq < 2))
+            return fail(KB_ERR_INVALID, "streaming kernel: flagged words need the round word and a chain position in 1..255 "
+                                        "(2.. for flagged activations)");
+        if (a.y_flagged && (!a.y || a.acc || (reinterpret_cast<uintptr_t>(a.y) & 7)))
+            return fail(KB_ERR_INVALID, "streaming kernel: flagged outputs need an 8-byte aligned y and no accumulator output");
+        if (a.xf && ((L->k % 4) || (a.ldxf % 2) || a.ldxf < L->k || (reinterpret_cast<uintptr_t>(a.xf) & 15)))
+            return fail(KB_ERR_UNSUPPORTED, "streaming kernel: flagged activations need K %% 4 == 0, 16-byte aligned rows, ld >= K");
+    }
+    if (!a.x && !a.xf) {
         if (!a.xq || !a.sx || !a.sumq) return fail(KB_ERR_INVALID, "streaming kernel: needs activations");
         if ((reinterpret_cast<uintptr_t>(a.xq) & 15) || (a.ldq % 16) || a.ldq < L->kp)
             return fail(KB_ERR_INVALID, "gemv: xq must be 16-byte aligned with ldq >= %zu and ldq %% 16 == 0", L->kp);
@@ -884,13 +1080,19 @@ int launch_gemv_stream(const FwdArgs &a, cudaStream_t stream) {
     p.status = L->dev_status;
     p.sync = PeerSync{};
     if (a.sync && a.y) p.sync = *a.sync;
+    p.xf = reinterpret_cast<const uint2 *>(a.xf);
+    p.ldxf = a.ldxf;
+    p.y_flagged = a.y_flagged ? 1 : 0;
+    p.flag_round = a.flag_round;
+    p.flag_seq = a.flag_seq;
+    if (flagged) p.sync = PeerSync{};  // the pairs replace the flag arrays: no fence-and-flag wait or publication
     const int gp = plan.warps / plan.ks;
     int grid = (p.row_blocks + gp - 1) / gp;
     const int sms = sm_count(L->device);
     if (grid > sms) grid = sms;
     const size_t smem = BAR_BYTES + (size_t)plan.warps * p.nst * STAGE_BYTES + (size_t)p.x_rows * p.xs_stride + plan.part_bytes;
     if (a.n == 1) return launch_stream<1, false, 1, 16>(p, L->device, grid, plan.warps, smem, stream);
-    if (a.n == 2) return launch_stream<1, false, 2, 12>(p, L->device, grid, plan.warps, smem, stream);
+    if (a.n == 2 && two_tokens_dp4a(L)) return launch_stream<1, false, 2, 12>(p, L->device, grid, plan.warps, smem, stream);
     if (a.n <= 8) return launch_stream<1, false, 0, 16>(p, L->device, grid, plan.warps, smem, stream);
     if (a.n <= 16) return launch_stream<2, false, 0, 12>(p, L->device, grid, plan.warps, smem, stream);
     return launch_stream<4, false, 0, 8>(p, L->device, grid, plan.warps, smem, stream);

@@ -7,6 +7,8 @@
 //
 // Everything here is HBM-bound byte work: one thread produces one aligned 32-bit word
 // of the destination so stores coalesce; nothing is reshaped into a GEMM.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "device_utils.cuh"
 
@@ -131,10 +133,172 @@ __global__ void __launch_bounds__(256) act_quant_regs_kernel(const float *__rest
     }
 }
 
+// The quantiser for a few tokens of a long row, plain f32 or flagged words ((f32 value, epoch) pairs written by the
+// ranks of a column-sharded layer): a cluster of FQ_CLUSTER CTAs per token, each owning a contiguous part of the row,
+// so that the row is pulled through eight SMs' load paths instead of one.  A thread holds G cells of 16 values in
+// registers; flagged: it waits, bounded, until both pairs of every 16-byte load carry the expected epoch.  The
+// cluster agrees on max|x| and on the code sum through distributed shared memory; the codes equal those of
+// act_quant_kernel bit for bit.  Dependent launches may start at once (they wait for this grid before they read).
+constexpr int FQ_CLUSTER = 8;
+template <int G, bool FLAGGED>
+__global__ void __cluster_dims__(FQ_CLUSTER, 1, 1) __launch_bounds__(256)
+    act_quant_cluster_kernel(const void *__restrict__ xin, size_t ldx, int k, const int *round, int seq, int8_t *__restrict__ xq,
+                             int ldq, float *__restrict__ sx, int32_t *__restrict__ sumq, int *status, long long max_cycles) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float red_f[32];
+    __shared__ int red_i[32];
+    __shared__ float part_max;
+    __shared__ int part_sum;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // flagged: the round word is final, the producer's own stores are done
+    const int t = blockIdx.x / FQ_CLUSTER, part = (int)cluster.block_rank();
+    const int cells = ldq / 16, per_cta = (cells + FQ_CLUSTER - 1) / FQ_CLUSTER;
+    float v[G][16];
+    float amax = 0.0f;
+    if (FLAGGED) {
+        const uint32_t epoch = ((uint32_t)(*reinterpret_cast<const volatile int *>(round)) << 8) | (uint32_t)seq;
+        const uint2 *row = static_cast<const uint2 *>(xin) + (size_t)t * ldx;
+        long long t0 = 0;
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            const int local = threadIdx.x + i * 256;
+            const int c = part * per_cta + local;
+            const bool mine = local < per_cta && c < cells;
+            uint4 raw[8];
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+                const int e = c * 16 + 2 * w;
+                raw[w] = make_uint4(0u, epoch, 0u, epoch);
+                if (mine && e < k)
+                    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(raw[w].x), "=r"(raw[w].y), "=r"(raw[w].z), "=r"(raw[w].w)
+                                 : "l"(row + e)
+                                 : "memory");
+            }
+            for (;;) {
+                bool all = true;
+#pragma unroll
+                for (int w = 0; w < 8; ++w)
+                    if (raw[w].y != epoch || raw[w].w != epoch) {
+                        all = false;
+                        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(raw[w].x), "=r"(raw[w].y), "=r"(raw[w].z), "=r"(raw[w].w)
+                                     : "l"(row + c * 16 + 2 * w)
+                                     : "memory");
+                    }
+                if (all) break;
+                const long long now = clock64();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > max_cycles) { ok = false; break; }
+            }
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+                v[i][2 * w] = __uint_as_float(raw[w].x);
+                v[i][2 * w + 1] = __uint_as_float(raw[w].z);
+            }
+        }
+        if (!ok) atomicCAS(status, 0, 110);
+    } else {
+        const float *row = static_cast<const float *>(xin) + (size_t)t * ldx;
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            const int local = threadIdx.x + i * 256;
+            const int c = part * per_cta + local;
+            const bool mine = local < per_cta && c < cells;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const int e = c * 16 + 4 * w;
+                const float4 f = (mine && e < k) ? *reinterpret_cast<const float4 *>(row + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[i][4 * w] = f.x; v[i][4 * w + 1] = f.y; v[i][4 * w + 2] = f.z; v[i][4 * w + 3] = f.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < G; ++i)
+#pragma unroll
+        for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[i][e]));
+    amax = block_reduce_max(amax, red_f);
+    if (threadIdx.x == 0) part_max = amax;
+    cluster.sync();
+    amax = 0.0f;
+#pragma unroll
+    for (int r = 0; r < FQ_CLUSTER; ++r) amax = fmaxf(amax, *cluster.map_shared_rank(&part_max, r));
+    const float s = amax < 1e-8f ? 1.0f : __fdiv_rn(amax, 127.0f);
+    const float rs = __frcp_rn(s);
+    int local_sum = 0;
+    int8_t *qrow = xq + (size_t)t * ldq;
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+        const int local = threadIdx.x + i * 256;
+        const int c = part * per_cta + local;
+        if (local < per_cta && c < cells) {
+            uint32_t out[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const int q0 = quantise_one_fast(v[i][4 * w], s, rs), q1 = quantise_one_fast(v[i][4 * w + 1], s, rs);
+                const int q2 = quantise_one_fast(v[i][4 * w + 2], s, rs), q3 = quantise_one_fast(v[i][4 * w + 3], s, rs);
+                local_sum += q0 + q1 + q2 + q3;
+                out[w] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+            }
+            *reinterpret_cast<uint4 *>(qrow + c * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+    }
+    local_sum = block_reduce_sum(local_sum, red_i);
+    if (threadIdx.x == 0) part_sum = local_sum;
+    cluster.sync();
+    if (part == 0 && threadIdx.x == 0) {
+        int total = 0;
+#pragma unroll
+        for (int r = 0; r < FQ_CLUSTER; ++r) total += *cluster.map_shared_rank(&part_sum, r);
+        sx[t] = s;
+        if (sumq) sumq[t] = total;
+    }
+    cluster.sync();  // no CTA leaves while its shared memory may still be read
+}
+
+template <bool FLAGGED>
+static int launch_act_quant_cluster(const void *x, size_t ldx, size_t n, size_t k, const int *round, int seq, int8_t *xq, size_t ldq,
+                                    float *sx, int32_t *sumq, int *status, cudaStream_t stream) {
+    const size_t per_cta = (ldq / 16 + FQ_CLUSTER - 1) / FQ_CLUSTER;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(n * FQ_CLUSTER), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = FLAGGED ? 1 : 0;  // the flagged form may start behind its producer; the plain form reads finished data
+    const int ki = (int)k, ldqi = (int)ldq;
+    const long long cycles = 2000000000ll;
+    cudaError_t e;
+    if (per_cta <= 256)
+        e = cudaLaunchKernelEx(&cfg, act_quant_cluster_kernel<1, FLAGGED>, x, ldx, ki, round, seq, xq, ldqi, sx, sumq, status, cycles);
+    else if (per_cta <= 512)
+        e = cudaLaunchKernelEx(&cfg, act_quant_cluster_kernel<2, FLAGGED>, x, ldx, ki, round, seq, xq, ldqi, sx, sumq, status, cycles);
+    else
+        e = cudaLaunchKernelEx(&cfg, act_quant_cluster_kernel<4, FLAGGED>, x, ldx, ki, round, seq, xq, ldqi, sx, sumq, status, cycles);
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "cluster quantiser launch");
+}
+
+int launch_act_quant_flagged(const unsigned long long *x, size_t ldx, size_t n, size_t k, const int *round, int seq, int8_t *xq,
+                             size_t ldq, float *sx, int32_t *sumq, int *status, cudaStream_t stream) {
+    if (n == 0) return KB_OK;
+    if ((k % 4) || (ldx % 2) || ldx < k || (reinterpret_cast<uintptr_t>(x) & 15) || (ldq % 16) || ldq < k)
+        return fail(KB_ERR_UNSUPPORTED, "flagged quantiser: K %% 4 == 0, 16-byte aligned rows and ld >= K are required");
+    if ((ldq / 16 + FQ_CLUSTER - 1) / FQ_CLUSTER > 4 * 256) return fail(KB_ERR_UNSUPPORTED, "flagged quantiser: K=%zu too large", k);
+    return launch_act_quant_cluster<true>(x, ldx, n, k, round, seq, xq, ldq, sx, sumq, status, stream);
+}
+
 int launch_act_quant(const float *x, size_t n, size_t k, int8_t *xq, size_t ldq, float *sx,
                      int32_t *sumq, cudaStream_t stream) {
     if (n == 0) return KB_OK;
     const bool vec4 = (k % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    // a few tokens of a long row: one CTA per token would pull the row through a single SM
+    if (vec4 && n <= 16 && k >= 4096 && (ldq % 16) == 0 && (ldq / 16 + FQ_CLUSTER - 1) / FQ_CLUSTER <= 4 * 256)
+        return launch_act_quant_cluster<false>(x, k, n, k, nullptr, 0, xq, ldq, sx, sumq, nullptr, stream);
     if (vec4 && ldq <= 4 * 4096) {
         const unsigned grid = (unsigned)n;
         if (ldq <= 4096) act_quant_regs_kernel<1><<<grid, 256, 0, stream>>>(x, (int)k, xq, (int)ldq, sx, sumq);

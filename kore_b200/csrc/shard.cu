@@ -64,6 +64,49 @@ __global__ void peer_wait_kernel(int *const *flag_arrays, int world, int rank, c
     }
 }
 
+// Flagged words -> plain f32, the end of a chain of flagged forwards: every thread waits, bounded, until its two
+// (value, epoch) pairs carry epoch (*round << 8) | seq and stores the two values; the last CTA to finish advances
+// the round (every CTA has read it by then), so the next chain's words differ from everything still in the buffers.
+__global__ void flagged_unpack_kernel(const uint2 *src, size_t ld_src, float *dst, size_t ld_dst, int n, int m, int seq,
+                                      int *round, int *done_counter, int *status, long long max_cycles) {
+    const int r_now = *reinterpret_cast<const volatile int *>(round);
+    const uint32_t epoch = ((uint32_t)r_now << 8) | (uint32_t)seq;
+    const int pairs = (m + 1) / 2;
+    const long long total = (long long)n * pairs;
+    bool ok = true;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / pairs), c = (int)(i - (long long)r * pairs) * 2;
+        const uint2 *s = src + (size_t)r * ld_src + c;
+        const bool two = c + 1 < m;
+        uint32_t v0, f0, v1 = 0, f1 = epoch;
+        long long t0 = 0;
+        for (;;) {
+            if (two) {
+                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v0), "=r"(f0), "=r"(v1), "=r"(f1) : "l"(s) : "memory");
+            } else {
+                asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v0), "=r"(f0) : "l"(s) : "memory");
+            }
+            if (f0 == epoch && f1 == epoch) break;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > max_cycles) { ok = false; break; }
+        }
+        float *d = dst + (size_t)r * ld_dst + c;
+        d[0] = __uint_as_float(v0);
+        if (two) d[1] = __uint_as_float(v1);
+    }
+    if (!ok) atomicCAS(status, 0, 110);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int ticket = atomicAdd(done_counter, 1);
+        if (ticket == (int)gridDim.x - 1) {
+            *done_counter = 0;
+            __threadfence();
+            *reinterpret_cast<volatile int *>(round) = (r_now + 1) & 0xffffff;
+        }
+    }
+}
+
 }  // namespace kb
 
 using namespace kb;
@@ -246,6 +289,124 @@ int kb_linear_forward_sharded_chain_q8(const kb_linear *h, const int8_t *xq, siz
     if (!xq || !sx || !sumq || !flag_arrays_dev || !sync_words_dev) return fail(KB_ERR_INVALID, "null pointer");
     return sharded_forward(h, nullptr, xq, ldq, sx, sumq, n, L->k, y_bases, world, rank, m_total, col_offset, KB_PATH_AUTO,
                            nullptr, 0, flag_arrays_dev, sync_words_dev, stream, true);
+}
+
+// Flagged exchange: the slice goes into every rank's buffer as (value, epoch) pairs; nothing waits in the producer
+// and nothing is fenced.  x is plain f32, the flagged output of the previous forward of the chain, or pre-quantised.
+// sync words: [2] status, [3] round of the flagged chains, [4] CTA counter of the unpack.
+static int sharded_flagged(const kb_linear *h, const void *x, int x_is_flagged, size_t ldx, const int8_t *xq, size_t ldq,
+                           const float *sx, const int32_t *sumq, size_t n, unsigned long long *const *y_bases, int world,
+                           int rank, size_t m_total, size_t col_offset, int seq, int fuse, void *workspace,
+                           size_t workspace_bytes, int *sync_words_dev, kb_stream stream) {
+    const Linear *L = reinterpret_cast<const Linear *>(h);
+    if (!L || L->magic != HANDLE_MAGIC) return fail(KB_ERR_BAD_HANDLE, "null or destroyed kb_linear handle");
+    if (!y_bases || !sync_words_dev || (!x && !(xq && sx && sumq))) return fail(KB_ERR_INVALID, "null pointer");
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world)
+        return fail(KB_ERR_INVALID, "world %d / rank %d outside 1..%d", world, rank, MAX_PEERS);
+    if (seq < 1 || seq > 255 || (x_is_flagged && seq < 2))
+        return fail(KB_ERR_INVALID, "chain position %d outside 1..255 (a forward on flagged activations is at least the second)", seq);
+    if (col_offset + L->m > m_total)
+        return fail(KB_ERR_SHAPE, "slice [%zu, %zu) does not fit in %zu output features", col_offset, col_offset + L->m, m_total);
+    if (n == 0) return KB_OK;
+    for (int q = 0; q < world; ++q)
+        if (!y_bases[q]) return fail(KB_ERR_INVALID, "null output base for rank %d", q);
+    if (!gemv_stream_supports(L, n))
+        return fail(KB_ERR_UNSUPPORTED, "flagged exchange: %zu tokens x K=%zu do not fit the streaming kernel", n, L->k);
+    if (!xq && !x_is_flagged && ldx && ldx != L->k)
+        return fail(KB_ERR_UNSUPPORTED, "flagged exchange: plain f32 activations must be dense rows");
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (prev != L->device && (e = cudaSetDevice(L->device)) != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    FwdArgs a = {};
+    a.lin = L; a.n = n; a.ldy = m_total;
+    a.y = reinterpret_cast<float *>(y_bases[rank] + col_offset);
+    a.n_more = 0;
+    for (int q = 0; q < world; ++q)
+        if (q != rank) a.y_more[a.n_more++] = reinterpret_cast<float *>(y_bases[q] + col_offset);
+    a.y_flagged = true;
+    a.flag_round = sync_words_dev + 3;
+    a.flag_seq = seq;
+    int rc = KB_OK;
+    uint8_t *ws = nullptr;
+    bool own = false;
+    // flagged activations: the kernel's own prologue waits for them and quantises (every CTA reads the whole row:
+    // short rows only), or a cluster kernel does it once for all CTAs
+    const bool separate = x_is_flagged && (fuse == 2 || (fuse == 0 && (L->kp > 4096 || n > 2)));
+    if (xq) {
+        a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq;
+    } else if (separate) {
+        const size_t xq_bytes = (n * L->kp + 255) / 256 * 256, vec_bytes = (n * 4 + 255) / 256 * 256;
+        const size_t need = xq_bytes + 2 * vec_bytes;
+        ws = static_cast<uint8_t *>(workspace);
+        if (!ws) {
+            e = cudaMallocAsync(reinterpret_cast<void **>(&ws), need, st);
+            if (e != cudaSuccess) rc = cuda_fail(e, "workspace allocation");
+            own = true;
+        } else if (workspace_bytes < 2 * need || (reinterpret_cast<uintptr_t>(ws) & 255)) {
+            rc = fail(KB_ERR_STORAGE, "workspace too small or misaligned: need %zu bytes (two halves), got %zu", 2 * need, workspace_bytes);
+        } else {
+            ws += (size_t)(seq & 1) * need;  // consecutive links never share a half
+        }
+        if (rc == KB_OK) {
+            int8_t *wq = reinterpret_cast<int8_t *>(ws);
+            float *wsx = reinterpret_cast<float *>(ws + xq_bytes);
+            int32_t *wsum = reinterpret_cast<int32_t *>(ws + xq_bytes + vec_bytes);
+            rc = launch_act_quant_flagged(static_cast<const unsigned long long *>(x), ldx ? ldx : L->k, n, L->k, sync_words_dev + 3,
+                                          seq - 1, wq, L->kp, wsx, wsum, sync_words_dev + 2, st);
+            a.xq = wq; a.ldq = L->kp; a.sx = wsx; a.sumq = wsum;
+        }
+    } else if (x_is_flagged) {
+        a.xf = static_cast<const unsigned long long *>(x);
+        a.ldxf = ldx ? ldx : L->k;
+    } else {
+        a.x = static_cast<const float *>(x);
+    }
+    if (rc == KB_OK) rc = launch_gemv_stream(a, st);
+    if (own && ws) cudaFreeAsync(ws, st);
+    if (prev != L->device) cudaSetDevice(prev);
+    return rc;
+}
+
+int kb_linear_forward_sharded_flagged(const kb_linear *h, const void *x, int x_is_flagged, size_t ldx, size_t n, size_t in_dim,
+                                      unsigned long long *const *y_bases, int world, int rank, size_t m_total, size_t col_offset,
+                                      int seq, int fuse, void *workspace, size_t workspace_bytes, int *sync_words_dev,
+                                      kb_stream stream) {
+    const Linear *L = reinterpret_cast<const Linear *>(h);
+    if (!L || L->magic != HANDLE_MAGIC) return fail(KB_ERR_BAD_HANDLE, "null or destroyed kb_linear handle");
+    if (!x) return fail(KB_ERR_INVALID, "null pointer");
+    if (in_dim != L->k) return fail(KB_ERR_SHAPE, "shape mismatch: expected [%zu], got last dimension %zu", L->k, in_dim);
+    if (fuse < 0 || fuse > 2) return fail(KB_ERR_INVALID, "fuse must be 0 (automatic), 1 (prologue) or 2 (separate quantiser)");
+    return sharded_flagged(h, x, x_is_flagged, ldx, nullptr, 0, nullptr, nullptr, n, y_bases, world, rank, m_total, col_offset, seq,
+                           fuse, workspace, workspace_bytes, sync_words_dev, stream);
+}
+
+int kb_linear_forward_sharded_flagged_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const float *sx, const int32_t *sumq,
+                                         size_t n, unsigned long long *const *y_bases, int world, int rank, size_t m_total,
+                                         size_t col_offset, int seq, int *sync_words_dev, kb_stream stream) {
+    if (!xq || !sx || !sumq) return fail(KB_ERR_INVALID, "null pointer");
+    return sharded_flagged(h, nullptr, 0, 0, xq, ldq, sx, sumq, n, y_bases, world, rank, m_total, col_offset, seq, 0, nullptr, 0,
+                           sync_words_dev, stream);
+}
+
+int kb_flagged_unpack(const unsigned long long *src, size_t ld_src, size_t n, size_t m, float *dst, size_t ld_dst, int seq,
+                      int *sync_words_dev, kb_stream stream) {
+    if (!src || !dst || !sync_words_dev) return fail(KB_ERR_INVALID, "null pointer");
+    if (seq < 1 || seq > 255) return fail(KB_ERR_INVALID, "chain position %d outside 1..255", seq);
+    if ((reinterpret_cast<uintptr_t>(src) & 15) || (ld_src % 2) || ld_src < m || ld_dst < m)
+        return fail(KB_ERR_INVALID, "flagged rows must be 16-byte aligned with an even leading dimension >= %zu", m);
+    if (n == 0 || m == 0) return KB_OK;
+    if (n > (size_t)1 << 20 || m > (size_t)1 << 30) return fail(KB_ERR_UNSUPPORTED, "flagged unpack: %zu x %zu too large", n, m);
+    const long long work = (long long)n * (long long)((m + 1) / 2);
+    const int threads = 256;
+    long long blocks = (work + threads - 1) / threads;
+    if (blocks > 1184) blocks = 1184;
+    flagged_unpack_kernel<<<(unsigned)blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint2 *>(src), ld_src, dst, ld_dst, (int)n, (int)m, seq, sync_words_dev + 3, sync_words_dev + 4,
+        sync_words_dev + 2, 2000000000ll);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "flagged unpack launch");
 }
 
 }  // extern "C"

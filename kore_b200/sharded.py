@@ -95,8 +95,12 @@ class ShardContext:
         self.lib = _cabi.lib()
         self.epoch = 0
         torch.cuda.set_device(device)
-        self.y_bytes = max_tokens * m_total * 4
-        total = 2 * self.y_bytes + 256
+        self.y_bytes = (max_tokens * m_total * 4 + 255) // 256 * 256
+        # flagged exchange (a few tokens): two buffers of [flagged_tokens, m_total] 8-byte (value, epoch) words
+        self.flagged_tokens = min(max_tokens, 32)
+        self.f_bytes = (self.flagged_tokens * m_total * 8 + 255) // 256 * 256
+        self.f_offset = 2 * self.y_bytes + 256
+        total = self.f_offset + 2 * self.f_bytes
         base = C.c_void_p()
         _cabi.check(self.lib.kb_symm_alloc(total, C.byref(base)))
         self.local_base = base.value
@@ -119,8 +123,12 @@ class ShardContext:
         self.y_tables = [torch.tensor(t, dtype=torch.int64, device=dev) for t in ybases]
         self.y_tables_host = [(C.c_void_p * world)(*t) for t in ybases]
         self.flag_table = torch.tensor([b + 2 * self.y_bytes for b in self.peer_bases], dtype=torch.int64, device=dev)
-        # {epoch counter, CTA-done counter, status}
-        self.sync_words = torch.zeros(3, dtype=torch.int32, device=dev)
+        self.f_tables_host = [(C.c_void_p * world)(*[b + self.f_offset + par * self.f_bytes for b in self.peer_bases])
+                              for par in range(2)]
+        # {epoch counter, CTA-done counter, status, round of the flagged chains, CTA counter of the unpack, spare}
+        self.sync_words = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.flag_seq = 0  # position of the last flagged forward in its chain (0: no chain open)
+        self.flag_ws = None
         self.epoch_counter = self.sync_words[0:1]
         self.status = self.sync_words[2:3]
         self.local_y = [torch.as_tensor(_DevView(self.local_base + par * self.y_bytes, (max_tokens, m_total), "<f4"),
@@ -153,6 +161,40 @@ class ShardContext:
         chain of ``forward_chain_q8`` calls before the last output is read."""
         _cabi.check(self.lib.kb_peer_wait(self.flag_table.data_ptr(), self.world, self.rank, self.epoch_counter.data_ptr(),
                                           self.status.data_ptr(), stream_ptr))
+
+    def local_flagged(self, par: int, n: int, m: int):
+        """This rank's flagged buffer of the given parity as an int64 tensor [n, m] (value bits in the low half of
+        every word, epoch in the high half)."""
+        import torch
+
+        return torch.as_tensor(_DevView(self.local_base + self.f_offset + par * self.f_bytes, (n, m), "<i8"),
+                               device=torch.device("cuda", self.device))
+
+    def flagged_workspace(self, n: int, kp: int):
+        """(pointer, bytes) of the two-half scratch of the separate flagged quantiser, grown on demand."""
+        import torch
+
+        need = 2 * ((n * kp + 255) // 256 * 256 + 2 * ((4 * n + 255) // 256 * 256))
+        if self.flag_ws is None or self.flag_ws.numel() < need:  # sized generously once, so that it rarely moves
+            self.flag_ws = torch.empty(max(need, 4 << 20), dtype=torch.uint8, device=torch.device("cuda", self.device))
+        return self.flag_ws.data_ptr(), self.flag_ws.numel()
+
+    def unpack(self, flagged, stream_ptr: Optional[int] = None, out=None):
+        """Ends a chain of flagged forwards: flagged words [n, m] (the view the last one returned) -> plain f32
+        [n, m]; waits on the stream, bounded, until every rank's slice has arrived."""
+        import torch
+
+        n, m = flagged.shape
+        if self.flag_seq < 1:
+            raise _cabi.KoreError(_cabi.ERR_INVALID, "no flagged forward to unpack")
+        if out is None:
+            out = torch.empty((n, m), dtype=torch.float32, device=flagged.device)
+        if stream_ptr is None:
+            stream_ptr = torch.cuda.current_stream(self.device).cuda_stream
+        _cabi.check(self.lib.kb_flagged_unpack(flagged.data_ptr(), flagged.stride(0), n, m, out.data_ptr(), out.stride(0),
+                                               self.flag_seq, self.sync_words.data_ptr(), stream_ptr))
+        self.flag_seq = 0
+        return out
 
     def check_status(self):
         code = int(self.status.item())
@@ -236,6 +278,52 @@ class ShardedLinear:
             self.layer.handle, xq.data_ptr(), xq.stride(0), sx.data_ptr(), sumq.data_ptr(), n, ctx.y_tables_host[par],
             self.world, self.rank, self.m_total, self.start, ctx.flag_table.data_ptr(), ctx.sync_words.data_ptr(), stream_ptr))
         return ctx.local_y[par][:n]
+
+    def forward_flagged(self, x, x_is_flagged: bool = False, stream_ptr: Optional[int] = None, fuse: int = 0):
+        """One link of a chain of dependent sharded layers (1..8 tokens) on the flagged exchange.  The first link
+        takes plain f32 x [N, K]; every later one the flagged view the previous link returned (any layer of the
+        same context).  The result is this rank's flagged buffer [N, M]: feed it to the next link, or end the
+        chain with ``ctx.unpack``.  Nothing waits in the producer; the consumer waits per word, behind its own
+        weight stream (fuse: 0 automatic, 1 in the forward kernel's prologue, 2 in a separate cluster kernel)."""
+        import torch
+
+        ctx, n = self.ctx, x.shape[0]
+        if self.exchange != "p2p" or ctx is None:
+            raise _cabi.KoreError(_cabi.ERR_UNSUPPORTED, "forward_flagged uses the p2p exchange")
+        if n > ctx.flagged_tokens or self.m_total > ctx.m_total or self.m_total % 2:
+            raise _cabi.KoreError(_cabi.ERR_UNSUPPORTED, "tokens or features exceed the shard context's flagged buffers")
+        if bool(x_is_flagged) != (ctx.flag_seq >= 1):
+            raise _cabi.KoreError(_cabi.ERR_INVALID, "a chain starts on plain activations and continues on flagged ones")
+        if stream_ptr is None:
+            stream_ptr = torch.cuda.current_stream(ctx.device).cuda_stream
+        ws, ws_bytes = ctx.flagged_workspace(n, (self.k + 127) // 128 * 128) if x_is_flagged else (None, 0)
+        par = ctx.next_parity()  # consecutive flagged forwards, across chains too, alternate between the two buffers
+        _cabi.check(ctx.lib.kb_linear_forward_sharded_flagged(
+            self.layer.handle, x.data_ptr(), 1 if x_is_flagged else 0, x.stride(0), n, self.k, ctx.f_tables_host[par],
+            self.world, self.rank, self.m_total, self.start, ctx.flag_seq + 1, fuse, ws, ws_bytes, ctx.sync_words.data_ptr(),
+            stream_ptr))
+        ctx.flag_seq += 1
+        return ctx.local_flagged(par, n, self.m_total)
+
+    def forward_flagged_q8(self, xq, sx, sumq, stream_ptr: Optional[int] = None):
+        """First link of a flagged chain on activations that are already quantised (up to 32 tokens)."""
+        import torch
+
+        ctx, n = self.ctx, xq.shape[0]
+        if self.exchange != "p2p" or ctx is None:
+            raise _cabi.KoreError(_cabi.ERR_UNSUPPORTED, "forward_flagged_q8 uses the p2p exchange")
+        if n > ctx.flagged_tokens or self.m_total > ctx.m_total or self.m_total % 2:
+            raise _cabi.KoreError(_cabi.ERR_UNSUPPORTED, "tokens or features exceed the shard context's flagged buffers")
+        if ctx.flag_seq:
+            raise _cabi.KoreError(_cabi.ERR_INVALID, "pre-quantised activations start a chain: unpack the open one first")
+        if stream_ptr is None:
+            stream_ptr = torch.cuda.current_stream(ctx.device).cuda_stream
+        par = ctx.next_parity()
+        _cabi.check(ctx.lib.kb_linear_forward_sharded_flagged_q8(
+            self.layer.handle, xq.data_ptr(), xq.stride(0), sx.data_ptr(), sumq.data_ptr(), n, ctx.f_tables_host[par],
+            self.world, self.rank, self.m_total, self.start, 1, ctx.sync_words.data_ptr(), stream_ptr))
+        ctx.flag_seq = 1
+        return ctx.local_flagged(par, n, self.m_total)
 
     def _local_forward(self, x, n, smax, path, stream_ptr):
         """This rank's slice of the output in a [N, smax] staging block (columns beyond the slice stay zero)."""

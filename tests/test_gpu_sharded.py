@@ -78,6 +78,45 @@ def _rank_main(rank, world, port, q):
                         dist.barrier()
         ctx.check_status()
         ctx.close()
+        # flagged exchange: a dependent chain 1000 -> 640 -> 1000 -> 640 ... in which every link reads the previous
+        # link's (value, epoch) words and waits per word; one unpack at the end; against the oracle's chain
+        m, k = 640, 1000
+        ctx = sharded.ShardContext(rank, world, max(m, k), 8, rank, dist)
+        kind = kbref.TERNARY
+        wa, wb = cases.gaussian(31, (m, k), 0.02), cases.gaussian(32, (k, m), 0.02)
+        pa, sa = cases.make_weights(kind, "absmean", wa)
+        pb, sb = cases.make_weights(kind, "absmean", wb)
+        la = sharded.ShardedLinear(kind, pa, sa, None, k, m, rank, world, device=rank, ctx=ctx, dist=dist)
+        lb = sharded.ShardedLinear(kind, pb, sb, None, m, k, rank, world, device=rank, ctx=ctx, dist=dist)
+        for n in (1, 2, 3, 8):
+            for rep in range(2):
+                x = cases.gaussian(700 + 10 * n + rep, (n, k), 1.0)
+                ref = x
+                fuse = 1 + rep  # the wait in the forward kernel's prologue / in the separate cluster quantiser
+                f = la.forward_flagged(torch.from_numpy(x).cuda())
+                ref = kbref.q_forward(kind, pa, sa, None, m, k, ref, threads=2)[0]
+                for link in range(3):
+                    f = lb.forward_flagged(f, x_is_flagged=True, fuse=fuse)
+                    ref = kbref.q_forward(kind, pb, sb, None, k, m, ref, threads=2)[0]
+                    f = la.forward_flagged(f, x_is_flagged=True, fuse=fuse)
+                    ref = kbref.q_forward(kind, pa, sa, None, m, k, ref, threads=2)[0]
+                y = ctx.unpack(f)
+                torch.cuda.synchronize()
+                if not bool((y.cpu().numpy() == ref).all()):
+                    ok = False
+                    msgs.append(f"rank {rank} flagged chain n={n} rep={rep} differs")
+            # stand-alone: pre-quantised input, unpack after every forward
+            x = cases.gaussian(800 + n, (n, k), 1.0)
+            xq, sx, sumq = kernels.quantize_act_i8(torch.from_numpy(x).cuda())
+            y_ref = kbref.q_forward(kind, pa, sa, None, m, k, x, threads=2)[0]
+            for rep in range(4):
+                y = ctx.unpack(la.forward_flagged_q8(xq, sx, sumq))
+                torch.cuda.synchronize()
+                if not bool((y.cpu().numpy() == y_ref).all()):
+                    ok = False
+                    msgs.append(f"rank {rank} flagged q8 n={n} rep={rep} differs")
+        ctx.check_status()
+        ctx.close()
     except Exception as exc:  # report instead of hanging the peers
         ok = False
         msgs.append(f"rank {rank}: {exc!r}")
@@ -105,3 +144,80 @@ def test_sharded_forward_two_gpus():
     [p.join(timeout=120) for p in procs]
     for rank, ok, msgs in results:
         assert ok, msgs
+
+
+@pytest.mark.parametrize("k,m", [(1000, 640), (8192, 384), (28672, 96)])
+def test_flagged_words_single_rank(k, m):
+    """The flagged form with one rank (no peers): the producer writes (value, epoch) words, the next forward's
+    prologue waits for them per word and quantises them, the unpack strips them; every step against the oracle.
+    Covers both forms of the flagged prologue (one cell per thread held in registers; rows read twice)."""
+    import ctypes as C
+
+    import torch
+
+    from kore_b200 import _cabi, nn
+
+    lib = _cabi.lib()
+    kind = kbref.TERNARY
+    wa, wb = cases.gaussian(41, (m, k), 0.02), cases.gaussian(42, (k, m), 0.02)
+    pa, sa = cases.make_weights(kind, "absmean", wa)
+    pb, sb = cases.make_weights(kind, "absmean", wb)
+    ba = cases.gaussian(43, (m,), 0.1)
+    la = nn.BitLinear.from_packed(pa, sa, ba, k, m, device=0)
+    lb = nn.BitLinear.from_packed(pb, sb, None, m, k, device=0)
+    dev = torch.device("cuda", 0)
+    sync = torch.zeros(8, dtype=torch.int32, device=dev)
+    sp = torch.cuda.current_stream().cuda_stream
+    for n in ((1, 2, 5, 8) if k <= 8192 else (1, 2, 3)):  # staged activation rows must fit in shared memory
+        fa = torch.zeros((n, m), dtype=torch.int64, device=dev)
+        fb = torch.zeros((n, k), dtype=torch.int64, device=dev)
+        x = cases.gaussian(500 + n, (n, k), 1.0)
+        xd = torch.from_numpy(x).cuda()
+
+        for fuse in (1, 2):  # the wait in the forward kernel's prologue / in the separate cluster quantiser
+            seq = [0]
+
+            def fwd(layer, src, flagged_in, dst, in_dim, out_dim):
+                table = (C.c_void_p * 1)(dst.data_ptr())
+                seq[0] += 1
+                _cabi.check(lib.kb_linear_forward_sharded_flagged(layer.handle, src.data_ptr(), 1 if flagged_in else 0,
+                                                                  src.stride(0), n, in_dim, table, 1, 0, out_dim, 0, seq[0],
+                                                                  fuse, None, 0, sync.data_ptr(), sp))
+
+            round_before = int(sync[3].item())
+            fwd(la, xd, False, fa, k, m)
+            ref = kbref.q_forward(kind, pa, sa, ba, m, k, x, threads=2)[0]
+            for link in range(2):
+                fwd(lb, fa, True, fb, m, k)
+                ref = kbref.q_forward(kind, pb, sb, None, k, m, ref, threads=2)[0]
+                fwd(la, fb, True, fa, k, m)
+                ref = kbref.q_forward(kind, pa, sa, ba, m, k, ref, threads=2)[0]
+            y = torch.empty((n, m), dtype=torch.float32, device=dev)
+            _cabi.check(lib.kb_flagged_unpack(fa.data_ptr(), fa.stride(0), n, m, y.data_ptr(), m, seq[0], sync.data_ptr(), sp))
+            torch.cuda.synchronize()
+            assert int(sync[2].item()) == 0
+            assert int(sync[3].item()) == round_before + 1  # the unpack advanced the round
+            words = fa.cpu().numpy()
+            assert ((words >> 32) & 0xffffffff == ((round_before << 8) | seq[0])).all()  # every word carries its epoch
+            assert (y.cpu().numpy() == ref).all(), f"n={n} fuse={fuse}"
+    for lay in (la, lb):
+        st = C.c_int(-1)
+        assert lib.kb_linear_last_device_status(lay.handle, None, C.byref(st)) == 0 and st.value == 0, st.value
+
+
+def test_flagged_unpack_reports_a_word_that_never_arrives():
+    """A flag that nothing sets: the bounded wait ends with the status code, the context stays usable."""
+    import torch
+
+    from kore_b200 import _cabi
+
+    lib = _cabi.lib()
+    dev = torch.device("cuda", 0)
+    sync = torch.zeros(8, dtype=torch.int32, device=dev)
+    f = torch.zeros((1, 64), dtype=torch.int64, device=dev)  # holds epoch 0; the unpack expects (0 << 8) | 1
+    y = torch.empty((1, 64), dtype=torch.float32, device=dev)
+    _cabi.check(lib.kb_flagged_unpack(f.data_ptr(), 64, 1, 64, y.data_ptr(), 64, 1, sync.data_ptr(),
+                                      torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert int(sync[2].item()) == 110
+    assert float((torch.ones(4, device=dev) * 2).sum().item()) == 8.0
