@@ -737,7 +737,8 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
     sp = stream.cuda_stream
     link_gbs = 770.0  # measured peer-copy bandwidth per direction on this pool
     out = {"world": world, "shard_copies": copies, "layer": "ternary 8192 -> 28672, absmean", "exchange": "p2p = epilogue peer "
-           "stores over NVLink + flag barrier; nccl = local slice then all_gather_into_tensor",
+           "stores over NVLink + fence + flag barrier; flagged = (value, epoch) words + unpack, no fence or barrier (the "
+           "library's default up to 8 tokens); nccl = local slice then all_gather_into_tensor",
            "matches_unsharded": True}
     for nb in (1, 8, 64, 512):
         x_host = gaussian(5002, (nb, k), 1.0)
@@ -758,6 +759,9 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
             y_chk = np.zeros((nb, m), np.float32)
             _cabi.check(lib.kb_linear_forward_host(full.handle, x_host.ctypes.data, nb, k, y_chk.ctypes.data))
         dist.barrier()
+
+        for lay in layers:
+            lay.use_flagged = False  # the fence-and-flag form first; the flagged form (the default up to 8 tokens) below
 
         def step_p2p():
             for lay in layers:
@@ -800,6 +804,8 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
             entry["chain_matches_unsharded"] = ok_chain
             if rank == 0:
                 out["matches_unsharded"] = out["matches_unsharded"] and ok_chain
+        for lay in layers:
+            lay.use_flagged = True
         # flagged exchange (up to 32 pre-quantised tokens): every value crosses NVLink as an 8-byte (value, epoch)
         # word, nothing is fenced and the producer does not wait; the unpack that follows every forward waits per
         # word and leaves the plain y [nb, m] on every rank

@@ -69,6 +69,10 @@ __global__ void peer_wait_kernel(int *const *flag_arrays, int world, int rank, c
 // the round (every CTA has read it by then), so the next chain's words differ from everything still in the buffers.
 __global__ void flagged_unpack_kernel(const uint2 *src, size_t ld_src, float *dst, size_t ld_dst, int n, int m, int seq,
                                       int *round, int *done_counter, int *status, long long max_cycles) {
+    // the next launch may start (it waits for this grid before it reads anything); this one waits for the forward
+    // before it, and with it for the previous chain's unpack, whose update of the round is then visible
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int r_now = *reinterpret_cast<const volatile int *>(round);
     const uint32_t epoch = ((uint32_t)r_now << 8) | (uint32_t)seq;
     const int pairs = (m + 1) / 2;
@@ -402,10 +406,17 @@ int kb_flagged_unpack(const unsigned long long *src, size_t ld_src, size_t n, si
     const int threads = 256;
     long long blocks = (work + threads - 1) / threads;
     if (blocks > 1184) blocks = 1184;
-    flagged_unpack_kernel<<<(unsigned)blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const uint2 *>(src), ld_src, dst, ld_dst, (int)n, (int)m, seq, sync_words_dev + 3, sync_words_dev + 4,
-        sync_words_dev + 2, 2000000000ll);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, flagged_unpack_kernel, reinterpret_cast<const uint2 *>(src), ld_src, dst, ld_dst, (int)n,
+                                       (int)m, seq, sync_words_dev + 3, sync_words_dev + 4, sync_words_dev + 2, 2000000000ll);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "flagged unpack launch");
 }
 

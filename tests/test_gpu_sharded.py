@@ -40,8 +40,9 @@ def _rank_main(rank, world, port, q):
             for exchange in ("p2p", "collective"):
                 lay = sharded.ShardedLinear(kind, packed, scales, bias, k, m, rank, world, device=rank, ctx=ctx,
                                             dist=dist, exchange=exchange)
-                for n in (1, 3, 5, 16, 64, 200):  # GEMV with fused barrier, small-batch kernel, both GEMMs
-                    for rep in range(3):  # repeated calls exercise the double buffering and epochs
+                for n in (1, 3, 5, 16, 64, 200):  # flagged words / GEMV with fused barrier, small-batch kernel, both GEMMs
+                    for rep in range(4):  # repeated calls exercise the double buffering and epochs
+                        lay.use_flagged = rep < 2  # up to 8 tokens: flagged words first, then peer stores + fence + barrier
                         x = cases.gaussian(100 * n + rep, (n, k), 1.0)
                         y = lay.forward(torch.from_numpy(x).cuda())
                         torch.cuda.synchronize()
