@@ -262,7 +262,7 @@ def main():
                     help="headline step: one grouped launch over the pool of independent layers (default), or one "
                          "quantiser + one GEMV launch per layer spread over --streams streams")
     ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "group_4096", "small_batch", "medium_batch", "prefill_up", "prefill_down",
-                             "decode_step", "attn_decode"],
+                             "decode_step", "decode_step_batch16", "attn_decode"],
                     help="run one small case and print its own JSON line (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -548,14 +548,16 @@ def main():
 
 def decoder_case(torch, lib, _cabi, dev, args):
     """Small cases of the decoder kernels for ncu: the persistent decode step on an 8-layer slice of the decoder
-    configuration (batch 1, 512-token prompt), or the batch-16 decode attention kernel on one layer's cache."""
+    configuration (batch 1, 512-token prompt), the graph of separate kernels on a 4-layer slice at batch 16, or the
+    batch-16 decode attention kernel on one layer's cache."""
     from kore_b200 import decoder
 
-    if args.only == "decode_step":
-        cfg = decoder.DecoderConfig(n_layers=8)
+    if args.only in ("decode_step", "decode_step_batch16"):
+        batch = 1 if args.only == "decode_step" else 16
+        cfg = decoder.DecoderConfig(n_layers=8 if batch == 1 else 4)
         weights = decoder.random_weights(cfg, seed=4000, device=dev.index)
-        dec = decoder.BitNetDecoder(cfg, weights, batch=1, device=dev.index)
-        prompt = torch.randint(0, cfg.vocab, (1, 512), generator=torch.Generator().manual_seed(4999)).to(dev)
+        dec = decoder.BitNetDecoder(cfg, weights, batch=batch, device=dev.index)
+        prompt = torch.randint(0, cfg.vocab, (batch, 512), generator=torch.Generator().manual_seed(4999)).to(dev)
         torch.argmax(dec.prefill(prompt), dim=1, out=dec.tokens)
         for _ in range(max(1, args.warmup)):
             dec.decode_step()
@@ -602,7 +604,7 @@ def decoder_case(torch, lib, _cabi, dev, args):
 
 def single_case(torch, lib, _cabi, nn, kernels, dev, args):
     """One kernel on one small case, a handful of eager launches: the command profiled with ncu."""
-    if args.only in ("decode_step", "attn_decode"):
+    if args.only in ("decode_step", "decode_step_batch16", "attn_decode"):
         return decoder_case(torch, lib, _cabi, dev, args)
     shapes = {"gemv_big": (28672, 8192, 1, 3), "gemv_4096": (4096, 4096, 1, 40), "group_4096": (4096, 4096, 1, 40),
               "small_batch": (28672, 8192, 16, 3),

@@ -388,13 +388,17 @@ int kb_attn_decode(const float *q, const float *k_cache, const float *v_cache, c
     if (!q || !k_cache || !v_cache || !lens || !out) return fail(KB_ERR_INVALID, "null pointer");
     if (head_dim < 1 || head_dim > ATT_MAX_HD) return fail(KB_ERR_UNSUPPORTED, "attention: head_dim %d outside 1..%d", head_dim, ATT_MAX_HD);
     if (batch == 0) return KB_OK;
-    // one batch of loads per warp where possible (a CTA covers 8 warps x 4 positions), as long as
-    // the grid stays within a couple of thousand CTAs; splitting needs the caller's scratch
+    // about one wave of CTAs (four are resident per SM): a CTA's start and its split merge are dead time for its
+    // warps, so for many sequences few long CTAs beat many short ones (16 sequences x 32 heads x 576 positions:
+    // 45.6 us with one CTA per head against 52.9 us with three); a split is at least 32 positions (8 warps x 4)
     const size_t bh = batch * (size_t)n_heads;
-    int splits = (lmax + 31) / 32;
-    if (splits > ATT_MAX_SPLITS) splits = ATT_MAX_SPLITS;
+    int dev = 0;
+    KB_CUDA(cudaGetDevice(&dev));
+    const size_t wave = (size_t)sm_count(dev) * 4 * 85 / 100;
+    int splits = (int)((wave + bh - 1) / bh);
+    const int max_splits = (lmax + 31) / 32 < ATT_MAX_SPLITS ? (lmax + 31) / 32 : ATT_MAX_SPLITS;
+    if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
-    while (splits > 1 && bh * (size_t)splits > 2048) splits = (splits + 1) / 2;
     const size_t need = bh * sizeof(int) + 256 + bh * (size_t)splits * (2 + ATT_MAX_HD) * sizeof(float);
     if (splits > 1 && (!scratch || scratch_bytes < need)) splits = 1;
     int *counters = reinterpret_cast<int *>(scratch);
