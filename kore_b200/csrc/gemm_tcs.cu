@@ -77,6 +77,10 @@ struct TcsParams {
     int n_more;
     const float *resid;
     int relu;  // max(y, 0) after the bias
+    // K split over CTAs (layers of few row tiles): work item = (tile, split), a split covers `split_slabs` slabs of K
+    // (a multiple of PKT_SLABS) and stores its raw int32 sums to part[split][n][m]; a second kernel adds them up
+    int splits, split_slabs;
+    int32_t *part;
 };
 
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
@@ -121,12 +125,13 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_kb = p.kp / BK;
-    const int num_st = (num_kb + ST_SLABS - 1) / ST_SLABS;     // stages per output tile
-    const int num_pkt = (num_kb + PKT_SLABS - 1) / PKT_SLABS;  // packed tiles per output tile
+    const int num_kb_all = p.kp / BK;
     const int tiles_n = (p.n + BN - 1) / BN;
     const int tiles_m = (p.m + BM - 1) / BM;
     const int num_tiles = tiles_m * tiles_n;
+    const int num_work = num_tiles * p.splits;  // work item w = tile * splits + split
+    // slabs, stages and packed tiles of split sp (the last split may be shorter; every role derives the same numbers)
+    auto slabs_of = [&](int sp) { return min(p.split_slabs, num_kb_all - sp * p.split_slabs); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
@@ -163,14 +168,17 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         if (lane == 0 && warp == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+                const int tile = w / p.splits, sp = w - tile * p.splits;
                 const int n0 = (tile % tiles_n) * BN;
+                const int num_kb = slabs_of(sp), slab0 = sp * p.split_slabs;
+                const int num_st = (num_kb + ST_SLABS - 1) / ST_SLABS;
                 for (int st = 0; st < num_st; ++st, ++it) {
                     const int s = it % NS;
                     if (!(ok = wait_bar(empty(s), ((it / NS) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_TMA_EMPTY))) break;
                     const int nsl = min(ST_SLABS, num_kb - st * ST_SLABS);
                     mbar_expect_tx(full(s), (uint32_t)(nsl * C::ACT_SLAB));
-                    for (int j = 0; j < nsl; ++j) tma_load_2d(act_addr(s, j), &tmap_x, full(s), (st * ST_SLABS + j) * BK, n0);
+                    for (int j = 0; j < nsl; ++j) tma_load_2d(act_addr(s, j), &tmap_x, full(s), (slab0 + st * ST_SLABS + j) * BK, n0);
                 }
             }
             // every copy this thread issued must have landed before the CTA exits
@@ -183,13 +191,15 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         } else if (lane == 0) {
             uint32_t pt = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+                const int tile = w / p.splits, sp = w - tile * p.splits;
                 const int m0 = (tile / tiles_n) * BM;
+                const int num_pkt = (slabs_of(sp) + PKT_SLABS - 1) / PKT_SLABS, pkt0 = sp * p.split_slabs / PKT_SLABS;
                 for (int k = 0; k < num_pkt; ++k, ++pt) {
                     const int q = pt % PKS;
                     if (!(ok = wait_bar(pk_empty(q), ((pt / PKS) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_TMA_EMPTY))) break;
                     mbar_expect_tx(pk_full(q), PKT_BYTES);  // columns past the row's end arrive as zeros and count
-                    tma_load_2d(pkt_addr(q), &tmap_w, pk_full(q), k * 128, m0);
+                    tma_load_2d(pkt_addr(q), &tmap_w, pk_full(q), (pkt0 + k) * 128, m0);
                 }
             }
             const uint32_t issued = pt;
@@ -206,8 +216,10 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
             const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             uint32_t it = 0, ti = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti) {
+            for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++ti) {
                 const int b = ti & 1;
+                const int num_kb = slabs_of(w % p.splits);
+                const int num_st = (num_kb + ST_SLABS - 1) / ST_SLABS;
                 if (!(ok = wait_bar(tempty(b), ((ti >> 1) & 1u) ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM_EMPTY))) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
@@ -243,7 +255,9 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         const uint32_t swz = (uint32_t)(r & 7);
         uint32_t it = 0, pt = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+            const int num_kb = slabs_of(w % p.splits);
+            const int num_st = (num_kb + ST_SLABS - 1) / ST_SLABS;
             for (int st = 0; st < num_st; ++st, ++it) {
                 const int s = it % NS, q = pt % PKS;
                 // a packed tile covers two stages; every unpack warp waits for it, also one that owns
@@ -291,11 +305,37 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         const bool has_bias = p.bias != nullptr;
         uint32_t ti = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti) {
+        for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++ti) {
             const int b = ti & 1;
+            const int tile = w / p.splits, sp = w - tile * p.splits;
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
             const int row = m0 + e * 32 + lane;
             const bool row_ok = row < p.m;
+            if (p.splits > 1) {
+                // K split: this item's raw sums go to its slice of the partial buffer ([split][token][row], rows
+                // contiguous: a warp stores 128 bytes per token)
+                ok = wait_bar(tfull(b), (ti >> 1) & 1u, abort_flag, p.status, DEV_TIMEOUT_EPI_TMEM_FULL);
+                if (!ok) break;
+                tc_fence_after();
+                int32_t *prow = p.part + ((size_t)sp * p.n + n0) * p.m + row;
+#pragma unroll 1
+                for (int c = 0; c < NCH; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + (uint32_t)(b * BN + c * 32) + ((uint32_t)(e * 32) << 16), v);
+                    if (c == NCH - 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty(b));
+                    }
+                    const int valid = p.n - (n0 + c * 32);
+                    if (row_ok) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (i < valid) prow[(size_t)(c * 32 + i) * p.m] = (int)v[i];
+                    }
+                }
+                continue;
+            }
             const float sw = row_ok ? p.sw[row] : 0.0f;
             const float bias = (row_ok && has_bias) ? p.bias[row] : 0.0f;
             const size_t yoff = (size_t)n0 * p.ldy + row;
@@ -371,6 +411,44 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
     }
 }
 
+// second step of the K split: adds the splits' raw sums (int32, exact in any order) and runs the epilogue of the
+// unsplit kernel on them; thread = one output, rows fastest
+struct CombineParams {
+    const int32_t *part;
+    int splits, n, m;
+    const float *sw, *bias, *sx;
+    const int32_t *sumq;
+    int mul, off;
+    float *y;
+    int32_t *acc;
+    size_t ldy;
+    const float *resid;
+    int relu;
+    float *y_more[MAX_PEERS - 1];
+    int n_more;
+};
+__global__ void __launch_bounds__(256) splitk_combine_kernel(const CombineParams p) {
+    const size_t total = (size_t)p.n * p.m;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) {
+        const int tok = (int)(idx / p.m), row = (int)(idx - (size_t)tok * p.m);
+        int sum = 0;
+        for (int sp = 0; sp < p.splits; ++sp) sum += p.part[(size_t)sp * total + idx];
+        const int a = p.mul * sum - p.off * p.sumq[tok];
+        const size_t o = (size_t)tok * p.ldy + row;
+        if (p.acc) p.acc[o] = a;
+        if (p.y) {
+            const bool has_bias = p.bias != nullptr;
+            float out = dequant_out(a, p.sw[row], p.sx[tok], has_bias ? p.bias[row] : 0.0f, has_bias);
+            if (p.resid) out = __fadd_rn(out, p.resid[o]);
+            if (p.relu) out = fmaxf(out, 0.0f);
+            p.y[o] = out;
+            for (int q = 0; q < p.n_more; ++q) p.y_more[q][o] = out;  // column-sharded layers: peer copies over NVLink
+        }
+    }
+    if (p.n_more) __threadfence_system();
+}
+
 template <int BN>
 int launch_bn(const FwdArgs &a, cudaStream_t stream) {
     using C = Cfg<BN>;
@@ -392,9 +470,51 @@ int launch_bn(const FwdArgs &a, cudaStream_t stream) {
     if (int rc_attr = set_dyn_smem_once(reinterpret_cast<const void *>(kern), dev, C::SMEM_BYTES, "gemm smem attribute")) return rc_attr;
     const int tiles = (int)(((L->m + BM - 1) / BM) * ((a.n + BN - 1) / BN));
     const int sms = sm_count(L->device);
-    const int grid = tiles < sms ? tiles : sms;
+    // A tile walks all of K on one SM, so a layer of few tiles leaves most SMs idle for the whole walk (25 tiles of
+    // 3200 x 8640: 21.5 us whatever the token count).  Then K is split over CTAs: at least 8 slabs per split, splits
+    // on packed-tile boundaries, raw sums through a scratch buffer (small: such layers have few rows) and a second
+    // launch that adds them up.  The two launches and the scratch traffic cost about 4 us, so short rows (K < 6144)
+    // and two-way splits of 128-token tiles stay unsplit (measured, 64 / 128 tokens: 8192 -> 3584 20.6 / 22.5 ->
+    // 14.0 / 17.7 us, 8640 -> 3200 21.6 / 23.4 -> 14.3 / 18.2 us, 8192 -> 7168 21.1 / 22.8 -> 19.3 / 25.0 us,
+    // 3200 -> 3200 11.7 / 13.4 -> 12.8 / 16.9 us).
+    const int num_kb = (int)(L->kp / BK);
+    static const int env_splits = []() { const char *e = getenv("KB_GEMM_SPLITS"); return e ? atoi(e) : 0; }();
+    int splits = 1;
+    if (tiles * 2 <= sms && num_kb >= 48) {
+        splits = sms / tiles;
+        if (splits > 8) splits = 8;
+        if (splits > num_kb / 8) splits = num_kb / 8;
+        if (splits < (BN > 64 ? 3 : 2)) splits = 1;
+    }
+    if (env_splits >= 1) splits = env_splits;
+    if (splits < 1) splits = 1;
+    int split_slabs = ((num_kb + splits - 1) / splits + PKT_SLABS - 1) / PKT_SLABS * PKT_SLABS;
+    splits = (num_kb + split_slabs - 1) / split_slabs;
+    p.splits = splits; p.split_slabs = splits > 1 ? split_slabs : num_kb; p.part = nullptr;
+    if (splits > 1) {
+        const size_t bytes = (size_t)splits * a.n * L->m * sizeof(int32_t);
+        cudaError_t ea = cudaMallocAsync(reinterpret_cast<void **>(&p.part), bytes, stream);
+        if (ea != cudaSuccess) return cuda_fail(ea, "split scratch allocation");
+    }
+    const int work = tiles * splits;
+    const int grid = work < sms ? work : sms;
     kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(tmap_x, L->tmap_w128, p);
     cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess && splits > 1) {
+        CombineParams c;
+        c.part = p.part; c.splits = splits; c.n = p.n; c.m = p.m;
+        c.sw = p.sw; c.bias = p.bias; c.sx = p.sx; c.sumq = p.sumq; c.mul = p.mul; c.off = p.off;
+        c.y = p.y; c.acc = p.acc; c.ldy = p.ldy; c.resid = p.resid; c.relu = p.relu;
+        c.n_more = p.n_more;
+        for (int q = 0; q < MAX_PEERS - 1; ++q) c.y_more[q] = p.y_more[q];
+        const size_t total = (size_t)p.n * p.m;
+        splitk_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(c);
+        e = cudaGetLastError();
+    }
+    if (p.part) {
+        cudaError_t ef = cudaFreeAsync(p.part, stream);
+        if (e == cudaSuccess) e = ef;
+    }
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "gemm launch");
 }
 

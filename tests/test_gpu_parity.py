@@ -148,6 +148,8 @@ SHAPES = [
     (50, 8640, 16), (3200, 3200, 12), (17, 4352, 27),
     # CTA-pair GEMM edges: odd number of 128-row blocks, odd number of 128-byte K slabs, ragged tokens
     (384, 640, 520), (130, 128, 257),
+    # medium-batch GEMM with K split over CTAs (few row tiles, long rows): ragged last split, both token tiles
+    (300, 8640, 100), (3200, 2048, 64), (1000, 4224, 40),
 ]
 
 
