@@ -765,15 +765,17 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
         for lay in layers:
             lay.use_flagged = False  # the fence-and-flag form first; the flagged form (the default up to 8 tokens) below
 
+        xq_c, sx_c, sm_c = kernels.quantize_act_i8(x)  # every sharded form below starts from these, like the unsharded layer
+
         def step_p2p():
             for lay in layers:
-                lay.forward(x, stream_ptr=sp)
+                lay.forward_q8(xq_c, sx_c, sm_c, stream_ptr=sp)
 
         sec, _ = time_graph(torch, step_p2p, 5, 3, stream)
         t = torch.tensor([sec / copies], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         per = float(t.item())
-        y_p2p = layers[-1].forward(x, stream_ptr=sp)  # one more forward whose result is read back
+        y_p2p = layers[-1].forward(x, stream_ptr=sp)  # one more forward (from f32) whose result is read back
         stream.synchronize()
         ok_p2p = bool((y_p2p.cpu().numpy() == y_chk).all()) if rank == 0 else True
         entry.update({"us_per_forward_p2p": per * 1e6, "GB/s": gemv_bytes(m, k, nb) / per / 1e9,
@@ -784,8 +786,6 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
         # chain form (pre-quantised activations, up to 32 tokens): every link waits only for the peers' PREVIOUS
         # publication, behind its own weight stream; one wait ends the chain
         if nb <= 32:
-            xq_c, sx_c, sm_c = kernels.quantize_act_i8(x)
-
             def step_chain():
                 for lay in layers:
                     lay.forward_chain_q8(xq_c, sx_c, sm_c, stream_ptr=sp)

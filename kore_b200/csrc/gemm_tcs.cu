@@ -20,10 +20,13 @@
 // Tensor memory (512 columns): two BN-column accumulators and (512 - 2 BN) / 64 stages of weight
 // slots — 6 stages at BN = 64, 4 at BN = 128; stage s of shared memory and stage s of tensor memory
 // are filled and freed together, so the MMA thread waits on one barrier and commits once per eight
-// MMAs.  All barriers are local to the CTA.  Every wait is bounded; a wait that gives up records a
+// MMAs.  Layers of few row tiles split K over CTAs (work item = (tile, split); the splits' raw int32 sums meet in a
+// scratch buffer and a second launch adds them and runs the epilogue).  All barriers are local to the CTA.  Every wait is bounded; a wait that gives up records a
 // code in the status word and raises the CTA's abort flag, and the CTA drains its copies, frees its
 // tensor memory and returns.
 #include <cstdlib>
+#include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "device_utils.cuh"
@@ -411,6 +414,35 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
     }
 }
 
+// Scratch of the K split: one buffer per (device, stream), created at the largest size a split launch can need
+// (8 splits x 128 tokens x 74 row tiles of int32: 38.8 MB) and never moved or freed, so a captured graph that holds
+// its address stays valid.  Launches on one stream use the buffer one after the other; other streams have their own,
+// so concurrent forwards never share one.  (A stream-ordered allocation per launch costs more than the split saves
+// on short layers and puts allocation nodes into captured graphs.)  A buffer cannot be created during stream capture
+// (cudaMalloc is not capturable) and at most SPLIT_SCRATCH_MAX exist: otherwise the launch falls back to a
+// stream-ordered allocation.
+constexpr size_t SPLIT_SCRATCH_BYTES = (size_t)8 * 128 * 74 * 128 * sizeof(int32_t);
+constexpr size_t SPLIT_SCRATCH_MAX = 64;
+struct SplitScratch {
+    struct Entry { int device; cudaStream_t stream; void *ptr; };
+    std::mutex mu;
+    std::vector<Entry> entries;
+    void *get(int device, cudaStream_t stream, size_t bytes) {
+        if (bytes > SPLIT_SCRATCH_BYTES) return nullptr;
+        std::lock_guard<std::mutex> lock(mu);
+        for (auto &e : entries)
+            if (e.device == device && e.stream == stream) return e.ptr;
+        if (entries.size() >= SPLIT_SCRATCH_MAX) return nullptr;
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) { cudaGetLastError(); return nullptr; }
+        void *ptr = nullptr;
+        if (cudaMalloc(&ptr, SPLIT_SCRATCH_BYTES) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        entries.push_back(Entry{device, stream, ptr});
+        return ptr;
+    }
+};
+SplitScratch g_split_scratch;
+
 // second step of the K split: adds the splits' raw sums (int32, exact in any order) and runs the epilogue of the
 // unsplit kernel on them; thread = one output, rows fastest
 struct CombineParams {
@@ -491,10 +523,15 @@ int launch_bn(const FwdArgs &a, cudaStream_t stream) {
     int split_slabs = ((num_kb + splits - 1) / splits + PKT_SLABS - 1) / PKT_SLABS * PKT_SLABS;
     splits = (num_kb + split_slabs - 1) / split_slabs;
     p.splits = splits; p.split_slabs = splits > 1 ? split_slabs : num_kb; p.part = nullptr;
+    bool part_async = false;
     if (splits > 1) {
         const size_t bytes = (size_t)splits * a.n * L->m * sizeof(int32_t);
-        cudaError_t ea = cudaMallocAsync(reinterpret_cast<void **>(&p.part), bytes, stream);
-        if (ea != cudaSuccess) return cuda_fail(ea, "split scratch allocation");
+        p.part = static_cast<int32_t *>(g_split_scratch.get(dev, stream, bytes));
+        if (!p.part) {
+            cudaError_t ea = cudaMallocAsync(reinterpret_cast<void **>(&p.part), bytes, stream);
+            if (ea != cudaSuccess) return cuda_fail(ea, "split scratch allocation");
+            part_async = true;
+        }
     }
     const int work = tiles * splits;
     const int grid = work < sms ? work : sms;
@@ -511,7 +548,7 @@ int launch_bn(const FwdArgs &a, cudaStream_t stream) {
         splitk_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(c);
         e = cudaGetLastError();
     }
-    if (p.part) {
+    if (part_async) {
         cudaError_t ef = cudaFreeAsync(p.part, stream);
         if (e == cudaSuccess) e = ef;
     }
