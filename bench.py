@@ -808,10 +808,10 @@ def sharded_projection(torch, lib, _cabi, nn, dist, dev, stream, rank, world, pe
                 out["matches_unsharded"] = out["matches_unsharded"] and ok_chain
         for lay in layers:
             lay.use_flagged = True
-        # flagged exchange (up to 32 pre-quantised tokens): every value crosses NVLink as an 8-byte (value, epoch)
-        # word, nothing is fenced and the producer does not wait; the unpack that follows every forward waits per
-        # word and leaves the plain y [nb, m] on every rank
-        if nb <= 32:
+        # flagged exchange (up to 128 tokens): every value crosses NVLink as an 8-byte (value, epoch) word, nothing
+        # is fenced and the producer does not wait; the unpack that follows every forward waits per word and leaves
+        # the plain y [nb, m] on every rank
+        if nb <= 128:
             y_fl = torch.empty((nb, m), dtype=torch.float32, device=dev)
 
             def step_flagged():

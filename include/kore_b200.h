@@ -368,7 +368,8 @@ int kb_linear_forward_sharded_chain_q8(const kb_linear *h, const int8_t *xq, siz
                                        const int32_t *sumq, size_t n, float *const *y_bases, int world,
                                        int rank, size_t m_total, size_t col_offset,
                                        int *const *flag_arrays_dev, int *sync_words_dev, kb_stream stream);
-/* Flagged exchange for chains of dependent sharded layers of one to eight tokens (up to 32 pre-quantised): every
+/* Flagged exchange for chains of dependent sharded layers of up to 128 tokens (streaming kernel up to 8 tokens, 32
+ * pre-quantised; medium-batch GEMM beyond): every
  * output value travels as an 8-byte word (f32 bits in the low half, an epoch in the high half) written with a
  * single 8-byte store into every rank's buffer, so a reader that finds the expected epoch has the value too — no
  * fence, no flag array, no barrier, and nothing waits in the producer.  y_bases[q] = rank q's buffer of

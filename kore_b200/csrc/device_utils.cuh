@@ -77,4 +77,12 @@ __device__ __forceinline__ float dequant_out(int acc, float sw, float sx, float 
     return has_bias ? __fadd_rn(v, bias) : v;
 }
 
+// one pair, one 8-byte store: value and epoch become visible together
+__device__ __forceinline__ void st_pair(float *base, size_t o, float value, uint32_t epoch) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(reinterpret_cast<uint2 *>(base) + o), "r"(__float_as_uint(value)),
+                 "r"(epoch)
+                 : "memory");
+}
+
+
 }  // namespace kb

@@ -84,6 +84,10 @@ struct TcsParams {
     // (a multiple of PKT_SLABS) and stores its raw int32 sums to part[split][n][m]; a second kernel adds them up
     int splits, split_slabs;
     int32_t *part;
+    // flagged words (see FwdArgs): y and y_more are buffers of (value, epoch) pairs, epoch = (*flag_round << 8) | flag_seq
+    int y_flagged;
+    const int *flag_round;
+    int flag_seq;
 };
 
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
@@ -306,6 +310,7 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         const int e = warp - 12;
         constexpr int NCH = BN / 32;
         const bool has_bias = p.bias != nullptr;
+        const uint32_t epoch = p.y_flagged ? (((uint32_t)(*reinterpret_cast<const volatile int *>(p.flag_round)) << 8) | (uint32_t)p.flag_seq) : 0u;
         uint32_t ti = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++ti) {
@@ -388,7 +393,16 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                         for (int i = 0; i < 32; ++i)
                             if (i < valid) arow[cbase + (size_t)i * p.ldy] = (int)v[i];
                     }
-                    if (yrow) {
+                    if (yrow && p.y_flagged) {  // (value, epoch) pairs, locally and into the peers' buffers
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (i < valid) st_pair(p.y, yoff + cbase + (size_t)i * p.ldy, outv[i], epoch);
+                        for (int q = 0; q < p.n_more; ++q) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < valid) st_pair(p.y_more[q], yoff + cbase + (size_t)i * p.ldy, outv[i], epoch);
+                        }
+                    } else if (yrow) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
                             if (i < valid) yrow[cbase + (size_t)i * p.ldy] = outv[i];
@@ -401,7 +415,7 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                     }
                 }
             }
-            if (p.n_more) __threadfence_system();
+            if (p.n_more && !p.y_flagged) __threadfence_system();
         }
     }
 
@@ -458,6 +472,9 @@ struct CombineParams {
     int relu;
     float *y_more[MAX_PEERS - 1];
     int n_more;
+    int y_flagged;
+    const int *flag_round;
+    int flag_seq;
 };
 __global__ void __launch_bounds__(256) splitk_combine_kernel(const CombineParams p) {
     const size_t total = (size_t)p.n * p.m;
@@ -474,11 +491,17 @@ __global__ void __launch_bounds__(256) splitk_combine_kernel(const CombineParams
             float out = dequant_out(a, p.sw[row], p.sx[tok], has_bias ? p.bias[row] : 0.0f, has_bias);
             if (p.resid) out = __fadd_rn(out, p.resid[o]);
             if (p.relu) out = fmaxf(out, 0.0f);
-            p.y[o] = out;
-            for (int q = 0; q < p.n_more; ++q) p.y_more[q][o] = out;  // column-sharded layers: peer copies over NVLink
+            if (p.y_flagged) {
+                const uint32_t epoch = ((uint32_t)(*reinterpret_cast<const volatile int *>(p.flag_round)) << 8) | (uint32_t)p.flag_seq;
+                st_pair(p.y, o, out, epoch);
+                for (int q = 0; q < p.n_more; ++q) st_pair(p.y_more[q], o, out, epoch);
+            } else {
+                p.y[o] = out;
+                for (int q = 0; q < p.n_more; ++q) p.y_more[q][o] = out;  // column-sharded layers: peer copies over NVLink
+            }
         }
     }
-    if (p.n_more) __threadfence_system();
+    if (p.n_more && !p.y_flagged) __threadfence_system();
 }
 
 template <int BN>
@@ -497,6 +520,9 @@ int launch_bn(const FwdArgs &a, cudaStream_t stream) {
     p.resid = a.y ? a.resid : nullptr;
     p.relu = a.relu ? 1 : 0;
     p.mul = L->mul; p.off = L->off; p.status = L->dev_status;
+    p.y_flagged = a.y_flagged ? 1 : 0; p.flag_round = a.flag_round; p.flag_seq = a.flag_seq;
+    if (a.y_flagged && (!a.y || a.acc || a.resid || !a.flag_round || a.flag_seq < 1 || a.flag_seq > 255))
+        return fail(KB_ERR_INVALID, "gemm: flagged outputs need y, the round word and a chain position, and take no accumulator or residual");
     auto kern = gemm_tcs_kernel<BN>;
     const int dev = L->device;
     if (int rc_attr = set_dyn_smem_once(reinterpret_cast<const void *>(kern), dev, C::SMEM_BYTES, "gemm smem attribute")) return rc_attr;
@@ -543,6 +569,7 @@ int launch_bn(const FwdArgs &a, cudaStream_t stream) {
         c.sw = p.sw; c.bias = p.bias; c.sx = p.sx; c.sumq = p.sumq; c.mul = p.mul; c.off = p.off;
         c.y = p.y; c.acc = p.acc; c.ldy = p.ldy; c.resid = p.resid; c.relu = p.relu;
         c.n_more = p.n_more;
+        c.y_flagged = p.y_flagged; c.flag_round = p.flag_round; c.flag_seq = p.flag_seq;
         for (int q = 0; q < MAX_PEERS - 1; ++q) c.y_more[q] = p.y_more[q];
         const size_t total = (size_t)p.n * p.m;
         splitk_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(c);

@@ -355,13 +355,6 @@ __device__ __forceinline__ uint4 ld_pairs(const uint2 *p) {
     asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-// one pair, one 8-byte store: value and epoch become visible together
-__device__ __forceinline__ void st_pair(float *base, size_t o, float value, uint32_t epoch) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(reinterpret_cast<uint2 *>(base) + o), "r"(__float_as_uint(value)),
-                 "r"(epoch)
-                 : "memory");
-}
-
 // 16 consecutive values of a flagged row from element e0 (k is a multiple of 4, rows are 16-byte aligned, so the
 // 16-byte loads never straddle the row's end): waits, bounded, until every pair carries `epoch`.  Elements from k on are 0.
 __device__ __forceinline__ bool load_cell_flagged(const uint2 *row, bool live, int e0, int k, uint32_t epoch, float (&v)[16],

@@ -314,8 +314,11 @@ static int sharded_flagged(const kb_linear *h, const void *x, int x_is_flagged, 
     if (n == 0) return KB_OK;
     for (int q = 0; q < world; ++q)
         if (!y_bases[q]) return fail(KB_ERR_INVALID, "null output base for rank %d", q);
-    if (!gemv_stream_supports(L, n))
-        return fail(KB_ERR_UNSUPPORTED, "flagged exchange: %zu tokens x K=%zu do not fit the streaming kernel", n, L->k);
+    // up to 8 tokens (32 pre-quantised) the streaming kernel, beyond it the medium-batch GEMM (up to 128 tokens)
+    const bool use_stream = gemv_stream_supports(L, n) && n <= (size_t)(xq ? 32 : 8);
+    if (!use_stream && (n > 128 || !L->has_tmap128))
+        return fail(KB_ERR_UNSUPPORTED, "flagged exchange: %zu tokens x K=%zu fit neither the streaming kernel nor the medium-batch GEMM", n,
+                    L->k);
     if (!xq && !x_is_flagged && ldx && ldx != L->k)
         return fail(KB_ERR_UNSUPPORTED, "flagged exchange: plain f32 activations must be dense rows");
     int prev = -1;
@@ -337,7 +340,7 @@ static int sharded_flagged(const kb_linear *h, const void *x, int x_is_flagged, 
     bool own = false;
     // flagged activations: the kernel's own prologue waits for them and quantises (every CTA reads the whole row:
     // short rows only), or a cluster kernel does it once for all CTAs
-    const bool separate = x_is_flagged && (fuse == 2 || (fuse == 0 && (L->kp > 4096 || n > 2)));
+    const bool separate = !use_stream || (x_is_flagged && (fuse == 2 || (fuse == 0 && (L->kp > 4096 || n > 2))));
     if (xq) {
         a.xq = xq; a.ldq = ldq; a.sx = sx; a.sumq = sumq;
     } else if (separate) {
@@ -357,8 +360,9 @@ static int sharded_flagged(const kb_linear *h, const void *x, int x_is_flagged, 
             int8_t *wq = reinterpret_cast<int8_t *>(ws);
             float *wsx = reinterpret_cast<float *>(ws + xq_bytes);
             int32_t *wsum = reinterpret_cast<int32_t *>(ws + xq_bytes + vec_bytes);
-            rc = launch_act_quant_flagged(static_cast<const unsigned long long *>(x), ldx ? ldx : L->k, n, L->k, sync_words_dev + 3,
-                                          seq - 1, wq, L->kp, wsx, wsum, sync_words_dev + 2, st);
+            rc = x_is_flagged ? launch_act_quant_flagged(static_cast<const unsigned long long *>(x), ldx ? ldx : L->k, n, L->k,
+                                                         sync_words_dev + 3, seq - 1, wq, L->kp, wsx, wsum, sync_words_dev + 2, st)
+                              : launch_act_quant(static_cast<const float *>(x), n, L->k, wq, L->kp, wsx, wsum, st);
             a.xq = wq; a.ldq = L->kp; a.sx = wsx; a.sumq = wsum;
         }
     } else if (x_is_flagged) {
@@ -367,7 +371,7 @@ static int sharded_flagged(const kb_linear *h, const void *x, int x_is_flagged, 
     } else {
         a.x = static_cast<const float *>(x);
     }
-    if (rc == KB_OK) rc = launch_gemv_stream(a, st);
+    if (rc == KB_OK) rc = use_stream ? launch_gemv_stream(a, st) : launch_gemm_tcs(a, st);
     if (own && ws) cudaFreeAsync(ws, st);
     if (prev != L->device) cudaSetDevice(prev);
     return rc;

@@ -97,7 +97,7 @@ class ShardContext:
         torch.cuda.set_device(device)
         self.y_bytes = (max_tokens * m_total * 4 + 255) // 256 * 256
         # flagged exchange (a few tokens): two buffers of [flagged_tokens, m_total] 8-byte (value, epoch) words
-        self.flagged_tokens = min(max_tokens, 32)
+        self.flagged_tokens = min(max_tokens, 128)
         self.f_bytes = (self.flagged_tokens * m_total * 8 + 255) // 256 * 256
         self.f_offset = 2 * self.y_bytes + 256
         total = self.f_offset + 2 * self.f_bytes
@@ -223,7 +223,7 @@ class ShardedLinear:
                              f"(slices are multiples of 32 features): use at most {max(1, (out_features + 31) // 32)} ranks")
         self.start, self.size = self.parts[rank]
         self.exchange, self.ctx, self.dist = exchange, ctx, (dist if dist is not None else (ctx.dist if ctx else None))
-        # p2p exchange of up to eight tokens: flagged words + unpack instead of peer stores + fence + flag barrier
+        # p2p exchange of up to 128 tokens: flagged words + unpack instead of peer stores + fence + flag barrier
         # (12.4 against 25.5 us for one token of 8192 -> 28672 on two GPUs)
         self.use_flagged = True
         p, s, b = slice_wire_rows(kind, packed, scales, bias, out_features, in_features, self.start, self.size)
@@ -268,8 +268,10 @@ class ShardedLinear:
 
     def _flagged_ok(self, n: int, path: int) -> bool:
         ctx = self.ctx
-        return (self.use_flagged and path == _cabi.PATH_AUTO and n <= min(8, ctx.flagged_tokens) and ctx.flag_seq == 0
-                and self.m_total == ctx.m_total and self.m_total % 2 == 0 and n * ((self.k + 1023) // 1024 * 1024 + 64) <= 96 * 1024)
+        if not (self.use_flagged and path == _cabi.PATH_AUTO and ctx.flag_seq == 0 and self.m_total == ctx.m_total
+                and self.m_total % 2 == 0 and n <= ctx.flagged_tokens):
+            return False
+        return n <= 128  # the library picks the streaming kernel (few tokens) or the medium-batch GEMM
 
     def forward_chain_q8(self, xq, sx, sumq, stream_ptr: Optional[int] = None):
         """One link of a chain of sharded layers on pre-quantised activations: the launch waits for the peers'
@@ -307,7 +309,7 @@ class ShardedLinear:
             raise _cabi.KoreError(_cabi.ERR_INVALID, "a chain starts on plain activations and continues on flagged ones")
         if stream_ptr is None:
             stream_ptr = torch.cuda.current_stream(ctx.device).cuda_stream
-        ws, ws_bytes = ctx.flagged_workspace(n, (self.k + 127) // 128 * 128) if x_is_flagged else (None, 0)
+        ws, ws_bytes = ctx.flagged_workspace(n, (self.k + 127) // 128 * 128)  # for the separate quantiser, where one runs
         par = ctx.next_parity()  # consecutive flagged forwards, across chains too, alternate between the two buffers
         _cabi.check(ctx.lib.kb_linear_forward_sharded_flagged(
             self.layer.handle, x.data_ptr(), 1 if x_is_flagged else 0, x.stride(0), n, self.k, ctx.f_tables_host[par],

@@ -40,9 +40,9 @@ def _rank_main(rank, world, port, q):
             for exchange in ("p2p", "collective"):
                 lay = sharded.ShardedLinear(kind, packed, scales, bias, k, m, rank, world, device=rank, ctx=ctx,
                                             dist=dist, exchange=exchange)
-                for n in (1, 3, 5, 16, 64, 200):  # flagged words / GEMV with fused barrier, small-batch kernel, both GEMMs
+                for n in (1, 3, 5, 16, 64, 100, 200):  # flagged words / GEMV with fused barrier, small-batch kernel, both GEMMs
                     for rep in range(4):  # repeated calls exercise the double buffering and epochs
-                        lay.use_flagged = rep < 2  # up to 8 tokens: flagged words first, then peer stores + fence + barrier
+                        lay.use_flagged = rep < 2  # up to 128 tokens: flagged words first, then peer stores + fence + barrier
                         x = cases.gaussian(100 * n + rep, (n, k), 1.0)
                         y = lay.forward(torch.from_numpy(x).cuda())
                         torch.cuda.synchronize()
@@ -169,7 +169,12 @@ def test_flagged_words_single_rank(k, m):
     dev = torch.device("cuda", 0)
     sync = torch.zeros(8, dtype=torch.int32, device=dev)
     sp = torch.cuda.current_stream().cuda_stream
-    for n in ((1, 2, 5, 8) if k <= 8192 else (1, 2, 3)):  # staged activation rows must fit in shared memory
+    # few tokens: streaming kernel (the staged rows must fit in shared memory); more: the medium-batch GEMM, which
+    # needs rows of at least 128 packed bytes in both layers of the chain
+    tokens = (1, 2, 5, 8) if k <= 8192 else (1, 2, 3)
+    if min(k, m) >= 512:
+        tokens += (40, 100)
+    for n in tokens:
         fa = torch.zeros((n, m), dtype=torch.int64, device=dev)
         fb = torch.zeros((n, k), dtype=torch.int64, device=dev)
         x = cases.gaussian(500 + n, (n, k), 1.0)
