@@ -223,7 +223,7 @@ class ShardedLinear:
                              f"(slices are multiples of 32 features): use at most {max(1, (out_features + 31) // 32)} ranks")
         self.start, self.size = self.parts[rank]
         self.exchange, self.ctx, self.dist = exchange, ctx, (dist if dist is not None else (ctx.dist if ctx else None))
-        # p2p exchange of up to 128 tokens: flagged words + unpack instead of peer stores + fence + flag barrier
+        # p2p exchange of up to eight tokens: flagged words + unpack instead of peer stores + fence + flag barrier
         # (12.4 against 25.5 us for one token of 8192 -> 28672 on two GPUs)
         self.use_flagged = True
         p, s, b = slice_wire_rows(kind, packed, scales, bias, out_features, in_features, self.start, self.size)
@@ -271,7 +271,10 @@ class ShardedLinear:
         if not (self.use_flagged and path == _cabi.PATH_AUTO and ctx.flag_seq == 0 and self.m_total == ctx.m_total
                 and self.m_total % 2 == 0 and n <= ctx.flagged_tokens):
             return False
-        return n <= 128  # the library picks the streaming kernel (few tokens) or the medium-batch GEMM
+        # more tokens can travel as flagged words too (forward_flagged, up to 128), but from 64 tokens on the exchange
+        # is bound by NVLink bytes, of which the words carry twice as many (8192 -> 28672 at 64 tokens: 40.1 against
+        # 36.7 us on two GPUs, 41.9 against 41.7 on eight)
+        return n <= 8 and n * ((self.k + 1023) // 1024 * 1024 + 64) <= 96 * 1024
 
     def forward_chain_q8(self, xq, sx, sumq, stream_ptr: Optional[int] = None):
         """One link of a chain of sharded layers on pre-quantised activations: the launch waits for the peers'

@@ -42,7 +42,7 @@ def _rank_main(rank, world, port, q):
                                             dist=dist, exchange=exchange)
                 for n in (1, 3, 5, 16, 64, 100, 200):  # flagged words / GEMV with fused barrier, small-batch kernel, both GEMMs
                     for rep in range(4):  # repeated calls exercise the double buffering and epochs
-                        lay.use_flagged = rep < 2  # up to 128 tokens: flagged words first, then peer stores + fence + barrier
+                        lay.use_flagged = rep < 2  # up to 8 tokens: flagged words first, then peer stores + fence + barrier
                         x = cases.gaussian(100 * n + rep, (n, k), 1.0)
                         y = lay.forward(torch.from_numpy(x).cuda())
                         torch.cuda.synchronize()
@@ -82,14 +82,14 @@ def _rank_main(rank, world, port, q):
         # flagged exchange: a dependent chain 1000 -> 640 -> 1000 -> 640 ... in which every link reads the previous
         # link's (value, epoch) words and waits per word; one unpack at the end; against the oracle's chain
         m, k = 640, 1000
-        ctx = sharded.ShardContext(rank, world, max(m, k), 8, rank, dist)
+        ctx = sharded.ShardContext(rank, world, max(m, k), 128, rank, dist)
         kind = kbref.TERNARY
         wa, wb = cases.gaussian(31, (m, k), 0.02), cases.gaussian(32, (k, m), 0.02)
         pa, sa = cases.make_weights(kind, "absmean", wa)
         pb, sb = cases.make_weights(kind, "absmean", wb)
         la = sharded.ShardedLinear(kind, pa, sa, None, k, m, rank, world, device=rank, ctx=ctx, dist=dist)
         lb = sharded.ShardedLinear(kind, pb, sb, None, m, k, rank, world, device=rank, ctx=ctx, dist=dist)
-        for n in (1, 2, 3, 8):
+        for n in (1, 2, 3, 8, 40, 100):  # streaming kernel up to 8 tokens, the medium-batch GEMM beyond
             for rep in range(2):
                 x = cases.gaussian(700 + 10 * n + rep, (n, k), 1.0)
                 ref = x
