@@ -262,7 +262,7 @@ def main():
                     help="headline step: one grouped launch over the pool of independent layers (default), or one "
                          "quantiser + one GEMV launch per layer spread over --streams streams")
     ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "group_4096", "small_batch", "medium_batch", "prefill_up", "prefill_down",
-                             "decode_step", "decode_step_batch16", "attn_decode"],
+                             "decode_step", "decode_step_batch16", "attn_decode", "medium_batch_few_tiles", "flagged_chain"],
                     help="run one small case and print its own JSON line (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -606,9 +606,12 @@ def single_case(torch, lib, _cabi, nn, kernels, dev, args):
     """One kernel on one small case, a handful of eager launches: the command profiled with ncu."""
     if args.only in ("decode_step", "decode_step_batch16", "attn_decode"):
         return decoder_case(torch, lib, _cabi, dev, args)
+    if args.only == "flagged_chain":
+        return flagged_chain_case(torch, lib, _cabi, nn, dev, args)
     shapes = {"gemv_big": (28672, 8192, 1, 3), "gemv_4096": (4096, 4096, 1, 40), "group_4096": (4096, 4096, 1, 40),
               "small_batch": (28672, 8192, 16, 3),
               "medium_batch": (28672, 8192, 64, 3),
+              "medium_batch_few_tiles": (3584, 8192, 64, 20),  # an eighth of the big layer: K split over CTAs
               "prefill_up": (11008, 4096, 2048, 1), "prefill_down": (4096, 11008, 2048, 1)}
     m, k, n, copies = shapes[args.only]
     w = (torch.randn((m, k), generator=torch.Generator().manual_seed(7)) * 0.02).numpy()
@@ -652,6 +655,53 @@ def single_case(torch, lib, _cabi, nn, kernels, dev, args):
         return
     print(json.dumps({"case": args.only, "m": m, "k": k, "n": n, "copies": copies, "us_per_launch": per * 1e6,
                       "GB/s": gemv_bytes(m, k, n) / per / 1e9, "TOPS": 2.0 * m * k * n / per / 1e12}), flush=True)
+
+
+def flagged_chain_case(torch, lib, _cabi, nn, dev, args):
+    """The kernels of the flagged exchange on one GPU (a sharded layer with a single rank): a chain of dependent
+    8192 -> 3584 -> 8192 layers at one token — every link's forward writes (value, epoch) words, the next link's
+    cluster quantiser waits for them — ended by one unpack.  Shapes of an eighth of the 8192 <-> 28672 pair."""
+    import ctypes as C
+
+    k, m, pairs = 8192, 3584, 12
+    ups, downs = [], []
+    wu = (torch.randn((m, k), generator=torch.Generator().manual_seed(7)) * 0.02).numpy()
+    wd = (torch.randn((k, m), generator=torch.Generator().manual_seed(8)) * 0.02).numpy()
+    u0 = nn.BitLinear.new(wu, None, 0.3, quantiser="absmean", device=dev.index)
+    d0 = nn.BitLinear.new(wd, None, 0.3, quantiser="absmean", device=dev.index)
+    del wu, wd
+    ups = [u0] + [nn.BitLinear.from_packed(u0.packed_weights(), u0.scales(), None, k, m, device=dev.index) for _ in range(pairs - 1)]
+    downs = [d0] + [nn.BitLinear.from_packed(d0.packed_weights(), d0.scales(), None, m, k, device=dev.index) for _ in range(pairs - 1)]
+    x = torch.from_numpy(gaussian(8, (1, k), 1.0)).to(dev)
+    bufs = [torch.zeros((1, k), dtype=torch.int64, device=dev) for _ in range(2)]
+    sync = torch.zeros(8, dtype=torch.int32, device=dev)
+    ws = torch.empty(1 << 20, dtype=torch.uint8, device=dev)
+    y = torch.empty((1, k), dtype=torch.float32, device=dev)
+    sp = torch.cuda.current_stream().cuda_stream
+
+    def once():
+        seq, src, flagged, width = 0, x, 0, k
+        for i in range(pairs):
+            for lay, out_dim in ((ups[i], m), (downs[i], k)):
+                dst = bufs[seq & 1]
+                table = (C.c_void_p * 1)(dst.data_ptr())
+                seq += 1
+                _cabi.check(lib.kb_linear_forward_sharded_flagged(lay.handle, src.data_ptr(), flagged, width, 1, width, table, 1, 0,
+                                                                  out_dim, 0, seq, 0, ws.data_ptr(), ws.numel(), sync.data_ptr(), sp))
+                src, flagged, width = dst, 1, out_dim
+        _cabi.check(lib.kb_flagged_unpack(src.data_ptr(), k, 1, k, y.data_ptr(), k, seq, sync.data_ptr(), sp))
+
+    for _ in range(max(1, args.warmup)):
+        once()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        once()
+    e1.record()
+    torch.cuda.synchronize()
+    per = e0.elapsed_time(e1) / 1e3 / (args.steps * 2 * pairs)
+    print(json.dumps({"case": args.only, "links": 2 * pairs, "us_per_link": per * 1e6, "status": int(sync[2].item())}), flush=True)
 
 
 def column_sharded_step(torch, lib, _cabi, dist, dev, main_stream, rank, local_rank, world, pool, x_dev, x_pin, args):
