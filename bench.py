@@ -23,7 +23,9 @@ With N > 1 the layers of the pool are independent units, so every rank runs the 
 (weak scaling, no exchange; value = all ranks' bytes / max time over ranks).  What does need an exchange is
 reported at the top level as `sharded_projection`: the 8192 -> 28672 projection split by output features
 over the ranks at batch 1 / 8 / 64 / 512, every rank ending with the full output, checked against the
-unsharded layer and timed next to it in the same run.
+unsharded layer and timed next to it in the same run (exchanges: flagged (value, epoch) words, peer stores
+with fence and flag barrier, NCCL all-gather), and a chain of dependent sharded layers on the flagged words
+(`dependent_chain_flagged`).
 
 `--impl reference` times the CPU port (oracle/kbref.c, a restatement of the reference's CPU code: the
 reference is Rust and no Rust toolchain exists here) on the same workload and config; a step there is a
