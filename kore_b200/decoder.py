@@ -10,9 +10,10 @@ RMSNorm and SwiGLU end in the per-token int8 quantiser, the residual adds live i
 projection epilogues.  Embedding and lm_head are dense f32; prefill attention uses torch's
 scaled_dot_product_attention, decode attention the library's own kernel.
 
-For one or two sequences a decode step is ONE launch of the library's persistent decode-step
-kernel (``kb_decoder_step``: every phase of every layer, the lm_head GEMV and the argmax inside
-one cooperative grid); larger batches run the step as a CUDA graph of the separate kernels.
+For one sequence a decode step is ONE launch of the library's persistent decode-step kernel
+(``kb_decoder_step``: every phase of every layer, the lm_head GEMV and the argmax inside one
+cooperative grid; it also takes two sequences, ``persistent=True``, where the graph is a few
+percent faster); larger batches run the step as a CUDA graph of the separate kernels.
 """
 from __future__ import annotations
 
@@ -103,7 +104,7 @@ def _interleave_rows(a, b):
 
 class BitNetDecoder:
     def __init__(self, cfg: DecoderConfig, weights: Dict, batch: int, device: int = 0, max_prefill_tokens: int = 0,
-                 persistent: bool = True):
+                 persistent: Optional[bool] = None):
         import torch
 
         self.cfg, self.batch, self.device = cfg, batch, device
@@ -145,6 +146,8 @@ class BitNetDecoder:
         # persistent decode step (one launch per step) where the library supports the shape
         self.persistent = None
         self.hidden_step = torch.zeros((batch, d), dtype=torch.float32, device=self.dev)
+        if persistent is None:
+            persistent = batch == 1
         if batch <= 2 and persistent:
             n = cfg.n_layers
             arr = lambda ptrs: (C.c_void_p * n)(*ptrs)
