@@ -389,8 +389,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     }
                 }
             }
-            if (p.n_more) __threadfence_system();  // peer copies of this tile are ordered before the exit
         }
+        if (p.n_more) __threadfence_system();  // once per launch: the peer copies are performed before the exit
     }
 
     tc_fence_before();

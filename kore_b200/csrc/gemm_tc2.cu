@@ -377,8 +377,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 process(vb, 2 * c + 1);
             }
             (void)N16;
-            if (p.n_more) __threadfence_system();
         }
+        if (p.n_more) __threadfence_system();  // once per launch: the peer copies are performed before the exit
     }
 
     tc_fence_before();

@@ -415,8 +415,8 @@ gemm_tcs_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                     }
                 }
             }
-            if (p.n_more && !p.y_flagged) __threadfence_system();
         }
+        if (p.n_more && !p.y_flagged) __threadfence_system();  // once per launch: the peer copies are performed before the exit
     }
 
     tc_fence_before();
@@ -478,8 +478,9 @@ struct CombineParams {
 };
 __global__ void __launch_bounds__(256) splitk_combine_kernel(const CombineParams p) {
     const size_t total = (size_t)p.n * p.m;
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx < total) {
+    // a few CTAs per SM walk the outputs: the system-scope fence behind the peer stores is then paid once per
+    // CTA at the end of the launch, not once per wave of short-lived CTAs
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const int tok = (int)(idx / p.m), row = (int)(idx - (size_t)tok * p.m);
         int sum = 0;
         for (int sp = 0; sp < p.splits; ++sp) sum += p.part[(size_t)sp * total + idx];
@@ -572,7 +573,9 @@ int launch_bn(const FwdArgs &a, cudaStream_t stream) {
         c.y_flagged = p.y_flagged; c.flag_round = p.flag_round; c.flag_seq = p.flag_seq;
         for (int q = 0; q < MAX_PEERS - 1; ++q) c.y_more[q] = p.y_more[q];
         const size_t total = (size_t)p.n * p.m;
-        splitk_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(c);
+        size_t blocks = (total + 255) / 256;
+        if (blocks > (size_t)sms * 4) blocks = (size_t)sms * 4;
+        splitk_combine_kernel<<<(unsigned)blocks, 256, 0, stream>>>(c);
         e = cudaGetLastError();
     }
     if (part_async) {
