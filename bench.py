@@ -435,8 +435,9 @@ def main():
         assert (yg_pin[pool_n - 1].numpy() == y_chk).all(), "group host entry point and graph replay disagree"
         e2e = {"value": step_bytes / ge_sec / 1e9, "unit": UNIT, "h2d_bytes_per_step": pool_n * 4 * K_DEC,
                "d2h_bytes_per_step": pool_n * 4 * M_DEC, "ms_per_step": ge_sec * 1e3,
-               "note": "kb_linear_group_forward_host: pinned x [pool, K] -> device, one grouped launch, y [pool, M] -> "
-                       "pinned host, synchronise; wall clock around the calls"}
+               "note": "kb_linear_group_forward_host: pinned x [pool, K] -> device, grouped launches, y [pool, M] -> "
+                       "pinned host, synchronise (inside the call a pipeline over four chunks of the pool); wall clock "
+                       "around the calls"}
         e2e_drop_in = per_layer
     else:
         e2e_drop_in = dict(e2e)

@@ -294,8 +294,10 @@ int kb_linear_group_forward_q8(const kb_linear_group *g, const int8_t *xq, size_
                                const int32_t *sumq, float *y, size_t ldy, kb_stream stream);
 int kb_linear_group_forward(const kb_linear_group *g, const float *x, size_t ldx, float *y, size_t ldy,
                             kb_stream stream);
-/* Host buffers: x [count, K] and y [count, M], contiguous; copies, launch and synchronisation inside
- * the call (the calling thread's per-thread stream).  Calls on one group are serialised. */
+/* Host buffers: x [count, K] and y [count, M], contiguous; copies, launches and synchronisation inside
+ * the call.  Groups of 32 or more members run as a pipeline over chunks of members on the group's own
+ * streams — upload, grouped launch and download of neighbouring chunks overlap when the host buffers are
+ * pinned (pageable buffers make the copies synchronous).  Calls on one group are serialised. */
 int kb_linear_group_forward_host(const kb_linear_group *g, const float *x, float *y);
 
 /* ---- kernel-shaped one-shots (host pointers), signatures of
