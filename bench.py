@@ -264,7 +264,7 @@ def main():
                     help="headline step: one grouped launch over the pool of independent layers (default), or one "
                          "quantiser + one GEMV launch per layer spread over --streams streams")
     ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "group_4096", "small_batch", "medium_batch", "prefill_up", "prefill_down",
-                             "decode_step", "decode_step_batch16", "attn_decode", "medium_batch_few_tiles", "flagged_chain"],
+                             "decode_step", "decode_step_batch16", "attn_decode", "medium_batch_few_tiles", "flagged_chain", "stream_batch8"],
                     help="run one small case and print its own JSON line (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -612,7 +612,7 @@ def single_case(torch, lib, _cabi, nn, kernels, dev, args):
     if args.only == "flagged_chain":
         return flagged_chain_case(torch, lib, _cabi, nn, dev, args)
     shapes = {"gemv_big": (28672, 8192, 1, 3), "gemv_4096": (4096, 4096, 1, 40), "group_4096": (4096, 4096, 1, 40),
-              "small_batch": (28672, 8192, 16, 3),
+              "small_batch": (28672, 8192, 16, 3), "stream_batch8": (28672, 8192, 8, 3),
               "medium_batch": (28672, 8192, 64, 3),
               "medium_batch_few_tiles": (3584, 8192, 64, 20),  # an eighth of the big layer: K split over CTAs
               "prefill_up": (11008, 4096, 2048, 1), "prefill_down": (4096, 11008, 2048, 1)}
@@ -626,6 +626,8 @@ def single_case(torch, lib, _cabi, nn, kernels, dev, args):
     y = torch.empty((n, m), dtype=torch.float32, device=dev)
     xq, sx, sumq = kernels.quantize_act_i8(x)
     path = _cabi.PATH_GEMV if n == 1 else (_cabi.PATH_GEMV_MMA if n <= 32 else _cabi.PATH_GEMM_TC)
+    if args.only == "stream_batch8":
+        path = _cabi.PATH_GEMV_STREAM
     sp = torch.cuda.current_stream().cuda_stream
 
     def once():

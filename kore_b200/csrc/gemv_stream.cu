@@ -675,13 +675,30 @@ __global__ void __launch_bounds__(W * 32, 1) gemv_stream_kernel(const StreamPara
         }
     } else {
         const int lim = GROUPED ? p.count : p.n;
-        for (int idx = threadIdx.x; idx < p.x_rows * cells; idx += blockDim.x) {
-            const int r = idx / cells, c = idx - r * cells;
-            const int src_row = GROUPED ? layer0 + r : r;
-            const int o = c * 16;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (src_row < lim && o < p.kp) v = *reinterpret_cast<const uint4 *>(p.xq + (size_t)src_row * p.ldq + o);
-            *reinterpret_cast<uint4 *>(xs + (size_t)r * p.xs_stride + xs_offset(o)) = v;
+        // eight 16-byte loads in flight per thread before the first store (a load-then-store loop pays one L2 round trip
+        // per iteration; asynchronous copies cannot be used here: their completion is tracked per thread in issue order,
+        // so waiting for them would also wait for every weight stage this thread has in flight)
+        constexpr int U = 8;
+        const int total = p.x_rows * cells;
+        for (int base = threadIdx.x; base < total; base += U * (int)blockDim.x) {
+            uint4 v[U];
+            int dst[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int idx = base + u * (int)blockDim.x;
+                v[u] = make_uint4(0, 0, 0, 0);
+                dst[u] = -1;
+                if (idx < total) {
+                    const int r = idx / cells, c = idx - r * cells;
+                    const int src_row = GROUPED ? layer0 + r : r;
+                    const int o = c * 16;
+                    dst[u] = r * p.xs_stride + xs_offset(o);
+                    if (src_row < lim && o < p.kp) v[u] = *reinterpret_cast<const uint4 *>(p.xq + (size_t)src_row * p.ldq + o);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (dst[u] >= 0) *reinterpret_cast<uint4 *>(xs + dst[u]) = v[u];
         }
         if ((int)threadIdx.x < p.x_rows) {
             const int src_row = GROUPED ? layer0 + threadIdx.x : threadIdx.x;
