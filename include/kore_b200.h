@@ -206,6 +206,16 @@ int kb_swiglu_quant_pairs(const float *gate_up, size_t n, size_t f, size_t ld, f
 int kb_rope_kv(const float *qkv, const int *positions, const long long *cache_rows,
                const float *cos_table, const float *sin_table, size_t n, int n_heads, int head_dim,
                int lmax, float *q_out, float *k_cache, float *v_cache, kb_stream stream);
+/* Dense f32 head of a greedy decode step for up to 16 sequences (the reference's lm_head is a dense f32 matmul
+ * followed by an argmax, crates/kore-edge/src/runtime.rs:283-294): logits[n][vocab] = x[n][d] . w[vocab][d]^T
+ * (logits nullable), and per token an argmax key folded into keys[n] (device words, zero before the call) by
+ * atomic max: the largest logit wins and, among equal ones, the lowest index.  d a multiple of 4 up to 4096. */
+int kb_lm_head_argmax(const float *x, size_t n, size_t d, const float *w, size_t vocab, float *logits,
+                      unsigned long long *keys, kb_stream stream);
+/* End of a greedy step: tokens[t] = the index in keys[t], keys[t] = 0, and positions / lens / cache_rows (each
+ * nullable) advance by one. */
+int kb_decode_advance(unsigned long long *keys, size_t n, long long *tokens, int *positions, int *lens,
+                      long long *cache_rows, kb_stream stream);
 /* One query token per sequence against its cache [batch][n_heads][lmax][head_dim]
  * (crates/kore-edge/src/ops/attention.rs:74-135); lens[b] counts the current token. */
 int kb_attn_decode(const float *q, const float *k_cache, const float *v_cache, const int *lens,

@@ -47,6 +47,8 @@ SIGNATURES = {
     "kb_rope_kv": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _sz, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp]),
     "kb_attn_decode": (C.c_int, [_vp, _vp, _vp, _vp, _sz, C.c_int, C.c_int, C.c_int, _vp, _vp, _sz, _vp]),
     "kb_attn_decode_scratch_bytes": (_sz, [_sz, C.c_int]),
+    "kb_lm_head_argmax": (C.c_int, [_vp, _sz, _sz, _vp, _sz, _vp, _vp, _vp]),
+    "kb_decode_advance": (C.c_int, [_vp, _sz, _vp, _vp, _vp, _vp, _vp]),
     "kb_decoder_create": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, C.c_float, _vp, _vp, _vp, _vp, _vp,
                                     C.POINTER(_vp)]),
     "kb_decoder_destroy": (None, [_vp]),

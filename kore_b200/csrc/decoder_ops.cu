@@ -27,6 +27,11 @@
 
 namespace kb {
 
+// Every kernel here is launched with programmatic stream serialization, so its CTAs may be resident while the
+// producer of its inputs still runs.  Inputs that an earlier kernel of the step writes (activations, positions,
+// lengths, caches) are therefore plain pointers, read after the wait below: a `const __restrict__` pointer would let
+// the compiler use the non-coherent path and hoist the loads above the wait (a head kernel did exactly that and read
+// the previous step's row).  Only true constants (weights, gamma, the RoPE tables) keep the qualifier.
 __device__ __forceinline__ void pdl_release_and_wait() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -92,7 +97,7 @@ __device__ __forceinline__ void quantise_row_from_regs(const float (&vals)[CNT],
 
 constexpr int ROW_REGS = 36;  // elements per thread held in registers: rows up to 36 * 256 = 9216
 
-__global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
+__global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const float *x, const float *__restrict__ gamma,
                                                             int d, float eps, float *__restrict__ xn,
                                                             int8_t *__restrict__ xq, int ldq, float *__restrict__ sx,
                                                             int32_t *__restrict__ sumq) {
@@ -134,7 +139,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const float *__restr
 
 // PAIRS: the row alternates gate_i, up_i instead of holding the two halves one after the other
 template <bool PAIRS>
-__global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restrict__ gu, int f, size_t ld,
+__global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *gu, int f, size_t ld,
                                                            float *__restrict__ h_out, int8_t *__restrict__ xq, int ldq,
                                                            float *__restrict__ sx, int32_t *__restrict__ sumq) {
     __shared__ float red_f[32];
@@ -173,8 +178,7 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restri
 // grid (token, chunk): thread handles one (head, i) pair of q and k and one or two elements of
 // v, so every load of a token is in flight at once.  Rotation pairs are (i, i + hd/2) inside
 // each head; k and v go to row cache_rows[t] of the caches; cos/sin tables are [max_pos][hd/2].
-__global__ void __launch_bounds__(256) rope_kv_kernel(const float *__restrict__ qkv, const int *__restrict__ positions,
-                                                      const long long *__restrict__ cache_rows,
+__global__ void __launch_bounds__(256) rope_kv_kernel(const float *qkv, const int *positions, const long long *cache_rows,
                                                       const float *__restrict__ cos_t, const float *__restrict__ sin_t,
                                                       int n_heads, int hd, int lmax, float *__restrict__ q_out,
                                                       float *__restrict__ k_cache, float *__restrict__ v_cache) {
@@ -219,8 +223,7 @@ constexpr int ATT_MAX_SPLITS = 32;
 // with one 128-bit load per row; otherwise lane l owns dims l, l + 32, ...
 template <bool VEC4>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
-    const float *__restrict__ q, const float *__restrict__ k_cache, const float *__restrict__ v_cache,
-    const int *__restrict__ lens, int n_heads, int hd, int lmax, int splits, float *__restrict__ scratch,
+    const float *q, const float *k_cache, const float *v_cache, const int *lens, int n_heads, int hd, int lmax, int splits, float *__restrict__ scratch,
     int *__restrict__ counters, float *__restrict__ out) {
     __shared__ float s_m[ATT_WARPS], s_l[ATT_WARPS], s_acc[ATT_WARPS][ATT_MAX_HD];
     __shared__ int s_last;
@@ -327,11 +330,214 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(
     }
 }
 
+// ---- dense f32 head of a greedy decode step for a few sequences: logits = x W^T, argmax per token ----
+// The weights [vocab][d] are the stream (410 MB for 32000 x 3200).  A CTA of 512 threads keeps up to 8 tokens' rows of x
+// in registers (thread t owns the float4s t and t + 512 of every row: 64 registers for 8 tokens) and walks the
+// vocabulary two rows per step.  The weights travel global -> shared memory as 16-byte asynchronous copies in a ring
+// of HEAD_DEPTH steps; every thread copies exactly the float4s it later multiplies, so its own copy groups are all the
+// synchronisation the ring needs (192 KB in flight per SM).  The 16 partial dot products of a thread are reduced over
+// the warp with a transposing shuffle reduction and over the 16 warps through shared memory (one barrier per row pair,
+// two buffers).  blockIdx.y selects the group of 8 tokens; both groups walk the same rows at the same pace, so the
+// second read of a row is an L2 hit.  Thread (row of the pair, token) keeps the running maximum and folds it into
+// keys[token] at the end: key = (order-preserving bits of the logit << 32) | ~row, so the largest key is the largest
+// logit and, among equals, the lowest row — torch.argmax's answer.
+constexpr int HEAD_THREADS = 512;
+constexpr int HEAD_TOK = 8;
+constexpr int HEAD_ROWS = 2;
+constexpr int HEAD_V4 = 2;     // float4s of a row per thread: d <= 4 * 512 * 2
+constexpr int HEAD_DEPTH = 6;  // steps of the weight ring
+constexpr int HEAD_STEP_BYTES = HEAD_ROWS * HEAD_V4 * HEAD_THREADS * 16;
+
+__device__ __forceinline__ unsigned long long argmax_key(float v, int row) {
+    uint32_t b = __float_as_uint(v);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);  // unsigned order == float order (NaN aside)
+    return ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - (uint32_t)row);
+}
+
+__global__ void __launch_bounds__(HEAD_THREADS, 1) lm_head_argmax_kernel(const float *x, int n, int d,
+                                                                          const float *__restrict__ w, int vocab,
+                                                                          float *__restrict__ logits,
+                                                                          unsigned long long *__restrict__ keys) {
+    extern __shared__ __align__(128) uint8_t head_ring[];  // [HEAD_DEPTH][HEAD_ROWS][HEAD_V4][HEAD_THREADS] float4
+    __shared__ float part[2][HEAD_THREADS / 32][HEAD_ROWS * HEAD_TOK];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tok0 = blockIdx.y * HEAD_TOK;
+    const int nv4 = d >> 2;
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(head_ring) + threadIdx.x * 16u;
+    const int stride = gridDim.x * HEAD_ROWS;
+    // the weights do not depend on the previous kernel: the ring fills before the wait
+    auto issue = [&](int step) {  // rows r0 = (blockIdx.x + step * gridDim.x) * HEAD_ROWS
+        const int r0 = blockIdx.x * HEAD_ROWS + step * stride;
+        const uint32_t dst = ring + (uint32_t)(step % HEAD_DEPTH) * HEAD_STEP_BYTES;
+#pragma unroll
+        for (int r = 0; r < HEAD_ROWS; ++r)
+#pragma unroll
+            for (int i = 0; i < HEAD_V4; ++i) {
+                const int c = threadIdx.x + i * HEAD_THREADS;
+                const bool live = r0 + r < vocab && c < nv4;
+                const float *src = live ? w + (size_t)(r0 + r) * d + 4 * c : w;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + (uint32_t)((r * HEAD_V4 + i) * HEAD_THREADS * 16)),
+                             "l"(src), "r"(live ? 16 : 0)
+                             : "memory");
+            }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int steps = blockIdx.x * HEAD_ROWS < vocab ? (vocab - blockIdx.x * HEAD_ROWS + stride - 1) / stride : 0;
+    for (int sft = 0; sft < HEAD_DEPTH - 1; ++sft) {
+        if (sft < steps) issue(sft);
+        else asm volatile("cp.async.commit_group;" ::: "memory");  // keeps the group count in step
+    }
+    // starts behind the final norm by programmatic dependent launch, but releases no dependent of its own early: the
+    // launch that ends the step must see this kernel's keys, and it is the last word on the step's state
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float4 xr[HEAD_TOK][HEAD_V4];
+#pragma unroll
+    for (int t = 0; t < HEAD_TOK; ++t)
+#pragma unroll
+        for (int i = 0; i < HEAD_V4; ++i) {
+            const int c = threadIdx.x + i * HEAD_THREADS;
+            // read through L2 (the producer of x may still have been running when this CTA became resident)
+            xr[t][i] = (tok0 + t < n && c < nv4) ? __ldcg(reinterpret_cast<const float4 *>(x + (size_t)(tok0 + t) * d) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    // reducer threads: thread r * 8 + t (< 16) owns (row r of the pair, token t)
+    const int red_r = threadIdx.x >> 3, red_t = threadIdx.x & 7;
+    float best = -INFINITY;
+    int best_row = 0;
+    for (int it = 0; it < steps; ++it) {
+        if (it + HEAD_DEPTH - 1 < steps) issue(it + HEAD_DEPTH - 1);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group %0;" ::"n"(HEAD_DEPTH - 1) : "memory");  // this thread's copies of step `it` have landed
+        const int r0 = blockIdx.x * HEAD_ROWS + it * stride;
+        const uint8_t *src = head_ring + (size_t)(it % HEAD_DEPTH) * HEAD_STEP_BYTES + threadIdx.x * 16;
+        float4 wv[HEAD_ROWS][HEAD_V4];
+#pragma unroll
+        for (int r = 0; r < HEAD_ROWS; ++r)
+#pragma unroll
+            for (int i = 0; i < HEAD_V4; ++i) wv[r][i] = *reinterpret_cast<const float4 *>(src + (size_t)((r * HEAD_V4 + i) * HEAD_THREADS * 16));
+        float acc[HEAD_ROWS * HEAD_TOK];
+#pragma unroll
+        for (int r = 0; r < HEAD_ROWS; ++r)
+#pragma unroll
+            for (int t = 0; t < HEAD_TOK; ++t) {
+                float a = 0.0f;
+#pragma unroll
+                for (int i = 0; i < HEAD_V4; ++i) {
+                    a = fmaf(wv[r][i].x, xr[t][i].x, a);
+                    a = fmaf(wv[r][i].y, xr[t][i].y, a);
+                    a = fmaf(wv[r][i].z, xr[t][i].z, a);
+                    a = fmaf(wv[r][i].w, xr[t][i].w, a);
+                }
+                acc[r * HEAD_TOK + t] = a;
+            }
+        // 16 values over 32 lanes: at each step a lane keeps half of its values and receives the partner's share of them
+        // (8 + 4 + 2 + 1 shuffles), then one more step sums the two lanes that hold the same value
+        float a8[8];
+        {
+            const bool hi = (lane & 16) != 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a8[j] = (hi ? acc[8 + j] : acc[j]) + __shfl_xor_sync(0xffffffffu, hi ? acc[j] : acc[8 + j], 16);
+        }
+        float a4[4];
+        {
+            const bool hi = (lane & 8) != 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) a4[j] = (hi ? a8[4 + j] : a8[j]) + __shfl_xor_sync(0xffffffffu, hi ? a8[j] : a8[4 + j], 8);
+        }
+        float a2[2];
+        {
+            const bool hi = (lane & 4) != 0;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) a2[j] = (hi ? a4[2 + j] : a4[j]) + __shfl_xor_sync(0xffffffffu, hi ? a4[j] : a4[2 + j], 4);
+        }
+        float a1;
+        {
+            const bool hi = (lane & 2) != 0;
+            a1 = (hi ? a2[1] : a2[0]) + __shfl_xor_sync(0xffffffffu, hi ? a2[0] : a2[1], 2);
+        }
+        a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+        // an even lane now holds value index 8 * bit4 + 4 * bit3 + 2 * bit2 + bit1 of its lane number
+        if ((lane & 1) == 0) {
+            const int idx = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+            part[it & 1][warp][idx] = a1;
+        }
+        __syncthreads();
+        if (threadIdx.x < HEAD_ROWS * HEAD_TOK) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int wp = 0; wp < HEAD_THREADS / 32; ++wp) sum += part[it & 1][wp][threadIdx.x];
+            const int row = r0 + red_r, tok = tok0 + red_t;
+            if (row < vocab && tok < n) {
+                if (logits) logits[(size_t)tok * vocab + row] = sum;
+                if (sum > best) { best = sum; best_row = row; }  // rows ascend: the first maximum stays
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (threadIdx.x < HEAD_ROWS * HEAD_TOK && tok0 + red_t < n && best > -INFINITY) atomicMax(keys + tok0 + red_t, argmax_key(best, best_row));
+}
+
+// End of a greedy step: token = the row in the key, positions / lens / cache rows advance by one, keys are cleared.
+__global__ void decode_advance_kernel(unsigned long long *keys, int n, long long *tokens, int *positions, int *lens,
+                                      long long *cache_rows) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n) {
+        const unsigned long long key = keys[t];
+        tokens[t] = key ? (long long)(0xffffffffu - (uint32_t)(key & 0xffffffffull)) : 0;  // no finite logit: token 0
+        keys[t] = 0ull;
+        if (positions) positions[t] += 1;
+        if (lens) lens[t] += 1;
+        if (cache_rows) cache_rows[t] += 1;
+    }
+}
+
 }  // namespace kb
 
 using namespace kb;
 
 extern "C" {
+
+int kb_lm_head_argmax(const float *x, size_t n, size_t d, const float *w, size_t vocab, float *logits, unsigned long long *keys,
+                      kb_stream stream) {
+    if (!x || !w || !keys) return fail(KB_ERR_INVALID, "null pointer");
+    if (n == 0) return KB_OK;
+    if (n > 16) return fail(KB_ERR_UNSUPPORTED, "lm_head: %zu tokens (at most 16)", n);
+    if (d == 0 || d % 4 || d > (size_t)4 * HEAD_THREADS * HEAD_V4 || ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15))
+        return fail(KB_ERR_UNSUPPORTED, "lm_head: width %zu must be a multiple of 4 up to %d, with 16-byte aligned rows", d,
+                    4 * HEAD_THREADS * HEAD_V4);
+    if (vocab == 0 || vocab > ((size_t)1 << 31)) return fail(KB_ERR_INVALID, "lm_head: vocabulary size %zu", vocab);
+    int dev = 0;
+    KB_CUDA(cudaGetDevice(&dev));
+    const unsigned groups = (unsigned)((n + HEAD_TOK - 1) / HEAD_TOK);
+    size_t gx = (size_t)sm_count(dev) / groups;
+    const size_t pairs = (vocab + HEAD_ROWS - 1) / HEAD_ROWS;
+    if (gx > pairs) gx = pairs;
+    if (gx < 1) gx = 1;
+    const size_t smem = (size_t)HEAD_DEPTH * HEAD_STEP_BYTES;
+    if (int rc = set_dyn_smem_once(reinterpret_cast<const void *>(lm_head_argmax_kernel), dev, (int)smem, "lm_head smem attribute")) return rc;
+    static const bool pdl = [] { const char *v = getenv("KB_GEMV_PDL"); return !(v && *v == '0'); }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)gx, groups);
+    cfg.blockDim = dim3(HEAD_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, lm_head_argmax_kernel, x, (int)n, (int)d, w, (int)vocab, logits, keys);
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "lm_head launch");
+}
+
+int kb_decode_advance(unsigned long long *keys, size_t n, long long *tokens, int *positions, int *lens, long long *cache_rows,
+                      kb_stream stream) {
+    if (!keys || !tokens) return fail(KB_ERR_INVALID, "null pointer");
+    if (n == 0) return KB_OK;
+    decode_advance_kernel<<<(unsigned)((n + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(keys, (int)n, tokens, positions, lens,
+                                                                                                    cache_rows);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? KB_OK : cuda_fail(e, "decode advance launch");
+}
 
 int kb_rmsnorm_quant(const float *x, const float *gamma, size_t n, size_t d, float eps, float *xn, int8_t *xq, size_t ldq,
                      float *sx, int32_t *sumq, kb_stream stream) {

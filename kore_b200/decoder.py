@@ -7,8 +7,10 @@ projection + residual, RMSNorm, SwiGLU feed-forward + residual, final RMSNorm, d
 lm_head, greedy argmax.  q/k/v share one launch (their packed rows are concatenated, each
 keeping its own per-tensor scale through the per-row scale vector) and so do gate/up.
 RMSNorm and SwiGLU end in the per-token int8 quantiser, the residual adds live in the
-projection epilogues.  Embedding and lm_head are dense f32; prefill attention uses torch's
-scaled_dot_product_attention, decode attention the library's own kernel.
+projection epilogues.  Embedding and lm_head are dense f32 (in a decode step of up to 16
+sequences the head is the library's own streaming kernel with the argmax folded in; in prefill
+it is torch's matmul); prefill attention uses torch's scaled_dot_product_attention, decode
+attention the library's own kernel.
 
 For one sequence a decode step is ONE launch of the library's persistent decode-step kernel
 (``kb_decoder_step``: every phase of every layer, the lm_head GEMV and the argmax inside one
@@ -146,6 +148,7 @@ class BitNetDecoder:
         # persistent decode step (one launch per step) where the library supports the shape
         self.persistent = None
         self.hidden_step = torch.zeros((batch, d), dtype=torch.float32, device=self.dev)
+        self.head_keys = torch.zeros(batch, dtype=torch.int64, device=self.dev)  # argmax keys of the library's head
         if persistent is None:
             persistent = batch == 1
         if batch <= 2 and persistent:
@@ -275,6 +278,19 @@ class BitNetDecoder:
 
     def _decode_body(self):
         B = self._layers(self.batch, self.tokens, self.positions, self.cache_rows, self.lens)
+        if self.batch <= 16 and self.cfg.d_model % 4 == 0 and self.cfg.d_model <= 4096:
+            # the library's own head: final norm, streaming f32 lm_head with the argmax folded in, then one launch that
+            # stores the tokens and advances positions, lengths and cache rows
+            torch, cfg, lib, n = self.torch, self.cfg, self.lib, self.batch
+            sp = torch.cuda.current_stream(self.device).cuda_stream
+            xn = self._bufs[n]["xn"][:n]
+            _cabi.check(lib.kb_rmsnorm_quant(B["hidden"].data_ptr(), self.norm_f.data_ptr(), n, cfg.d_model, C.c_float(cfg.eps),
+                                             xn.data_ptr(), None, 0, None, None, sp))
+            _cabi.check(lib.kb_lm_head_argmax(xn.data_ptr(), n, cfg.d_model, self.lm_head.data_ptr(), cfg.vocab,
+                                              self.logits.data_ptr(), self.head_keys.data_ptr(), sp))
+            _cabi.check(lib.kb_decode_advance(self.head_keys.data_ptr(), n, self.tokens.data_ptr(), self.positions.data_ptr(),
+                                              self.lens.data_ptr(), self.cache_rows.data_ptr(), sp))
+            return
         logits = self._head(B["hidden"])
         self.torch.argmax(logits, dim=1, out=self.tokens)
         self.positions.add_(1)

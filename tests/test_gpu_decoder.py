@@ -429,3 +429,38 @@ def test_persistent_decode_step_matches_the_separate_kernels(env, batch):
     (tok_p, lg_p), (tok_s, lg_s) = outs
     assert (tok_p == tok_s).all()
     assert np.abs(lg_p - lg_s).max() <= 0.02 * np.abs(lg_s).max()
+
+
+@pytest.mark.parametrize("n,d,vocab", [(1, 256, 301), (5, 3200, 1000), (16, 3200, 3001), (9, 128, 77), (8, 4096, 515)])
+def test_lm_head_argmax_and_advance(env, n, d, vocab):
+    """The library's dense f32 head: logits against a float64 product, the argmax keys against numpy's argmax of the
+    kernel's own logits (first index among equal maxima), and the launch that ends a greedy step."""
+    t = env.torch
+    x = cases.gaussian(600 + n + d, (n, d), 1.0)
+    w = cases.gaussian(601 + vocab, (vocab, d), 0.05)
+    w[vocab // 3] = w[vocab // 2]  # two identical rows: equal logits for every token
+    x[0] = w[vocab // 2] * 5.0     # ... and token 0 points at them, so its maximum is a tie
+    xd, wd = t.from_numpy(x).cuda(), t.from_numpy(w).cuda()
+    logits = t.zeros((n, vocab), device="cuda")
+    keys = t.zeros(n, dtype=t.int64, device="cuda")
+    tokens = t.full((n,), -1, dtype=t.int64, device="cuda")
+    pos = t.arange(n, dtype=t.int32, device="cuda")
+    lens = t.arange(n, dtype=t.int32, device="cuda") + 1
+    rows = t.arange(n, dtype=t.int64, device="cuda") * 100
+    for rep in range(2):  # the second pass checks that the keys were cleared
+        env.cabi.check(env.lib.kb_lm_head_argmax(xd.data_ptr(), n, d, wd.data_ptr(), vocab, logits.data_ptr(), keys.data_ptr(), env.sp))
+        env.cabi.check(env.lib.kb_decode_advance(keys.data_ptr(), n, tokens.data_ptr(), pos.data_ptr(), lens.data_ptr(), rows.data_ptr(), env.sp))
+        t.cuda.synchronize()
+        lg = logits.cpu().numpy()
+        ref = x.astype(np.float64) @ w.astype(np.float64).T
+        assert np.abs(lg - ref).max() <= 1e-5 * np.abs(ref).max()
+        assert (tokens.cpu().numpy() == lg.argmax(axis=1)).all()
+        assert int(tokens[0]) == min(vocab // 3, vocab // 2)
+        assert (keys.cpu().numpy() == 0).all()
+        assert (pos.cpu().numpy() == np.arange(n) + rep + 1).all() and (lens.cpu().numpy() == np.arange(n) + rep + 2).all()
+        assert (rows.cpu().numpy() == np.arange(n) * 100 + rep + 1).all()
+    # without a logits buffer the keys are the same
+    env.cabi.check(env.lib.kb_lm_head_argmax(xd.data_ptr(), n, d, wd.data_ptr(), vocab, None, keys.data_ptr(), env.sp))
+    env.cabi.check(env.lib.kb_decode_advance(keys.data_ptr(), n, tokens.data_ptr(), None, None, None, env.sp))
+    t.cuda.synchronize()
+    assert (tokens.cpu().numpy() == logits.cpu().numpy().argmax(axis=1)).all()
