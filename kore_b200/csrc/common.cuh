@@ -152,6 +152,8 @@ struct FwdArgs {
     bool y_flagged;
     const int *flag_round;
     int flag_seq;
+    // the launch must not allocate: the medium-batch GEMM then never splits K (its scratch is created on first use)
+    bool no_alloc;
 };
 // kernel choice for `n` tokens when the caller passes KB_PATH_AUTO: the dp4a GEMV for one or two
 // tokens (up to four when it also has to quantise, which it does in its prologue), the

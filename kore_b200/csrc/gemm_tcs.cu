@@ -539,13 +539,13 @@ int launch_bn(const FwdArgs &a, cudaStream_t stream) {
     const int num_kb = (int)(L->kp / BK);
     static const int env_splits = []() { const char *e = getenv("KB_GEMM_SPLITS"); return e ? atoi(e) : 0; }();
     int splits = 1;
-    if (tiles * 2 <= sms && num_kb >= 48) {
+    if (tiles * 2 <= sms && num_kb >= 48 && !a.no_alloc) {
         splits = sms / tiles;
         if (splits > 8) splits = 8;
         if (splits > num_kb / 8) splits = num_kb / 8;
         if (splits < (BN > 64 ? 3 : 2)) splits = 1;
     }
-    if (env_splits >= 1) splits = env_splits;
+    if (env_splits >= 1 && !a.no_alloc) splits = env_splits;
     if (splits < 1) splits = 1;
     int split_slabs = ((num_kb + splits - 1) / splits + PKT_SLABS - 1) / PKT_SLABS * PKT_SLABS;
     splits = (num_kb + split_slabs - 1) / split_slabs;

@@ -88,6 +88,7 @@ extern "C" int kb_linear_forward_static(const kb_linear *h, const float *x, size
         if (rc == KB_OK) {
             FwdArgs a = {};
             a.lin = L; a.xq = xq; a.ldq = L->kp; a.sx = sx; a.sumq = sumq; a.n = n; a.y = y; a.ldy = 0;
+            a.no_alloc = true;  // no K split in the medium-batch GEMM: its scratch buffer would be an allocation
             rc = (n <= 8 && gemv_supports(L, n)) ? launch_gemv(a, st) : launch_gemm_tc(a, st);
         }
     }

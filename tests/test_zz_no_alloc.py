@@ -80,3 +80,28 @@ def test_static_scratch_rejects_oversized_and_bad_arguments():
     _cabi.check(lib.kb_linear_forward_static(lay.handle, x.data_ptr(), 255, 4096, y.data_ptr(), stream))
     torch.cuda.synchronize()
     assert not y[:255].any()  # zero activations -> zero outputs (no bias)
+
+
+def test_static_scratch_forward_takes_no_device_memory_where_the_regular_path_would():
+    """A layer of few row tiles with long rows: the regular entry splits K over CTAs and creates a scratch buffer on
+    first use; the static entry must not, and still returns the same values (integer partial sums are exact)."""
+    import torch
+
+    from kore_b200 import _cabi, nn
+
+    lib = _cabi.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    lay = nn.QuatLinear.new(_gauss(21, (200, 8192), 0.02))
+    n, k, m = 40, 8192, 200
+    x = torch.from_numpy(_gauss(22, (n, k), 1.0)).cuda()
+    y_static = torch.full((n, m), float("nan"), device="cuda")
+    y_regular = torch.full((n, m), float("nan"), device="cuda")
+    _cabi.check(lib.kb_linear_forward_static(lay.handle, x.data_ptr(), n, k, y_static.data_ptr(), stream))  # warm-up: loads the kernels
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    _cabi.check(lib.kb_linear_forward_static(lay.handle, x.data_ptr(), n, k, y_static.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    _cabi.check(lib.kb_linear_forward_ex(lay.handle, x.data_ptr(), n, k, y_regular.data_ptr(), 0, None, _cabi.PATH_GEMM_TC, None, 0, stream))
+    torch.cuda.synchronize()
+    assert torch.equal(y_static, y_regular)
