@@ -160,7 +160,9 @@ int kb_linear_forward_q8(const kb_linear *h, const int8_t *xq, size_t ldq, const
  * y = ((float(acc) * w_scale) * s + bias) + resid.  Stands in for the project() +
  * residual_add() pairs of the reference's decoder loop
  * (crates/kore-edge/src/runtime.rs:197-212,254-265).  With f32 input and the GEMM path a
- * caller workspace (kb_linear_workspace_bytes) is required; nothing is allocated here. */
+ * caller workspace (kb_linear_workspace_bytes) is required; nothing is allocated per call (the
+ * medium-batch GEMM creates one scratch buffer per stream the first time it splits K, see
+ * kb_linear_forward_static for the entry that never allocates). */
 int kb_linear_forward_fused(const kb_linear *h, const float *x, const int8_t *xq, size_t ldq,
                             const float *sx, const int32_t *sumq, size_t n, const float *resid,
                             float *y, size_t ldy, int path, void *workspace,
