@@ -354,14 +354,17 @@ __device__ __forceinline__ unsigned long long argmax_key(float v, int row) {
     return ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - (uint32_t)row);
 }
 
+// TOK = tokens per CTA (8, 4 or 2: fewer tokens, fewer multiply-adds per weight)
+template <int TOK>
 __global__ void __launch_bounds__(HEAD_THREADS, 1) lm_head_argmax_kernel(const float *x, int n, int d,
                                                                           const float *__restrict__ w, int vocab,
                                                                           float *__restrict__ logits,
                                                                           unsigned long long *__restrict__ keys) {
     extern __shared__ __align__(128) uint8_t head_ring[];  // [HEAD_DEPTH][HEAD_ROWS][HEAD_V4][HEAD_THREADS] float4
-    __shared__ float part[2][HEAD_THREADS / 32][HEAD_ROWS * HEAD_TOK];
+    constexpr int NVAL = HEAD_ROWS * TOK;  // dot products a thread carries per step: 16, 8 or 4
+    __shared__ float part[2][HEAD_THREADS / 32][NVAL];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int tok0 = blockIdx.y * HEAD_TOK;
+    const int tok0 = blockIdx.y * TOK;
     const int nv4 = d >> 2;
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(head_ring) + threadIdx.x * 16u;
     const int stride = gridDim.x * HEAD_ROWS;
@@ -390,17 +393,17 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) lm_head_argmax_kernel(const f
     // starts behind the final norm by programmatic dependent launch, but releases no dependent of its own early: the
     // launch that ends the step must see this kernel's keys, and it is the last word on the step's state
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    float4 xr[HEAD_TOK][HEAD_V4];
+    float4 xr[TOK][HEAD_V4];
 #pragma unroll
-    for (int t = 0; t < HEAD_TOK; ++t)
+    for (int t = 0; t < TOK; ++t)
 #pragma unroll
         for (int i = 0; i < HEAD_V4; ++i) {
             const int c = threadIdx.x + i * HEAD_THREADS;
             // read through L2 (the producer of x may still have been running when this CTA became resident)
             xr[t][i] = (tok0 + t < n && c < nv4) ? __ldcg(reinterpret_cast<const float4 *>(x + (size_t)(tok0 + t) * d) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-    // reducer threads: thread r * 8 + t (< 16) owns (row r of the pair, token t)
-    const int red_r = threadIdx.x >> 3, red_t = threadIdx.x & 7;
+    // reducer threads: thread r * TOK + t (< NVAL) owns (row r of the pair, token t)
+    const int red_r = threadIdx.x / TOK, red_t = threadIdx.x % TOK;
     float best = -INFINITY;
     int best_row = 0;
     for (int it = 0; it < steps; ++it) {
@@ -414,11 +417,11 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) lm_head_argmax_kernel(const f
         for (int r = 0; r < HEAD_ROWS; ++r)
 #pragma unroll
             for (int i = 0; i < HEAD_V4; ++i) wv[r][i] = *reinterpret_cast<const float4 *>(src + (size_t)((r * HEAD_V4 + i) * HEAD_THREADS * 16));
-        float acc[HEAD_ROWS * HEAD_TOK];
+        float acc[NVAL];
 #pragma unroll
         for (int r = 0; r < HEAD_ROWS; ++r)
 #pragma unroll
-            for (int t = 0; t < HEAD_TOK; ++t) {
+            for (int t = 0; t < TOK; ++t) {
                 float a = 0.0f;
 #pragma unroll
                 for (int i = 0; i < HEAD_V4; ++i) {
@@ -427,41 +430,33 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) lm_head_argmax_kernel(const f
                     a = fmaf(wv[r][i].z, xr[t][i].z, a);
                     a = fmaf(wv[r][i].w, xr[t][i].w, a);
                 }
-                acc[r * HEAD_TOK + t] = a;
+                acc[r * TOK + t] = a;
             }
-        // 16 values over 32 lanes: at each step a lane keeps half of its values and receives the partner's share of them
-        // (8 + 4 + 2 + 1 shuffles), then one more step sums the two lanes that hold the same value
-        float a8[8];
+        // NVAL values over 32 lanes: while more than one value is left, a lane keeps half of its values and receives the
+        // partner's share of them (lane bit 16, 8, ... decides which half); the remaining steps sum the lanes that hold the
+        // same value.  Value index = the kept-half bits in order, most significant first.
+        int idx = 0;
         {
-            const bool hi = (lane & 16) != 0;
+            int cnt = NVAL;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) a8[j] = (hi ? acc[8 + j] : acc[j]) + __shfl_xor_sync(0xffffffffu, hi ? acc[j] : acc[8 + j], 16);
-        }
-        float a4[4];
-        {
-            const bool hi = (lane & 8) != 0;
+            for (int off = 16; off > 0; off >>= 1) {
+                if (cnt > 1) {
+                    const bool hi = (lane & off) != 0;
+                    cnt >>= 1;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) a4[j] = (hi ? a8[4 + j] : a8[j]) + __shfl_xor_sync(0xffffffffu, hi ? a8[j] : a8[4 + j], 8);
+                    for (int j = 0; j < NVAL / 2; ++j)
+                        if (j < cnt) acc[j] = (hi ? acc[cnt + j] : acc[j]) + __shfl_xor_sync(0xffffffffu, hi ? acc[j] : acc[cnt + j], off);
+                    idx = idx * 2 + (hi ? 1 : 0);
+                } else {
+                    acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], off);
+                }
+            }
         }
-        float a2[2];
-        {
-            const bool hi = (lane & 4) != 0;
-#pragma unroll
-            for (int j = 0; j < 2; ++j) a2[j] = (hi ? a4[2 + j] : a4[j]) + __shfl_xor_sync(0xffffffffu, hi ? a4[j] : a4[2 + j], 4);
-        }
-        float a1;
-        {
-            const bool hi = (lane & 2) != 0;
-            a1 = (hi ? a2[1] : a2[0]) + __shfl_xor_sync(0xffffffffu, hi ? a2[0] : a2[1], 2);
-        }
-        a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
-        // an even lane now holds value index 8 * bit4 + 4 * bit3 + 2 * bit2 + bit1 of its lane number
-        if ((lane & 1) == 0) {
-            const int idx = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
-            part[it & 1][warp][idx] = a1;
-        }
+        // lanes whose low bits (those of the summing steps) are zero publish
+        constexpr int SUM_MASK = NVAL == 16 ? 1 : (NVAL == 8 ? 3 : 7);
+        if ((lane & SUM_MASK) == 0) part[it & 1][warp][idx] = acc[0];
         __syncthreads();
-        if (threadIdx.x < HEAD_ROWS * HEAD_TOK) {
+        if (threadIdx.x < NVAL) {
             float sum = 0.0f;
 #pragma unroll
             for (int wp = 0; wp < HEAD_THREADS / 32; ++wp) sum += part[it & 1][wp][threadIdx.x];
@@ -473,7 +468,7 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) lm_head_argmax_kernel(const f
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    if (threadIdx.x < HEAD_ROWS * HEAD_TOK && tok0 + red_t < n && best > -INFINITY) atomicMax(keys + tok0 + red_t, argmax_key(best, best_row));
+    if (threadIdx.x < NVAL && tok0 + red_t < n && best > -INFINITY) atomicMax(keys + tok0 + red_t, argmax_key(best, best_row));
 }
 
 // End of a greedy step: token = the row in the key, positions / lens / cache rows advance by one, keys are cleared.
@@ -507,13 +502,16 @@ int kb_lm_head_argmax(const float *x, size_t n, size_t d, const float *w, size_t
     if (vocab == 0 || vocab > ((size_t)1 << 31)) return fail(KB_ERR_INVALID, "lm_head: vocabulary size %zu", vocab);
     int dev = 0;
     KB_CUDA(cudaGetDevice(&dev));
-    const unsigned groups = (unsigned)((n + HEAD_TOK - 1) / HEAD_TOK);
+    const int tok = n <= 2 ? 2 : (n <= 4 ? 4 : HEAD_TOK);
+    const unsigned groups = (unsigned)((n + tok - 1) / tok);
     size_t gx = (size_t)sm_count(dev) / groups;
     const size_t pairs = (vocab + HEAD_ROWS - 1) / HEAD_ROWS;
     if (gx > pairs) gx = pairs;
     if (gx < 1) gx = 1;
     const size_t smem = (size_t)HEAD_DEPTH * HEAD_STEP_BYTES;
-    if (int rc = set_dyn_smem_once(reinterpret_cast<const void *>(lm_head_argmax_kernel), dev, (int)smem, "lm_head smem attribute")) return rc;
+    void (*kern)(const float *, int, int, const float *, int, float *, unsigned long long *) =
+        tok == 2 ? lm_head_argmax_kernel<2> : (tok == 4 ? lm_head_argmax_kernel<4> : lm_head_argmax_kernel<HEAD_TOK>);
+    if (int rc = set_dyn_smem_once(reinterpret_cast<const void *>(kern), dev, (int)smem, "lm_head smem attribute")) return rc;
     static const bool pdl = [] { const char *v = getenv("KB_GEMV_PDL"); return !(v && *v == '0'); }();
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)gx, groups);
@@ -525,7 +523,7 @@ int kb_lm_head_argmax(const float *x, size_t n, size_t d, const float *w, size_t
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, lm_head_argmax_kernel, x, (int)n, (int)d, w, (int)vocab, logits, keys);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, x, (int)n, (int)d, w, (int)vocab, logits, keys);
     return e == cudaSuccess ? KB_OK : cuda_fail(e, "lm_head launch");
 }
 
