@@ -264,7 +264,7 @@ def main():
                     help="headline step: one grouped launch over the pool of independent layers (default), or one "
                          "quantiser + one GEMV launch per layer spread over --streams streams")
     ap.add_argument("--only", default=None, choices=["gemv_big", "gemv_4096", "group_4096", "small_batch", "medium_batch", "prefill_up", "prefill_down",
-                             "decode_step", "decode_step_batch16", "attn_decode", "medium_batch_few_tiles", "flagged_chain", "stream_batch8"],
+                             "decode_step", "decode_step_graph", "decode_step_batch16", "attn_decode", "medium_batch_few_tiles", "flagged_chain", "stream_batch8"],
                     help="run one small case and print its own JSON line (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -555,11 +555,14 @@ def decoder_case(torch, lib, _cabi, dev, args):
     batch-16 decode attention kernel on one layer's cache."""
     from kore_b200 import decoder
 
-    if args.only in ("decode_step", "decode_step_batch16"):
-        batch = 1 if args.only == "decode_step" else 16
+    if args.only in ("decode_step", "decode_step_graph", "decode_step_batch16"):
+        batch = 16 if args.only == "decode_step_batch16" else 1
         cfg = decoder.DecoderConfig(n_layers=8 if batch == 1 else 4)
         weights = decoder.random_weights(cfg, seed=4000, device=dev.index)
-        dec = decoder.BitNetDecoder(cfg, weights, batch=batch, device=dev.index)
+        # decode_step: the persistent kernel (the decoder's choice for one sequence); decode_step_graph: the same step as
+        # a CUDA graph of the separate kernels
+        dec = decoder.BitNetDecoder(cfg, weights, batch=batch, device=dev.index,
+                                    persistent=False if args.only == "decode_step_graph" else None)
         prompt = torch.randint(0, cfg.vocab, (batch, 512), generator=torch.Generator().manual_seed(4999)).to(dev)
         torch.argmax(dec.prefill(prompt), dim=1, out=dec.tokens)
         for _ in range(max(1, args.warmup)):
@@ -607,7 +610,7 @@ def decoder_case(torch, lib, _cabi, dev, args):
 
 def single_case(torch, lib, _cabi, nn, kernels, dev, args):
     """One kernel on one small case, a handful of eager launches: the command profiled with ncu."""
-    if args.only in ("decode_step", "decode_step_batch16", "attn_decode"):
+    if args.only in ("decode_step", "decode_step_graph", "decode_step_batch16", "attn_decode"):
         return decoder_case(torch, lib, _cabi, dev, args)
     if args.only == "flagged_chain":
         return flagged_chain_case(torch, lib, _cabi, nn, dev, args)

@@ -293,8 +293,10 @@ int auto_path(const Linear *lin, size_t n, bool prequantised) {
     // (measured, one / two tokens, streaming kernel against the GEMV: 14336 x 8192 8.6 / 11.2 against 8.9 / 11.8 us,
     // 4096 x 28672 9.3 / 14.1 against 12.6 / 17.4, 8192 x 28672 14.8 / 22.0 against 16.9 / 19.6, 28672 x 8192
     // 13.9 / 17.1 against 13.4 / 17.9)
+    // and many short rows (9600 x 3200: 5.2 / 7.3 against 4.1 / 5.5 us; 17280 x 3200: 6.4 / 9.4 against 5.8 / 7.3)
     const bool big = lin->m_alloc * lin->row_bytes > ((size_t)32 << 20), wide = lin->kp >= 16384;
-    if (prequantised && ((n == 1 && (!big || wide)) || (n == 2 && !(big && wide))) && gemv_stream_supports(lin, n))
+    const bool many_short_rows = lin->kp < 4096 && lin->m >= 8192;
+    if (prequantised && !many_short_rows && ((n == 1 && (!big || wide)) || (n == 2 && !(big && wide))) && gemv_stream_supports(lin, n))
         return KB_PATH_GEMV_STREAM;
     if (n <= gemv_max && gemv_supports(lin, n)) return KB_PATH_GEMV;
     // 3..8 tokens of a large layer: the streaming kernel's MMA form (19 us against 23 for 4 tokens of 8192 -> 28672);

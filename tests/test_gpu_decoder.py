@@ -116,7 +116,7 @@ def test_projection_with_rmsnorm_prologue(env, n, m, k):
     lay.close()
 
 
-@pytest.mark.parametrize("n,f,k", [(1, 8640, 3200), (2, 150, 256)])
+@pytest.mark.parametrize("n,f,k", [(1, 8640, 3200), (2, 8640, 3200), (2, 150, 256), (1, 4096, 512)])
 def test_swiglu_epilogue_and_prescaled_projection(env, n, f, k):
     """gate/up projection with interleaved rows + SwiGLU epilogue + atomic max|h|, then the down
     projection quantising with that maximum: equal to the separate kernels bit for bit"""
